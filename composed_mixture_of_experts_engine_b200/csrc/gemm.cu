@@ -1,0 +1,620 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a: TMA -> shared memory -> tcgen05.mma with
+// the fp32 accumulator in tensor memory -> tcgen05.ld epilogue.  One kernel serves the dense
+// projections, the grouped expert GEMMs (rows grouped in 128-row tiles per expert), the grouped
+// weight-gradient GEMMs (contraction over each expert's rows) and the fused SwiGLU epilogues.
+//
+// Replaces the per-expert Python loop of three cuBLAS calls in the reference
+// (pkg/distributed/moe_layer.py:197-198, 327-337) with one launch per GEMM of the layer.
+//
+// CTA layout (192 threads, one CTA per SM):
+//   warp 0      TMA producer (one elected lane)
+//   warp 1      TMEM allocation + MMA issue (one lane)
+//   warps 2..5  epilogue: each warp owns the TMEM lane quadrant (warp_id % 4)
+// Tile 128 x 256 x 64, 4 shared-memory stages (48 KiB each), two accumulators of 256 TMEM
+// columns so that the epilogue of tile i overlaps the main loop of tile i+1.
+#include "gemm.cuh"
+
+#include <cstdio>
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace cmoe {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int CHUNK_BYTES = 64 * BK * 2;  // one 64 x 64 bf16 box (MN-major operands) = 8 KiB
+constexpr int GEMM_THREADS = 192;
+constexpr int TMEM_COLS = 2 * BN;  // 512: two accumulators
+constexpr int GROUP_M_SWIZZLE = 8;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+struct KParams {
+  int mode, M, N, K, groups;
+  int a_mn, b_mn;
+  int b_group_rows, split_n;
+  const int* tile_group;
+  const int* num_m_tiles;
+  const int* group_offsets;
+  void* D;
+  long long ldd, d_group_stride;
+  int d_fp32, accumulate;
+  const __nv_bfloat16* aux_in;
+  long long ld_aux_in;
+  __nv_bfloat16* aux_out;
+  long long ld_aux_out;
+  const uint32_t* ready_flags;
+  int ready_stride, ready_count;
+  uint32_t ready_target;
+  int* status;
+  unsigned long long timeout_ns;
+  int n_cols_per_tile;  // output columns covered by one tile (256, or 128 with the SwiGLU forward)
+};
+
+struct Tile {
+  int m0, n0;    // origin of the output tile (rows are group-local in grouped-K mode)
+  int group;     // expert / group id (0 when dense)
+  int a_mn0;     // A: first M index of the tile (row coordinate if K-major, inner coordinate if M-major)
+  int a_k0;      // A: first K index
+  int b_n0;      // B K-major: row coordinate of the first 128 tile rows; N-major: inner coordinate
+  int b_n1;      // B K-major: row coordinate of tile rows 128..255
+  int b_k0;      // B: first K index (inner coordinate if K-major, row coordinate if N-major)
+  int k_blocks;  // number of 64-wide K blocks
+  bool skip;
+};
+
+__device__ __forceinline__ int total_tiles(const KParams& p, int m_tiles, int n_tiles) {
+  return (p.mode == GEMM_GROUPED_K ? p.groups : 1) * m_tiles * n_tiles;
+}
+
+__device__ __forceinline__ Tile decode_tile(const KParams& p, int t, int m_tiles, int n_tiles) {
+  Tile ti;
+  ti.skip = false;
+  int g = 0;
+  if (p.mode == GEMM_GROUPED_K) {
+    g = t / (m_tiles * n_tiles);
+    t -= g * m_tiles * n_tiles;
+  }
+  // walk the tile grid in bands of GROUP_M_SWIZZLE row tiles so that concurrently running CTAs
+  // share both A and B tiles in L2
+  const int band = t / (GROUP_M_SWIZZLE * n_tiles);
+  const int r = t - band * GROUP_M_SWIZZLE * n_tiles;
+  const int band_rows = min(GROUP_M_SWIZZLE, m_tiles - band * GROUP_M_SWIZZLE);
+  const int mt = band * GROUP_M_SWIZZLE + r % band_rows;
+  const int nt = r / band_rows;
+  ti.m0 = mt * BM;
+  ti.n0 = nt * p.n_cols_per_tile;
+  ti.group = g;
+  if (p.mode == GEMM_DENSE) {
+    ti.a_mn0 = ti.m0;
+    ti.a_k0 = 0;
+    ti.b_n0 = ti.n0;
+    ti.b_n1 = ti.n0 + 128;
+    ti.b_k0 = 0;
+    ti.k_blocks = (p.K + BK - 1) / BK;
+  } else if (p.mode == GEMM_GROUPED_M) {
+    g = p.tile_group[mt];
+    ti.group = g;
+    if (g < 0) {
+      ti.skip = true;
+      g = 0;
+    }
+    ti.a_mn0 = ti.m0;
+    ti.a_k0 = 0;
+    if (p.b_mn) {
+      ti.b_n0 = ti.n0;
+      ti.b_n1 = 0;
+      ti.b_k0 = g * p.b_group_rows;
+    } else {
+      ti.b_n0 = g * p.b_group_rows + ti.n0;
+      ti.b_n1 = p.split_n ? (g * p.b_group_rows + p.split_n + ti.n0) : (ti.b_n0 + 128);
+      ti.b_k0 = 0;
+    }
+    ti.k_blocks = (p.K + BK - 1) / BK;
+  } else {  // grouped-K: both operands are MN-major, contraction over the rows of group g
+    const int r0 = p.group_offsets[g];
+    const int r1 = p.group_offsets[g + 1];
+    ti.a_mn0 = ti.m0;
+    ti.a_k0 = r0;
+    ti.b_n0 = ti.n0;
+    ti.b_n1 = 0;
+    ti.b_k0 = r0;
+    ti.k_blocks = (r1 - r0 + BK - 1) / BK;
+  }
+  return ti;
+}
+
+__device__ __forceinline__ float sigmoidf_fast(float x) { return 1.0f / (1.0f + __expf(-x)); }
+
+// 32 fp32 values of one output row -> bf16 (or fp32) in global memory, columns [col, col+32) masked by n_limit
+__device__ __forceinline__ void store_row_chunk(void* D, long long ldd, int d_fp32, int accumulate, long long row,
+                                                int col, int n_limit, const float (&v)[32]) {
+  if (col >= n_limit) return;
+  if (d_fp32) {
+    float* dst = reinterpret_cast<float*>(D) + row * ldd + col;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      if (col + j < n_limit) {  // N is a multiple of 8, so groups of 4 are all-in or all-out
+        float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        if (accumulate) {
+          const float4 old = *reinterpret_cast<const float4*>(dst + j);
+          o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+        }
+        *reinterpret_cast<float4*>(dst + j) = o;
+      }
+    }
+  } else {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(D) + row * ldd + col;
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      if (col + j < n_limit) {
+        float f[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) f[q] = v[j + q];
+        if (accumulate) {
+          const uint4 old = *reinterpret_cast<const uint4*>(dst + j);
+          const float2 o0 = unpack_bf16x2(old.x), o1 = unpack_bf16x2(old.y), o2 = unpack_bf16x2(old.z),
+                       o3 = unpack_bf16x2(old.w);
+          f[0] += o0.x; f[1] += o0.y; f[2] += o1.x; f[3] += o1.y;
+          f[4] += o2.x; f[5] += o2.y; f[6] += o3.x; f[7] += o3.y;
+        }
+        uint4 o;
+        o.x = pack_bf16x2(f[0], f[1]);
+        o.y = pack_bf16x2(f[2], f[3]);
+        o.z = pack_bf16x2(f[4], f[5]);
+        o.w = pack_bf16x2(f[6], f[7]);
+        *reinterpret_cast<uint4*>(dst + j) = o;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void load_row_chunk_bf16(const __nv_bfloat16* src, float (&v)[32]) {
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    const uint4 x = *reinterpret_cast<const uint4*>(src + j);
+    const float2 a = unpack_bf16x2(x.x), b = unpack_bf16x2(x.y), c = unpack_bf16x2(x.z), d = unpack_bf16x2(x.w);
+    v[j] = a.x; v[j + 1] = a.y; v[j + 2] = b.x; v[j + 3] = b.y;
+    v[j + 4] = c.x; v[j + 5] = c.y; v[j + 6] = d.x; v[j + 7] = d.y;
+  }
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const KParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full_bar = bars;                 // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;       // [STAGES]
+  uint64_t* tfull_bar = bars + 2 * STAGES;   // [2]
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 128);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  WaitCtx wc;
+  wc.abort_flag = abort_flag;
+  wc.status = p.status;
+  wc.timeout_ns = p.timeout_ns;
+
+  int m_tiles;
+  if (p.mode == GEMM_GROUPED_M) {
+    m_tiles = *p.num_m_tiles;
+  } else {
+    m_tiles = (p.M + BM - 1) / BM;
+  }
+  const int n_tiles = (p.N + p.n_cols_per_tile - 1) / p.n_cols_per_tile;
+  const int n_total = total_tiles(p, m_tiles, n_tiles);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < n_total; t += gridDim.x) {
+        const Tile ti = decode_tile(p, t, m_tiles, n_tiles);
+        if (ti.skip || ti.k_blocks == 0) continue;
+        if (p.ready_flags != nullptr) {
+          const uint32_t* f = p.ready_flags + (long long)ti.group * p.ready_stride;
+          for (int s = 0; s < p.ready_count; ++s) flag_wait_ge(f + s, p.ready_target, wc);
+        }
+        for (int kb = 0; kb < ti.k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, wc, ST_TIMEOUT_SMEM_EMPTY)) break;
+          mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
+          uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
+          uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
+          const int k = kb * BK;
+          if (p.a_mn) {
+            tma_load_2d(a_dst, &tmA, &full_bar[stage], ti.a_mn0, ti.a_k0 + k);
+            tma_load_2d(a_dst + CHUNK_BYTES, &tmA, &full_bar[stage], ti.a_mn0 + 64, ti.a_k0 + k);
+          } else {
+            tma_load_2d(a_dst, &tmA, &full_bar[stage], ti.a_k0 + k, ti.a_mn0);
+          }
+          if (p.b_mn) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              tma_load_2d(b_dst + j * CHUNK_BYTES, &tmB, &full_bar[stage], ti.b_n0 + 64 * j, ti.b_k0 + k);
+          } else {
+            tma_load_2d(b_dst, &tmB, &full_bar[stage], ti.b_k0 + k, ti.b_n0);
+            tma_load_2d(b_dst + 128 * BK * 2, &tmB, &full_bar[stage], ti.b_k0 + k, ti.b_n1);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (*abort_flag) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn, p.b_mn);
+      const uint32_t a_lbo = p.a_mn ? CHUNK_BYTES : 16;
+      const uint32_t b_lbo = p.b_mn ? CHUNK_BYTES : 16;
+      const uint32_t a_kstep = p.a_mn ? 2048u : 32u;  // bytes per UMMA_K = 16 step
+      const uint32_t b_kstep = p.b_mn ? 2048u : 32u;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int t = blockIdx.x; t < n_total; t += gridDim.x) {
+        const Tile ti = decode_tile(p, t, m_tiles, n_tiles);
+        if (ti.skip || ti.k_blocks == 0) continue;
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, wc, ST_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < ti.k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, wc, ST_TIMEOUT_SMEM_FULL)) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + stage * A_STAGE_BYTES);
+          const uint32_t b_addr = smem_u32(sB + stage * B_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t ad = make_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, 1024);
+            const uint64_t bd = make_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, 1024);
+            umma_bf16_ss(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // the stage is free once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        umma_commit(&tfull_bar[acc]);
+        if (*abort_flag) break;
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const int m_limit = (p.mode == GEMM_GROUPED_M) ? (m_tiles * BM) : p.M;
+    for (int t = blockIdx.x; t < n_total; t += gridDim.x) {
+      const Tile ti = decode_tile(p, t, m_tiles, n_tiles);
+      if (ti.skip) continue;
+      const long long row = ti.m0 + row_in_tile;
+      const bool row_ok = (ti.m0 + row_in_tile) < m_limit;
+      void* Dg = p.D;
+      if (p.mode == GEMM_GROUPED_K) {
+        Dg = p.d_fp32 ? static_cast<void*>(reinterpret_cast<float*>(p.D) + ti.group * p.d_group_stride)
+                      : static_cast<void*>(reinterpret_cast<__nv_bfloat16*>(p.D) + ti.group * p.d_group_stride);
+      }
+      if (ti.k_blocks == 0) {
+        // nothing to contract over: the product is zero
+        if (EPI == EPI_STORE && !p.accumulate && row_ok) {
+          float z[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) z[j] = 0.f;
+          for (int c = 0; c < BN / 32; ++c) store_row_chunk(Dg, p.ldd, p.d_fp32, 0, row, ti.n0 + c * 32, p.N, z);
+        }
+        continue;
+      }
+      const bool ok = mbar_wait(&tfull_bar[acc], acc_phase, wc, ST_TIMEOUT_TMEM_FULL);
+      tc_fence_after();
+      const uint32_t t_acc = tmem_base + acc * BN + lane_base;
+      if (ok) {
+        if (EPI == EPI_STORE) {
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            if (ti.n0 + c * 32 >= p.N) break;  // uniform across the warp
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(t_acc + c * 32, r);
+            tmem_ld_wait();
+            if (row_ok) {
+              float v[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+              store_row_chunk(Dg, p.ldd, p.d_fp32, p.accumulate, row, ti.n0 + c * 32, p.N, v);
+            }
+          }
+        } else if (EPI == EPI_SWIGLU_FWD) {
+          // accumulator columns [0,128) = gate, [128,256) = up for output columns n0 .. n0+127
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            if (ti.n0 + c * 32 >= p.N) break;
+            uint32_t rg[32], ru[32];
+            tmem_ld_32x32b_x32(t_acc + c * 32, rg);
+            tmem_ld_32x32b_x32(t_acc + 128 + c * 32, ru);
+            tmem_ld_wait();
+            if (row_ok) {
+              float g[32], u[32], h[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                g[j] = __uint_as_float(rg[j]);
+                u[j] = __uint_as_float(ru[j]);
+                h[j] = g[j] * sigmoidf_fast(g[j]) * u[j];
+              }
+              const int col = ti.n0 + c * 32;
+              store_row_chunk(Dg, p.ldd, 0, 0, row, col, p.N, h);
+              if (p.aux_out != nullptr) {
+                store_row_chunk(p.aux_out, p.ld_aux_out, 0, 0, row, col, p.N, g);
+                store_row_chunk(p.aux_out + p.N, p.ld_aux_out, 0, 0, row, col, p.N, u);
+              }
+            }
+          }
+        } else {  // EPI_SWIGLU_BWD: acc = dH; D = [dGate | dUp] with row stride ldd (>= 2N)
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            const int col = ti.n0 + c * 32;
+            if (col >= p.N) break;
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(t_acc + c * 32, r);
+            tmem_ld_wait();
+            if (row_ok) {
+              float g[32], u[32], dg[32], du[32];
+              const __nv_bfloat16* gu = p.aux_in + row * p.ld_aux_in + col;
+              if (col + 32 <= p.N) {
+                load_row_chunk_bf16(gu, g);
+                load_row_chunk_bf16(gu + p.N, u);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  const bool in = (col + j) < p.N;
+                  g[j] = in ? __bfloat162float(gu[j]) : 0.f;
+                  u[j] = in ? __bfloat162float(gu[p.N + j]) : 0.f;
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float dh = __uint_as_float(r[j]);
+                const float s = sigmoidf_fast(g[j]);
+                const float silu = g[j] * s;
+                dg[j] = dh * u[j] * (s * (1.f + g[j] * (1.f - s)));
+                du[j] = dh * silu;
+              }
+              store_row_chunk(Dg, p.ldd, 0, 0, row, col, p.N, dg);
+              store_row_chunk(reinterpret_cast<__nv_bfloat16*>(Dg) + p.N, p.ldd, 0, 0, row, col, p.N, du);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&tempty_bar[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+      if (*abort_flag) break;
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (*abort_flag) {
+      // a wait ran out: give copies and MMAs that are still in flight time to land before the
+      // shared and tensor memory of this CTA are handed back
+      for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
+// host side
+// ----------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  });
+  return fn;
+}
+
+struct TmapKey {
+  const void* ptr;
+  long long rows, cols, ld;
+  int box_rows;
+  bool operator==(const TmapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h = h * 1000003u ^ static_cast<size_t>(k.rows);
+    h = h * 1000003u ^ static_cast<size_t>(k.cols);
+    h = h * 1000003u ^ static_cast<size_t>(k.ld);
+    h = h * 1000003u ^ static_cast<size_t>(k.box_rows);
+    return h;
+  }
+};
+
+// bf16 row-major [rows, cols] (leading dimension ld), box = 64 columns x box_rows rows, 128-byte swizzle
+cudaError_t make_tmap(CUtensorMap* out, const void* ptr, long long rows, long long cols, long long ld, int box_rows) {
+  static std::mutex mu;
+  static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  TmapKey key{ptr, rows, cols, ld, box_rows};
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return cudaSuccess;
+    }
+  }
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0 || (ld * 2) % 16 != 0 || cols <= 0 || rows <= 0)
+    return cudaErrorInvalidValue;
+  cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t gstride[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estride[2] = {1u, 1u};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estride,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    std::fprintf(stderr, "cmoe: cuTensorMapEncodeTiled failed (%d) rows=%lld cols=%lld ld=%lld box_rows=%d\n",
+                 static_cast<int>(r), rows, cols, ld, box_rows);
+    return cudaErrorInvalidValue;
+  }
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    if (cache.size() > 8192) cache.clear();
+    cache.emplace(key, *out);
+  }
+  return cudaSuccess;
+}
+
+template <int EPI>
+cudaError_t launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const KParams& kp, int grid,
+                           cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  gemm_kernel<EPI><<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, kp);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream) {
+  if (a.N % 8 != 0 || a.N <= 0) return cudaErrorInvalidValue;
+  if (a.mode == GEMM_GROUPED_K && !(a.a_mn && a.b_mn)) return cudaErrorInvalidValue;
+  if (a.mode == GEMM_GROUPED_M && a.a_mn) return cudaErrorInvalidValue;
+  if (a.epilogue == EPI_SWIGLU_FWD && (a.b_mn || a.split_n <= 0)) return cudaErrorInvalidValue;
+
+  CUtensorMap tmA, tmB;
+  cudaError_t e = make_tmap(&tmA, a.A, a.a_rows, a.a_cols, a.a_ld, a.a_mn ? 64 : 128);
+  if (e != cudaSuccess) return e;
+  e = make_tmap(&tmB, a.B, a.b_rows, a.b_cols, a.b_ld, a.b_mn ? 64 : 128);
+  if (e != cudaSuccess) return e;
+
+  KParams kp;
+  kp.mode = a.mode;
+  kp.M = a.M;
+  kp.N = a.N;
+  kp.K = a.K;
+  kp.groups = a.groups;
+  kp.a_mn = a.a_mn;
+  kp.b_mn = a.b_mn;
+  kp.b_group_rows = static_cast<int>(a.b_group_rows);
+  kp.split_n = a.split_n;
+  kp.tile_group = a.tile_group;
+  kp.num_m_tiles = a.num_m_tiles;
+  kp.group_offsets = a.group_offsets;
+  kp.D = a.D;
+  kp.ldd = a.ldd;
+  kp.d_group_stride = a.d_group_stride;
+  kp.d_fp32 = a.d_fp32;
+  kp.accumulate = a.accumulate;
+  kp.aux_in = reinterpret_cast<const __nv_bfloat16*>(a.aux_in);
+  kp.ld_aux_in = a.ld_aux_in;
+  kp.aux_out = reinterpret_cast<__nv_bfloat16*>(a.aux_out);
+  kp.ld_aux_out = a.ld_aux_out;
+  kp.ready_flags = a.ready_flags;
+  kp.ready_stride = a.ready_stride;
+  kp.ready_count = a.ready_count;
+  kp.ready_target = a.ready_target;
+  kp.status = a.status;
+  kp.timeout_ns = a.timeout_ns ? a.timeout_ns : kDefaultTimeoutNs;
+  kp.n_cols_per_tile = (a.epilogue == EPI_SWIGLU_FWD) ? 128 : BN;
+
+  int num_sms = a.num_sms;
+  if (num_sms <= 0) {
+    int dev = 0;
+    e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    static int cached_dev = -1, cached_sms = 0;
+    if (cached_dev != dev) {
+      e = cudaDeviceGetAttribute(&cached_sms, cudaDevAttrMultiProcessorCount, dev);
+      if (e != cudaSuccess) return e;
+      cached_dev = dev;
+    }
+    num_sms = cached_sms;
+  }
+  const long long n_tiles = (a.N + kp.n_cols_per_tile - 1) / kp.n_cols_per_tile;
+  long long m_tiles = (a.mode == GEMM_GROUPED_M) ? a.max_m_tiles : (a.M + BM - 1) / BM;
+  long long tiles = m_tiles * n_tiles * (a.mode == GEMM_GROUPED_K ? a.groups : 1);
+  if (tiles <= 0) return cudaSuccess;
+  const int grid = static_cast<int>(tiles < num_sms ? tiles : num_sms);
+
+  switch (a.epilogue) {
+    case EPI_STORE:
+      return launch_variant<EPI_STORE>(tmA, tmB, kp, grid, stream);
+    case EPI_SWIGLU_FWD:
+      return launch_variant<EPI_SWIGLU_FWD>(tmA, tmB, kp, grid, stream);
+    case EPI_SWIGLU_BWD:
+      return launch_variant<EPI_SWIGLU_BWD>(tmA, tmB, kp, grid, stream);
+    default:
+      return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace cmoe

@@ -1,0 +1,635 @@
+// Bandwidth-bound kernels of the training step: RMSNorm, RoPE, fused AdamW (+ global-norm clipping
+// without a host round trip), cross-entropy with in-place gradient, and the MoE bookkeeping kernels
+// (deterministic expert-sorted row plan, row gather, weighted combine).
+//
+// Reference counterparts: RMSNorm eager ops (pkg/models/moe.py:83-86); torch.optim.AdamW +
+// clip_grad_norm_ + F.cross_entropy (train.py:207-212, 297-303, 322-323); argsort /
+// repeat_interleave / per-k scatter loop of the MoE layer (pkg/distributed/moe_layer.py:309-353);
+// capacity dropping (moe_layer.py:64-155).  RoPE has no counterpart there.
+#include "ops.cuh"
+
+#include "common.cuh"
+
+namespace cmoe {
+
+namespace {
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 x = *reinterpret_cast<const uint4*>(p);
+  const float2 a = unpack_bf16x2(x.x), b = unpack_bf16x2(x.y), c = unpack_bf16x2(x.z), d = unpack_bf16x2(x.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  uint4 o;
+  o.x = pack_bf16x2(f[0], f[1]);
+  o.y = pack_bf16x2(f[2], f[3]);
+  o.z = pack_bf16x2(f[4], f[5]);
+  o.w = pack_bf16x2(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = o;
+}
+
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (threadIdx.x < THREADS / 32) ? red[threadIdx.x] : 0.f;
+  if (warp == 0) {
+    t = warp_sum(t);
+    if (lane == 0) red[0] = t;
+  }
+  __syncthreads();
+  return red[0];
+}
+
+// ------------------------------------------------------------------------------------ RMSNorm
+constexpr int RN_THREADS = 256;
+constexpr int RN_MAX_VEC = 4;  // up to H = 256 * 8 * 4 = 8192 columns kept in registers
+
+__global__ void __launch_bounds__(RN_THREADS) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                 const __nv_bfloat16* __restrict__ w,
+                                                                 __nv_bfloat16* __restrict__ y,
+                                                                 float* __restrict__ rstd, long long rows, int H,
+                                                                 float eps) {
+  __shared__ float red[RN_THREADS / 32];
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * H;
+  float v[RN_MAX_VEC][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < RN_MAX_VEC; ++i) {
+    const int c = (i * RN_THREADS + threadIdx.x) * 8;
+    if (c < H) {
+      load8(xr + c, v[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+    }
+  }
+  ss = block_sum<RN_THREADS>(ss, red);
+  const float r = rsqrtf(ss / H + eps);
+  if (threadIdx.x == 0 && rstd) rstd[row] = r;
+#pragma unroll
+  for (int i = 0; i < RN_MAX_VEC; ++i) {
+    const int c = (i * RN_THREADS + threadIdx.x) * 8;
+    if (c < H) {
+      float wv[8], o[8];
+      load8(w + c, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = v[i][j] * r * wv[j];
+      store8(y + row * H + c, o);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                                 const __nv_bfloat16* __restrict__ x,
+                                                                 const __nv_bfloat16* __restrict__ w,
+                                                                 const float* __restrict__ rstd,
+                                                                 __nv_bfloat16* __restrict__ dx, float* __restrict__ dw,
+                                                                 long long rows, int H) {
+  __shared__ float red[RN_THREADS / 32];
+  float wv[RN_MAX_VEC][8], dwacc[RN_MAX_VEC][8];
+#pragma unroll
+  for (int i = 0; i < RN_MAX_VEC; ++i) {
+    const int c = (i * RN_THREADS + threadIdx.x) * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+    if (c < H) load8(w + c, wv[i]);
+  }
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float r = rstd[row];
+    float xh[RN_MAX_VEC][8], g[RN_MAX_VEC][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < RN_MAX_VEC; ++i) {
+      const int c = (i * RN_THREADS + threadIdx.x) * 8;
+      if (c < H) {
+        float xv[8], dv[8];
+        load8(x + row * H + c, xv);
+        load8(dy + row * H + c, dv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = xv[j] * r;
+          g[i][j] = dv[j] * wv[i][j];
+          dot += g[i][j] * xh[i][j];
+          dwacc[i][j] += dv[j] * xh[i][j];
+        }
+      }
+    }
+    dot = block_sum<RN_THREADS>(dot, red) / H;
+#pragma unroll
+    for (int i = 0; i < RN_MAX_VEC; ++i) {
+      const int c = (i * RN_THREADS + threadIdx.x) * 8;
+      if (c < H) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = r * (g[i][j] - xh[i][j] * dot);
+        store8(dx + row * H + c, o);
+      }
+    }
+  }
+  if (dw) {
+#pragma unroll
+    for (int i = 0; i < RN_MAX_VEC; ++i) {
+      const int c = (i * RN_THREADS + threadIdx.x) * 8;
+      if (c < H) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) atomicAdd(dw + c + j, dwacc[i][j]);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------ RoPE
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ t, const float* __restrict__ cos_tab,
+                            const float* __restrict__ sin_tab, long long rows, int seq, int heads, int head_dim,
+                            long long row_stride, int inverse) {
+  const int half = head_dim / 2;
+  const int vec_per_head = half / 8;
+  const long long total = rows * heads * vec_per_head;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int vi = static_cast<int>(i % vec_per_head);
+    const long long rh = i / vec_per_head;
+    const int h = static_cast<int>(rh % heads);
+    const long long r = rh / heads;
+    const int pos = static_cast<int>(r % seq);
+    __nv_bfloat16* base = t + r * row_stride + static_cast<long long>(h) * head_dim + vi * 8;
+    float a[8], b[8], oa[8], ob[8];
+    load8(base, a);
+    load8(base + half, b);
+    const float* cp = cos_tab + static_cast<long long>(pos) * half + vi * 8;
+    const float* sp = sin_tab + static_cast<long long>(pos) * half + vi * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float c = cp[j];
+      const float s = inverse ? -sp[j] : sp[j];
+      oa[j] = a[j] * c - b[j] * s;
+      ob[j] = b[j] * c + a[j] * s;
+    }
+    store8(base, oa);
+    store8(base + half, ob);
+  }
+}
+
+// ------------------------------------------------------------------------------------ AdamW
+__global__ void adamw_kernel(const AdamWArgs a) {
+  float gs = a.grad_scale;
+  if (a.max_norm > 0.f && a.sumsq != nullptr) {
+    const float norm = sqrtf(*a.sumsq) * a.grad_scale;
+    gs *= fminf(1.f, a.max_norm / (norm + 1e-6f));
+  }
+  const float inv_bc1 = 1.f / a.bias_corr1;
+  const float inv_sqrt_bc2 = rsqrtf(a.bias_corr2);
+  const long long n4 = a.n / 4;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4; i += stride) {
+    float4 p = reinterpret_cast<const float4*>(a.p32)[i];
+    float4 m = reinterpret_cast<const float4*>(a.m)[i];
+    float4 v = reinterpret_cast<const float4*>(a.v)[i];
+    float g[4];
+    if (a.grad_is_bf16) {
+      const uint2 raw = reinterpret_cast<const uint2*>(a.grad)[i];
+      const float2 g0 = unpack_bf16x2(raw.x), g1 = unpack_bf16x2(raw.y);
+      g[0] = g0.x; g[1] = g0.y; g[2] = g1.x; g[3] = g1.y;
+      if (a.zero_grad) reinterpret_cast<uint2*>(const_cast<void*>(a.grad))[i] = make_uint2(0u, 0u);
+    } else {
+      const float4 raw = reinterpret_cast<const float4*>(a.grad)[i];
+      g[0] = raw.x; g[1] = raw.y; g[2] = raw.z; g[3] = raw.w;
+      if (a.zero_grad) reinterpret_cast<float4*>(const_cast<void*>(a.grad))[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float pp[4] = {p.x, p.y, p.z, p.w}, mm[4] = {m.x, m.y, m.z, m.w}, vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float gj = g[j] * gs;
+      mm[j] = a.beta1 * mm[j] + (1.f - a.beta1) * gj;
+      vv[j] = a.beta2 * vv[j] + (1.f - a.beta2) * gj * gj;
+      const float denom = sqrtf(vv[j]) * inv_sqrt_bc2 + a.eps;
+      pp[j] = pp[j] * (1.f - a.lr * a.weight_decay) - a.lr * (mm[j] * inv_bc1) / denom;
+    }
+    reinterpret_cast<float4*>(a.p32)[i] = make_float4(pp[0], pp[1], pp[2], pp[3]);
+    reinterpret_cast<float4*>(a.m)[i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    reinterpret_cast<float4*>(a.v)[i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    if (a.p16) reinterpret_cast<uint2*>(a.p16)[i] = make_uint2(pack_bf16x2(pp[0], pp[1]), pack_bf16x2(pp[2], pp[3]));
+  }
+  // tail (n not a multiple of 4)
+  const long long tail0 = n4 * 4;
+  const long long gi = tail0 + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (gi < a.n) {
+    float g = a.grad_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.grad)[gi])
+                             : reinterpret_cast<const float*>(a.grad)[gi];
+    if (a.zero_grad) {
+      if (a.grad_is_bf16) reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(a.grad))[gi] = __float2bfloat16(0.f);
+      else reinterpret_cast<float*>(const_cast<void*>(a.grad))[gi] = 0.f;
+    }
+    g *= gs;
+    const float m = a.beta1 * a.m[gi] + (1.f - a.beta1) * g;
+    const float v = a.beta2 * a.v[gi] + (1.f - a.beta2) * g * g;
+    const float denom = sqrtf(v) * inv_sqrt_bc2 + a.eps;
+    const float p = a.p32[gi] * (1.f - a.lr * a.weight_decay) - a.lr * (m * inv_bc1) / denom;
+    a.p32[gi] = p;
+    a.m[gi] = m;
+    a.v[gi] = v;
+    if (a.p16) reinterpret_cast<__nv_bfloat16*>(a.p16)[gi] = __float2bfloat16(p);
+  }
+}
+
+__global__ void __launch_bounds__(256) sumsq_kernel(const void* x, int is_bf16, long long n, float* out) {
+  __shared__ float red[8];
+  float acc = 0.f;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  if (is_bf16) {
+    const long long n8 = n / 8;
+    const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8; i += stride) {
+      float f[8];
+      load8(xb + i * 8, f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc += f[j] * f[j];
+    }
+    const long long gi = n8 * 8 + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (gi < n) {
+      const float f = __bfloat162float(xb[gi]);
+      acc += f * f;
+    }
+  } else {
+    const long long n4 = n / 4;
+    const float* xf = reinterpret_cast<const float*>(x);
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4; i += stride) {
+      const float4 f = reinterpret_cast<const float4*>(xf)[i];
+      acc += f.x * f.x + f.y * f.y + f.z * f.z + f.w * f.w;
+    }
+    const long long gi = n4 * 4 + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (gi < n) acc += xf[gi] * xf[gi];
+  }
+  acc = block_sum<256>(acc, red);
+  if (threadIdx.x == 0) atomicAdd(out, acc);
+}
+
+// ------------------------------------------------------------------------------------ cross-entropy
+constexpr int CE_THREADS = 512;
+__global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(__nv_bfloat16* __restrict__ logits,
+                                                                   const long long* __restrict__ targets,
+                                                                   float* __restrict__ loss_sum, long long rows, int V,
+                                                                   long long ld, float grad_scale) {
+  __shared__ float red[CE_THREADS / 32];
+  __shared__ float s_max, s_sum;
+  const long long row = blockIdx.x;
+  __nv_bfloat16* lr = logits + row * ld;
+  const long long tgt = targets[row];
+  const int nvec = V / 8;
+  // online max / sum-exp per thread, then merged across the block
+  float mx = -INFINITY, se = 0.f;
+  for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
+    float f[8];
+    load8(lr + i * 8, f);
+    float lm = f[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) lm = fmaxf(lm, f[j]);
+    if (lm > mx) {
+      se *= __expf(mx - lm);
+      mx = lm;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) se += __expf(f[j] - mx);
+  }
+  for (int c = nvec * 8 + threadIdx.x; c < V; c += CE_THREADS) {
+    const float f = __bfloat162float(lr[c]);
+    if (f > mx) {
+      se *= __expf(mx - f);
+      mx = f;
+    }
+    se += __expf(f - mx);
+  }
+  // block max
+  float bm = warp_max(mx);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) red[warp] = bm;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < CE_THREADS / 32 ? red[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) s_max = t;
+  }
+  __syncthreads();
+  bm = s_max;
+  se = (mx == -INFINITY) ? 0.f : se * __expf(mx - bm);
+  se = block_sum<CE_THREADS>(se, red);
+  if (threadIdx.x == 0) s_sum = se;
+  __syncthreads();
+  const float lse = bm + logf(s_sum);
+  const bool ignore = tgt < 0 || tgt >= V;
+  if (threadIdx.x == 0 && !ignore) atomicAdd(loss_sum, lse - __bfloat162float(lr[tgt]));
+  __syncthreads();
+  const float gs = ignore ? 0.f : grad_scale;
+  for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
+    float f[8], o[8];
+    load8(lr + i * 8, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float p = __expf(f[j] - lse);
+      o[j] = (p - ((i * 8 + j) == tgt ? 1.f : 0.f)) * gs;
+    }
+    store8(lr + i * 8, o);
+  }
+  for (int c = nvec * 8 + threadIdx.x; c < V; c += CE_THREADS) {
+    const float p = __expf(__bfloat162float(lr[c]) - lse);
+    lr[c] = __float2bfloat16((p - (c == tgt ? 1.f : 0.f)) * gs);
+  }
+}
+
+// ------------------------------------------------------------------------------------ MoE plan
+constexpr int PLAN_UNIT_SLOTS = 256;  // slots ranked by one warp
+constexpr int PLAN_WARPS = 8;
+
+__device__ __forceinline__ int plan_bin(const MoePlanArgs& a, long long slot) {
+  const int e = a.topk_idx[slot] - a.expert_lo;
+  if (e < 0 || e >= a.n_local) return -1;
+  return a.per_k_bins ? e * a.K + static_cast<int>(slot % a.K) : e;
+}
+
+// pass 1: per-unit histogram.  hist[unit][bin]
+__global__ void __launch_bounds__(PLAN_WARPS * 32) moe_plan_hist_kernel(const MoePlanArgs a, int nbins, int n_units) {
+  const int unit = blockIdx.x * PLAN_WARPS + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (unit >= n_units) return;
+  int* hist = a.scratch + static_cast<long long>(unit) * nbins;
+  for (int b = lane; b < nbins; b += 32) hist[b] = 0;
+  __syncwarp();
+  const long long s0 = static_cast<long long>(unit) * PLAN_UNIT_SLOTS;
+  for (int r = 0; r < PLAN_UNIT_SLOTS / 32; ++r) {
+    const long long slot = s0 + r * 32 + lane;
+    const int bin = slot < a.n_slots ? plan_bin(a, slot) : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, bin);
+    if (bin >= 0 && (peers & ((1u << lane) - 1u)) == 0u) hist[bin] += __popc(peers);
+    __syncwarp();
+  }
+}
+
+// pass 2 (one CTA): exclusive prefix of hist over units within each bin, clipped bin totals,
+// 128-row-padded expert offsets, tile table
+__global__ void __launch_bounds__(1024) moe_plan_scan_kernel(const MoePlanArgs a, int nbins, int n_units) {
+  int* hist = a.scratch;
+  int* bin_base = a.scratch + static_cast<long long>(n_units) * nbins;
+  int* bin_total = bin_base + nbins;
+  for (int b = threadIdx.x; b < nbins; b += blockDim.x) {
+    int run = 0;
+    for (int u = 0; u < n_units; ++u) {
+      const int c = hist[static_cast<long long>(u) * nbins + b];
+      hist[static_cast<long long>(u) * nbins + b] = run;
+      run += c;
+    }
+    bin_total[b] = (a.capacity > 0 && run > a.capacity) ? a.capacity : run;
+  }
+  __syncthreads();
+  __shared__ int s_total_rows;
+  if (threadIdx.x == 0) {
+    const int kb = a.per_k_bins ? a.K : 1;
+    int off = 0;
+    for (int e = 0; e < a.n_local; ++e) {
+      a.group_offsets[e] = off;
+      int cnt = 0;
+      for (int k = 0; k < kb; ++k) {
+        bin_base[e * kb + k] = off + cnt;
+        cnt += bin_total[e * kb + k];
+      }
+      a.counts_kept[e] = cnt;
+      off += (cnt + 127) / 128 * 128;
+    }
+    a.group_offsets[a.n_local] = off;
+    *a.num_m_tiles = off / 128;
+    s_total_rows = off;
+  }
+  __syncthreads();
+  const int tiles = s_total_rows / 128;
+  for (int t = threadIdx.x; t < tiles; t += blockDim.x) {
+    const int row = t * 128;
+    int lo = 0, hi = a.n_local;  // largest e with group_offsets[e] <= row
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (a.group_offsets[mid] <= row) lo = mid; else hi = mid;
+    }
+    a.tile_group[t] = lo;
+  }
+}
+
+// pass 3: destination row of every slot
+__global__ void __launch_bounds__(PLAN_WARPS * 32) moe_plan_assign_kernel(const MoePlanArgs a, int nbins, int n_units) {
+  const int unit = blockIdx.x * PLAN_WARPS + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (unit >= n_units) return;
+  int* hist = a.scratch + static_cast<long long>(unit) * nbins;
+  const int* bin_base = a.scratch + static_cast<long long>(n_units) * nbins;
+  const long long s0 = static_cast<long long>(unit) * PLAN_UNIT_SLOTS;
+  for (int r = 0; r < PLAN_UNIT_SLOTS / 32; ++r) {
+    const long long slot = s0 + r * 32 + lane;
+    const int bin = slot < a.n_slots ? plan_bin(a, slot) : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, bin);
+    int row = -1;
+    if (bin >= 0) {
+      const int rank = hist[bin] + __popc(peers & ((1u << lane) - 1u));
+      if (a.capacity <= 0 || rank < a.capacity) row = bin_base[bin] + rank;
+    }
+    __syncwarp();
+    if (bin >= 0 && (peers & ((1u << lane) - 1u)) == 0u) hist[bin] += __popc(peers);
+    __syncwarp();
+    if (slot < a.n_slots) {
+      a.slot_row[slot] = row;
+      if (row >= 0 && row < a.cap_rows) a.row_slot[row] = static_cast<int>(slot);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------ gather / combine
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ row_slot,
+                                   int slot_div, const float* __restrict__ slot_scale,
+                                   __nv_bfloat16* __restrict__ out, long long cap_rows,
+                                   const int* __restrict__ num_m_tiles, int H, long long ld_src, long long ld_out) {
+  const long long n_rows = num_m_tiles ? min(static_cast<long long>(*num_m_tiles) * 128, cap_rows) : cap_rows;
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (long long r = blockIdx.x * static_cast<long long>(warps_per_block) + (threadIdx.x >> 5); r < n_rows;
+       r += static_cast<long long>(gridDim.x) * warps_per_block) {
+    const int slot = row_slot[r];
+    __nv_bfloat16* o = out + r * ld_out;
+    if (slot < 0) {
+      for (int c = lane * 8; c < H; c += 256) *reinterpret_cast<uint4*>(o + c) = make_uint4(0u, 0u, 0u, 0u);
+    } else {
+      const __nv_bfloat16* s = src + static_cast<long long>(slot / slot_div) * ld_src;
+      if (slot_scale == nullptr) {
+        for (int c = lane * 8; c < H; c += 256) *reinterpret_cast<uint4*>(o + c) = *reinterpret_cast<const uint4*>(s + c);
+      } else {
+        const float sc = slot_scale[slot];
+        for (int c = lane * 8; c < H; c += 256) {
+          float f[8];
+          load8(s + c, f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] *= sc;
+          store8(o + c, f);
+        }
+      }
+    }
+  }
+}
+
+__global__ void combine_rows_kernel(const __nv_bfloat16* __restrict__ rows, const int* __restrict__ slot_row,
+                                    const float* __restrict__ w, __nv_bfloat16* __restrict__ y, long long n_tokens,
+                                    int K, int H, long long ld_rows, long long ld_y) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (long long t = blockIdx.x * static_cast<long long>(warps_per_block) + (threadIdx.x >> 5); t < n_tokens;
+       t += static_cast<long long>(gridDim.x) * warps_per_block) {
+    for (int c = lane * 8; c < H; c += 256) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int k = 0; k < K; ++k) {
+        const int r = slot_row[t * K + k];
+        if (r < 0) continue;
+        const float wk = w ? w[t * K + k] : 1.f;
+        float f[8];
+        load8(rows + static_cast<long long>(r) * ld_rows + c, f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += wk * f[j];
+      }
+      store8(y + t * ld_y + c, acc);
+    }
+  }
+}
+
+__global__ void combine_bwd_w_kernel(const __nv_bfloat16* __restrict__ rows, const int* __restrict__ slot_row,
+                                     const __nv_bfloat16* __restrict__ dy, float* __restrict__ dw, long long n_tokens,
+                                     int K, int H, long long ld_rows, long long ld_dy) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long n_slots = n_tokens * K;
+  for (long long s = blockIdx.x * static_cast<long long>(warps_per_block) + (threadIdx.x >> 5); s < n_slots;
+       s += static_cast<long long>(gridDim.x) * warps_per_block) {
+    const int r = slot_row[s];
+    float acc = 0.f;
+    if (r >= 0) {
+      const __nv_bfloat16* a = rows + static_cast<long long>(r) * ld_rows;
+      const __nv_bfloat16* b = dy + (s / K) * ld_dy;
+      for (int c = lane * 8; c < H; c += 256) {
+        float fa[8], fb[8];
+        load8(a + c, fa);
+        load8(b + c, fb);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc += fa[j] * fb[j];
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) dw[s] = acc;
+  }
+}
+
+inline unsigned grid_for(long long work_items, int per_block, int max_blocks) {
+  long long b = (work_items + per_block - 1) / per_block;
+  if (b < 1) b = 1;
+  if (b > max_blocks) b = max_blocks;
+  return static_cast<unsigned>(b);
+}
+
+}  // namespace
+
+cudaError_t launch_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int H, float eps,
+                               cudaStream_t stream) {
+  if (H % 8 != 0 || H > RN_THREADS * 8 * RN_MAX_VEC || rows <= 0) return cudaErrorInvalidValue;
+  rmsnorm_fwd_kernel<<<static_cast<unsigned>(rows), RN_THREADS, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(w),
+      reinterpret_cast<__nv_bfloat16*>(y), rstd, rows, H, eps);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw,
+                               long long rows, int H, int num_sms, cudaStream_t stream) {
+  if (H % 8 != 0 || H > RN_THREADS * 8 * RN_MAX_VEC || rows <= 0) return cudaErrorInvalidValue;
+  const unsigned grid = grid_for(rows, 1, (num_sms > 0 ? num_sms : 148) * 4);
+  rmsnorm_bwd_kernel<<<grid, RN_THREADS, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x),
+      reinterpret_cast<const __nv_bfloat16*>(w), rstd, reinterpret_cast<__nv_bfloat16*>(dx), dw, rows, H);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rope(void* t, const float* cos_tab, const float* sin_tab, long long rows, int seq, int heads,
+                        int head_dim, long long row_stride, int inverse, cudaStream_t stream) {
+  if (head_dim % 16 != 0 || rows <= 0) return cudaErrorInvalidValue;
+  const long long total = rows * heads * (head_dim / 16);
+  rope_kernel<<<grid_for(total, 256, 148 * 16), 256, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(t), cos_tab, sin_tab,
+                                                                  rows, seq, heads, head_dim, row_stride, inverse);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_adamw(const AdamWArgs& a, cudaStream_t stream) {
+  if (a.n <= 0) return cudaSuccess;
+  adamw_kernel<<<grid_for(a.n / 4 + 1, 256, 148 * 16), 256, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_sumsq(const void* x, int is_bf16, long long n, float* out, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  sumsq_kernel<<<grid_for(n / 8 + 1, 256, 148 * 8), 256, 0, stream>>>(x, is_bf16, n, out);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_cross_entropy(void* logits, const long long* targets, float* loss_sum, long long rows, int V,
+                                 long long ld, float grad_scale, cudaStream_t stream) {
+  if (rows <= 0) return cudaSuccess;
+  if (ld % 8 != 0) return cudaErrorInvalidValue;
+  cross_entropy_kernel<<<static_cast<unsigned>(rows), CE_THREADS, 0, stream>>>(
+      reinterpret_cast<__nv_bfloat16*>(logits), targets, loss_sum, rows, V, ld, grad_scale);
+  return cudaGetLastError();
+}
+
+size_t moe_plan_scratch_words(long long n_slots, int n_local, int K, int per_k_bins) {
+  const long long nbins = static_cast<long long>(n_local) * (per_k_bins ? K : 1);
+  const long long n_units = (n_slots + PLAN_UNIT_SLOTS - 1) / PLAN_UNIT_SLOTS;
+  return static_cast<size_t>(n_units * nbins + 2 * nbins);
+}
+
+cudaError_t launch_moe_plan(const MoePlanArgs& a, cudaStream_t stream) {
+  if (a.n_slots <= 0 || a.n_local <= 0) return cudaErrorInvalidValue;
+  const int nbins = a.n_local * (a.per_k_bins ? a.K : 1);
+  const int n_units = static_cast<int>((a.n_slots + PLAN_UNIT_SLOTS - 1) / PLAN_UNIT_SLOTS);
+  cudaError_t e = cudaMemsetAsync(a.row_slot, 0xFF, sizeof(int) * a.cap_rows, stream);
+  if (e != cudaSuccess) return e;
+  e = cudaMemsetAsync(a.tile_group, 0xFF, sizeof(int) * ((a.cap_rows + 127) / 128), stream);
+  if (e != cudaSuccess) return e;
+  const unsigned blocks = static_cast<unsigned>((n_units + PLAN_WARPS - 1) / PLAN_WARPS);
+  moe_plan_hist_kernel<<<blocks, PLAN_WARPS * 32, 0, stream>>>(a, nbins, n_units);
+  moe_plan_scan_kernel<<<1, 1024, 0, stream>>>(a, nbins, n_units);
+  moe_plan_assign_kernel<<<blocks, PLAN_WARPS * 32, 0, stream>>>(a, nbins, n_units);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gather_rows(const void* src, const int* row_slot, int slot_div, const float* slot_scale, void* out,
+                               long long cap_rows, const int* num_m_tiles, int H, long long ld_src, long long ld_out,
+                               cudaStream_t stream) {
+  if (H % 8 != 0 || cap_rows <= 0 || slot_div <= 0) return cudaErrorInvalidValue;
+  gather_rows_kernel<<<grid_for(cap_rows, 8, 148 * 8), 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(src), row_slot, slot_div, slot_scale,
+      reinterpret_cast<__nv_bfloat16*>(out), cap_rows, num_m_tiles, H, ld_src, ld_out);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_combine_rows(const void* rows, const int* slot_row, const float* w, void* y, long long n_tokens,
+                                int K, int H, long long ld_rows, long long ld_y, cudaStream_t stream) {
+  if (H % 8 != 0 || n_tokens <= 0) return cudaErrorInvalidValue;
+  combine_rows_kernel<<<grid_for(n_tokens, 8, 148 * 8), 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(rows), slot_row, w, reinterpret_cast<__nv_bfloat16*>(y), n_tokens, K, H,
+      ld_rows, ld_y);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_combine_bwd_w(const void* rows, const int* slot_row, const void* dy, float* dw, long long n_tokens,
+                                 int K, int H, long long ld_rows, long long ld_dy, cudaStream_t stream) {
+  if (H % 8 != 0 || n_tokens <= 0) return cudaErrorInvalidValue;
+  combine_bwd_w_kernel<<<grid_for(n_tokens * K, 8, 148 * 8), 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(rows), slot_row, reinterpret_cast<const __nv_bfloat16*>(dy), dw, n_tokens,
+      K, H, ld_rows, ld_dy);
+  return cudaGetLastError();
+}
+
+}  // namespace cmoe

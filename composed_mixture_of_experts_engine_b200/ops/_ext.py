@@ -1,0 +1,132 @@
+"""Builds and loads the sm_100a CUDA extension of this package.
+
+The extension lives in ``csrc/`` and is built in-tree (``_build/``) with
+``-gencode arch=compute_100a,code=sm_100a``.  A stamp file records a hash of the
+sources, so a machine that received a built ``.so`` together with the sources
+imports it without compiling again.
+
+``ext()`` returns the module or raises; it never falls back silently: on a
+machine with a GPU the CUDA path is the only path of the hot ops.
+"""
+
+from __future__ import annotations
+
+import hashlib
+import importlib.util
+import os
+import sys
+import threading
+from pathlib import Path
+from types import ModuleType
+from typing import Optional
+
+_PKG_DIR = Path(__file__).resolve().parent.parent
+CSRC_DIR = _PKG_DIR / "csrc"
+BUILD_DIR = _PKG_DIR / "_build"
+EXT_NAME = "cmoe_sm100a"
+
+_SOURCES = [
+    "bindings.cpp",
+    "bindings_attention.cpp",
+    "bindings_ep.cpp",
+    "bindings_io.cpp",
+    "odirect_writer.cpp",
+    "gemm.cu",
+    "router.cu",
+    "ops.cu",
+    "attention.cu",
+    "ep.cu",
+    "noalloc.cu",
+]
+
+NVCC_FLAGS = [
+    "-gencode",
+    "arch=compute_100a,code=sm_100a",
+    "-lineinfo",
+    "-O3",
+    "-std=c++17",
+    "--expt-relaxed-constexpr",
+    "-Xptxas",
+    "-v",
+]
+
+_lock = threading.Lock()
+_module: Optional[ModuleType] = None
+
+
+def sources() -> list[Path]:
+    return [CSRC_DIR / s for s in _SOURCES if (CSRC_DIR / s).exists()]
+
+
+def _source_hash() -> str:
+    h = hashlib.sha256()
+    files = sorted(list(CSRC_DIR.glob("*.cu")) + list(CSRC_DIR.glob("*.cuh")) + list(CSRC_DIR.glob("*.cpp")) + list(CSRC_DIR.glob("*.h")))
+    for f in files:
+        h.update(f.name.encode())
+        h.update(f.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def _so_path() -> Path:
+    return BUILD_DIR / f"{EXT_NAME}.so"
+
+
+def _import_so(path: Path) -> ModuleType:
+    import torch  # noqa: F401  (libtorch must be loaded before the extension)
+
+    spec = importlib.util.spec_from_file_location(EXT_NAME, str(path))
+    if spec is None or spec.loader is None:
+        raise ImportError(f"cannot load extension from {path}")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    sys.modules[EXT_NAME] = mod
+    return mod
+
+
+def build(verbose: bool = False, force: bool = False) -> Path:
+    """Compile the extension for sm_100a if the stamp does not match the sources."""
+    stamp = BUILD_DIR / ".srchash"
+    want = _source_hash()
+    so = _so_path()
+    if not force and so.exists() and stamp.exists() and stamp.read_text().strip() == want:
+        return so
+    from torch.utils import cpp_extension
+
+    BUILD_DIR.mkdir(parents=True, exist_ok=True)
+    os.environ.setdefault("MAX_JOBS", str(min(8, os.cpu_count() or 4)))
+    cpp_extension.load(
+        name=EXT_NAME,
+        sources=[str(s) for s in sources()],
+        extra_cflags=["-O3", "-std=c++17"],
+        extra_cuda_cflags=NVCC_FLAGS,
+        extra_include_paths=[str(CSRC_DIR)],
+        build_directory=str(BUILD_DIR),
+        verbose=verbose,
+        is_python_module=False,
+    )
+    if not so.exists():
+        raise RuntimeError(f"extension build did not produce {so}")
+    stamp.write_text(want)
+    return so
+
+
+def ext() -> ModuleType:
+    """The loaded extension module (built on first use if needed)."""
+    global _module
+    if _module is not None:
+        return _module
+    with _lock:
+        if _module is None:
+            so = build()
+            _module = _import_so(so)
+    return _module
+
+
+def available() -> bool:
+    """True when the extension can be imported (it is built for sm_100a only)."""
+    try:
+        ext()
+        return True
+    except Exception:
+        return False
