@@ -1,5 +1,5 @@
 // pybind11 layer: torch tensors in, raw-pointer launchers of gemm.cu / router.cu / ops.cu / attention.cu /
-// ep.cu / odirect_writer.cpp out.  All launches go to the current CUDA stream of the calling thread.
+// ep.cu out.  All launches go to the current CUDA stream of the calling thread.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
@@ -292,7 +292,6 @@ void combine_bwd_w(const Tensor& rows, const Tensor& slot_row, const Tensor& dy,
 
 void register_attention(pybind11::module_& m);
 void register_ep(pybind11::module_& m);
-void register_io(pybind11::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "sm_100a kernels of the composed MoE engine";
@@ -312,5 +311,4 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("combine_bwd_w", &combine_bwd_w);
   register_attention(m);
   register_ep(m);
-  register_io(m);
 }

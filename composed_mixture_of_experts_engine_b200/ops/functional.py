@@ -1,0 +1,259 @@
+"""Differentiable ops of the model, each with one CUDA path (the sm_100a kernels) and one PyTorch path.
+
+The PyTorch path is what runs on CPU (gloo tests, the fp32 smoke config) and what the GPU numerics
+tests compare against; on a CUDA device with bf16 tensors the kernels are the only path.  Reference
+counterparts: RMSNorm (pkg/models/moe.py:63-86), the expert FFN and dispatch/combine of
+``DistributedMoELayer.forward`` (pkg/distributed/moe_layer.py:264-360), cross-entropy (train.py:297-303).
+RoPE and attention are additions (the reference model has neither).
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from . import _ext, kernels
+from .kernels import EPI_STORE, EPI_SWIGLU_BWD, EPI_SWIGLU_FWD, GEMM_GROUPED_K, GEMM_GROUPED_M, MoEPlan
+
+
+def on_device_path(*tensors: torch.Tensor) -> bool:
+    """True when the sm_100a kernels handle these tensors (CUDA + bf16)."""
+    return all(t.is_cuda and t.dtype == torch.bfloat16 for t in tensors)
+
+
+# ------------------------------------------------------------------------------------------ RMSNorm
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        xc = x.contiguous()
+        y = torch.empty_like(xc)
+        rstd = torch.empty(xc.numel() // xc.shape[-1], device=x.device, dtype=torch.float32)
+        _ext.ext().rmsnorm_fwd(xc, weight, y, rstd, eps)
+        ctx.save_for_backward(xc, weight, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight, rstd = ctx.saved_tensors
+        dx = torch.empty_like(x)
+        dw = torch.zeros(weight.shape, device=x.device, dtype=torch.float32)
+        _ext.ext().rmsnorm_bwd(dy.contiguous(), x, weight, rstd, dx, dw)
+        return dx, dw.to(weight.dtype), None
+
+
+def rmsnorm_reference(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * weight.float()).to(x.dtype)
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    if on_device_path(x, weight) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 8192:
+        return _RMSNormFn.apply(x, weight, eps)
+    return rmsnorm_reference(x, weight, eps)
+
+
+# ------------------------------------------------------------------------------------------ RoPE
+def rope_tables(seq_len: int, head_dim: int, theta: float, device: torch.device) -> Tuple[torch.Tensor, torch.Tensor]:
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
+    ang = torch.arange(seq_len, device=device, dtype=torch.float32)[:, None] * inv[None, :]
+    return ang.cos().contiguous(), ang.sin().contiguous()
+
+
+class _RopeFn(torch.autograd.Function):
+    """Rotates the first ``n_rot_heads`` heads of ``t`` [rows, heads, head_dim] in place."""
+
+    @staticmethod
+    def forward(ctx, t, cos, sin, seq, n_rot_heads):
+        view = t[:, :n_rot_heads]
+        _ext.ext().rope(view, cos, sin, seq, False)
+        ctx.save_for_backward(cos, sin)
+        ctx.seq, ctx.n_rot = seq, n_rot_heads
+        ctx.mark_dirty(t)
+        return t
+
+    @staticmethod
+    def backward(ctx, g):
+        cos, sin = ctx.saved_tensors
+        g = g.contiguous().clone()
+        _ext.ext().rope(g[:, : ctx.n_rot], cos, sin, ctx.seq, True)
+        return g, None, None, None, None
+
+
+def rope_reference(t: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seq: int, n_rot_heads: int) -> torch.Tensor:
+    rows, heads, hd = t.shape
+    pos = torch.arange(rows, device=t.device) % seq
+    c = cos[pos][:, None, :].to(torch.float32)
+    s = sin[pos][:, None, :].to(torch.float32)
+    rot = t[:, :n_rot_heads].float()
+    a, b = rot[..., : hd // 2], rot[..., hd // 2:]
+    out = torch.cat([a * c - b * s, b * c + a * s], dim=-1).to(t.dtype)
+    return torch.cat([out, t[:, n_rot_heads:]], dim=1)
+
+
+def rope(t: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seq: int, n_rot_heads: int) -> torch.Tensor:
+    """Rotary embedding on heads [0, n_rot_heads) of ``t`` [rows, heads, head_dim]; row r sits at position r % seq."""
+    if on_device_path(t) and t.shape[-1] % 16 == 0 and t.is_contiguous():
+        return _RopeFn.apply(t, cos, sin, seq, n_rot_heads)
+    return rope_reference(t, cos, sin, seq, n_rot_heads)
+
+
+# ------------------------------------------------------------------------------------------ attention
+def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """q [B,S,nh,hd], k/v [B,S,nkv,hd] -> [B,S,nh,hd], causal, grouped-query when nkv < nh."""
+    from . import attention as _attn
+
+    return _attn.causal_attention(q, k, v)
+
+
+# ------------------------------------------------------------------------------------------ cross-entropy
+class _CrossEntropyFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, targets, scale):
+        loss = torch.zeros(1, device=logits.device, dtype=torch.float32)
+        _ext.ext().cross_entropy(logits, targets, loss, scale)
+        ctx.save_for_backward(logits)  # now holds d(loss)/d(logits)
+        return loss[0] * scale
+
+    @staticmethod
+    def backward(ctx, g):
+        (grad,) = ctx.saved_tensors
+        return grad * g.to(grad.dtype), None, None
+
+
+def cross_entropy_sum_scaled(logits: torch.Tensor, targets: torch.Tensor, scale: float) -> torch.Tensor:
+    """``scale * sum_rows CE(logits, targets)``.  On the device path the logits buffer is consumed:
+    it is overwritten with the gradient, so the caller must not use it afterwards."""
+    if on_device_path(logits) and logits.dim() == 2 and logits.stride(1) == 1 and logits.stride(0) % 8 == 0:
+        return _CrossEntropyFn.apply(logits, targets, scale)
+    return F.cross_entropy(logits.float(), targets, reduction="sum", ignore_index=-100) * scale
+
+
+# ------------------------------------------------------------------------------------------ expert FFN
+def experts_reference(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor,
+                      expert_lo: int = 0, keep: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y_t = sum_k w[t,k] * Expert_{idx[t,k]}(x_t) for the experts [expert_lo, expert_lo + E_local) held in
+    ``w13`` [E_local, 2F, H] (gate rows then up rows) and ``w2`` [E_local, H, F].  Plain PyTorch, any dtype."""
+    N, H = x.shape
+    E_local, twoF, _ = w13.shape
+    Fdim = twoF // 2
+    y = torch.zeros(N, H, dtype=torch.float32, device=x.device)
+    for e in range(E_local):
+        mask = idx == (e + expert_lo)
+        if keep is not None:
+            mask = mask & keep
+        tok, slot = mask.nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        xe = x[tok]
+        g = xe @ w13[e, :Fdim].t()
+        u = xe @ w13[e, Fdim:].t()
+        out = (F.silu(g) * u) @ w2[e].t()
+        y.index_add_(0, tok, out.float() * w[tok, slot].float()[:, None])
+    return y.to(x.dtype)
+
+
+def _weight_grad(a: torch.Tensor, b: torch.Tensor, param: torch.Tensor, M: int, N: int, plan: MoEPlan):
+    """dW[e] = a[rows_e, :M]^T @ b[rows_e, :N]; accumulated into ``param.main_grad`` (fp32) when present."""
+    E = plan.n_local
+    main = getattr(param, "main_grad", None)
+    if main is not None:
+        kernels.gemm(a, b, main.view(E, M, N), mode=GEMM_GROUPED_K, M=M, N=N, a_mn=True, b_mn=True, groups=E,
+                     group_offsets=plan.group_offsets, d_group_stride=M * N, accumulate=True)
+        return None
+    out = torch.empty(E, M, N, device=a.device, dtype=torch.float32)
+    kernels.gemm(a, b, out, mode=GEMM_GROUPED_K, M=M, N=N, a_mn=True, b_mn=True, groups=E,
+                 group_offsets=plan.group_offsets, d_group_stride=M * N)
+    return out.to(param.dtype)
+
+
+def grouped_swiglu_forward(xp: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, plan: MoEPlan,
+                           ready: Optional[dict] = None):
+    """(hact, gu, yp) for expert-sorted rows ``xp`` [cap_rows, H]."""
+    E, twoF, H = w13.shape
+    Fdim = twoF // 2
+    dev = xp.device
+    hact = torch.empty(plan.cap_rows, Fdim, device=dev, dtype=torch.bfloat16)
+    gu = torch.empty(plan.cap_rows, twoF, device=dev, dtype=torch.bfloat16)
+    yp = torch.empty(plan.cap_rows, H, device=dev, dtype=torch.bfloat16)
+    kw = ready or {}
+    kernels.gemm(xp, w13.view(E * twoF, H), hact, mode=GEMM_GROUPED_M, epilogue=EPI_SWIGLU_FWD, N=Fdim, K=H, groups=E,
+                 b_group_rows=twoF, split_n=Fdim, tile_group=plan.tile_group, num_m_tiles=plan.num_m_tiles,
+                 max_m_tiles=plan.max_m_tiles, aux_out=gu, **kw)
+    kernels.gemm(hact, w2.view(E * H, Fdim), yp, mode=GEMM_GROUPED_M, N=H, K=Fdim, groups=E, b_group_rows=H,
+                 tile_group=plan.tile_group, num_m_tiles=plan.num_m_tiles, max_m_tiles=plan.max_m_tiles)
+    return hact, gu, yp
+
+
+def grouped_swiglu_backward(dyp: torch.Tensor, xp: torch.Tensor, hact: torch.Tensor, gu: torch.Tensor,
+                            w13: torch.Tensor, w2: torch.Tensor, plan: MoEPlan, need_dx: bool = True):
+    """(dxp, dW13, dW2) of the grouped SwiGLU FFN; weight gradients go to ``main_grad`` when the parameters have one."""
+    E, twoF, H = w13.shape
+    Fdim = twoF // 2
+    dgu = torch.empty_like(gu)
+    kernels.gemm(dyp, w2.view(E * H, Fdim), dgu, mode=GEMM_GROUPED_M, epilogue=EPI_SWIGLU_BWD, N=Fdim, K=H, b_mn=True,
+                 groups=E, b_group_rows=H, tile_group=plan.tile_group, num_m_tiles=plan.num_m_tiles,
+                 max_m_tiles=plan.max_m_tiles, aux_in=gu)
+    dxp = None
+    if need_dx:
+        dxp = torch.empty_like(xp)
+        kernels.gemm(dgu, w13.view(E * twoF, H), dxp, mode=GEMM_GROUPED_M, N=H, K=twoF, b_mn=True, groups=E,
+                     b_group_rows=twoF, tile_group=plan.tile_group, num_m_tiles=plan.num_m_tiles,
+                     max_m_tiles=plan.max_m_tiles)
+    dw2 = _weight_grad(dyp, hact, w2, H, Fdim, plan)
+    dw13 = _weight_grad(dgu, xp, w13, twoF, H, plan)
+    return dxp, dw13, dw2
+
+
+class _LocalMoEFn(torch.autograd.Function):
+    """Route-sorted expert FFN on one GPU: plan -> gather -> grouped SwiGLU GEMMs -> weighted combine."""
+
+    @staticmethod
+    def forward(ctx, x, gate_w32, idx32, w13, w2, capacity: int, holder: Optional[dict]):
+        E = w13.shape[0]
+        plan = kernels.moe_plan(idx32, E, capacity=capacity)
+        xp = kernels.gather_rows(x, plan)
+        hact, gu, yp = grouped_swiglu_forward(xp, w13, w2, plan)
+        y = kernels.combine_rows(yp, plan, gate_w32)
+        ctx.save_for_backward(xp, hact, gu, yp, gate_w32, w13, w2)
+        ctx.plan = plan
+        if holder is not None:
+            holder["plan"] = plan
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xp, hact, gu, yp, gate_w32, w13, w2 = ctx.saved_tensors
+        plan = ctx.plan
+        dy = dy.contiguous()
+        d_gate = kernels.combine_bwd_w(yp, plan, dy) if ctx.needs_input_grad[1] else None
+        dyp = kernels.gather_rows(dy, plan, slot_scale=gate_w32.reshape(-1))
+        dxp, dw13, dw2 = grouped_swiglu_backward(dyp, xp, hact, gu, w13, w2, plan, need_dx=ctx.needs_input_grad[0])
+        dx = kernels.combine_rows(dxp, plan, None) if dxp is not None else None
+        return dx, d_gate, None, dw13, dw2, None, None
+
+
+def local_moe(x: torch.Tensor, gate_w: torch.Tensor, idx: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor,
+              capacity: int = 0, holder: Optional[dict] = None) -> torch.Tensor:
+    """All experts on this rank.  ``x`` [N,H], ``gate_w`` [N,K] gate weights, ``idx`` [N,K] expert ids."""
+    if on_device_path(x, w13, w2):
+        return _LocalMoEFn.apply(x, gate_w.float().contiguous(), idx.to(torch.int32).contiguous(), w13, w2, capacity,
+                                 holder)
+    keep = None
+    if capacity > 0:
+        keep = ~capacity_drop_mask_reference(idx, w13.shape[0], capacity)
+    return experts_reference(x, idx, gate_w, w13, w2, 0, keep)
+
+
+def capacity_drop_mask_reference(idx: torch.Tensor, num_experts: int, capacity: int) -> torch.Tensor:
+    """True where slot (t, k) is the (capacity+1)-th or later token of its expert *within column k*
+    (first come first served in token order, each k column on its own; reference moe_layer.py:150-155)."""
+    N, K = idx.shape
+    drop = torch.zeros(N, K, dtype=torch.bool, device=idx.device)
+    for k in range(K):
+        onehot = F.one_hot(idx[:, k].long(), num_experts)
+        pos = (onehot.cumsum(0) - 1).gather(1, idx[:, k : k + 1].long()).squeeze(1)
+        drop[:, k] = pos >= capacity
+    return drop

@@ -1,0 +1,214 @@
+"""Thin, allocation-aware Python wrappers over the sm_100a extension entry points.
+
+Nothing here is differentiable; the autograd functions live in ``functional.py``.  Every wrapper
+launches on the current stream and returns at once.  Waits inside the kernels are bounded; a wait that
+ran out sets a status word that :func:`check_status` turns into :class:`KernelTimeoutError`.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import _ext
+
+GEMM_DENSE, GEMM_GROUPED_M, GEMM_GROUPED_K = 0, 1, 2
+EPI_STORE, EPI_SWIGLU_FWD, EPI_SWIGLU_BWD = 0, 1, 2
+
+STATUS_NAMES = {
+    0: "ok",
+    1: "timeout: shared-memory stage never filled (TMA)",
+    2: "timeout: shared-memory stage never released",
+    3: "timeout: accumulator never committed",
+    4: "timeout: accumulator never drained",
+    5: "timeout: peer flag never written",
+    6: "bad argument",
+}
+
+
+class KernelTimeoutError(RuntimeError):
+    """A bounded wait inside a kernel ran out; the CUDA context is still usable."""
+
+
+_status: Dict[int, torch.Tensor] = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """The per-device int32 status word that all launches of this package share."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _status.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status[idx] = t
+    return t
+
+
+def check_status(device: Optional[torch.device] = None, reset: bool = True) -> None:
+    """Synchronises with the device and raises if any kernel since the last check recorded an error."""
+    dev = device or torch.device("cuda", torch.cuda.current_device())
+    t = status_word(dev)
+    code = int(t.item())
+    if code != 0:
+        if reset:
+            t.zero_()
+        raise KernelTimeoutError(f"kernel status {code}: {STATUS_NAMES.get(code, 'unknown')}")
+
+
+def gemm(
+    A: torch.Tensor,
+    B: torch.Tensor,
+    D: torch.Tensor,
+    *,
+    mode: int = GEMM_DENSE,
+    epilogue: int = EPI_STORE,
+    M: int = 0,
+    N: int = 0,
+    K: int = 0,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    groups: int = 1,
+    b_group_rows: int = 0,
+    split_n: int = 0,
+    tile_group: Optional[torch.Tensor] = None,
+    num_m_tiles: Optional[torch.Tensor] = None,
+    max_m_tiles: int = 0,
+    group_offsets: Optional[torch.Tensor] = None,
+    d_group_stride: int = 0,
+    accumulate: bool = False,
+    aux_in: Optional[torch.Tensor] = None,
+    aux_out: Optional[torch.Tensor] = None,
+    ready_flags: Optional[torch.Tensor] = None,
+    ready_stride: int = 0,
+    ready_count: int = 0,
+    ready_target: int = 0,
+    timeout_ns: int = 0,
+) -> torch.Tensor:
+    _ext.ext().gemm(
+        A, B, D, mode, epilogue, M, N, K, a_mn, b_mn, groups, b_group_rows, split_n, tile_group, num_m_tiles,
+        max_m_tiles, group_offsets, d_group_stride, accumulate, aux_in, aux_out, ready_flags, ready_stride,
+        ready_count, ready_target, status_word(A.device), timeout_ns,
+    )
+    return D
+
+
+def linear_nt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False,
+              out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T (the nn.Linear contraction) on the tcgen05 GEMM."""
+    M, K = x.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty(M, N, device=x.device, dtype=out_dtype)
+    return gemm(x, w, out, M=M, N=N, K=K, accumulate=accumulate)
+
+
+def linear_nn(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False,
+              out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[K, N] (w read N-major, no transpose copy)."""
+    M, K = x.shape
+    N = w.shape[1]
+    if out is None:
+        out = torch.empty(M, N, device=x.device, dtype=out_dtype)
+    return gemm(x, w, out, M=M, N=N, K=K, b_mn=True, accumulate=accumulate)
+
+
+def linear_tn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False,
+              splits: int = 0) -> torch.Tensor:
+    """out[M, N] (fp32) = a[R, M]^T @ b[R, N]: the weight-gradient contraction over R rows.
+
+    The R rows are cut into ``splits`` chunks (multiples of 64 rows) that run as separate tiles and
+    are summed afterwards, so that small outputs still fill the GPU.
+    """
+    R, M = a.shape
+    N = b.shape[1]
+    if splits <= 0:
+        tiles = ((M + 127) // 128) * ((N + 255) // 256)
+        splits = max(1, min(R // 512 if R >= 512 else 1, (148 + tiles - 1) // tiles))
+    chunk = ((R + splits - 1) // splits + 63) // 64 * 64
+    offs = [min(i * chunk, R) for i in range(splits)] + [R]
+    offs_t = torch.tensor(offs, device=a.device, dtype=torch.int32)
+    part = torch.empty(splits, M, N, device=a.device, dtype=torch.float32)
+    gemm(a, b, part, mode=GEMM_GROUPED_K, M=M, N=N, a_mn=True, b_mn=True, groups=splits, group_offsets=offs_t,
+         d_group_stride=M * N)
+    red = part[0] if splits == 1 else part.sum(0)
+    if out is None:
+        return red
+    if accumulate:
+        out.add_(red.to(out.dtype))
+    else:
+        out.copy_(red)
+    return out
+
+
+class MoEPlan:
+    """Device-resident description of one expert-sorted, 128-row-padded row layout."""
+
+    __slots__ = ("n_tokens", "K", "n_local", "cap_rows", "slot_row", "row_slot", "group_offsets", "tile_group",
+                 "num_m_tiles", "counts_kept", "max_m_tiles")
+
+    def __init__(self, n_tokens: int, K: int, n_local: int, cap_rows: int, device: torch.device):
+        self.n_tokens, self.K, self.n_local, self.cap_rows = n_tokens, K, n_local, cap_rows
+        i32 = dict(device=device, dtype=torch.int32)
+        self.slot_row = torch.empty(n_tokens * K, **i32)
+        self.row_slot = torch.empty(cap_rows, **i32)
+        self.group_offsets = torch.empty(n_local + 1, **i32)
+        self.tile_group = torch.empty(cap_rows // 128, **i32)
+        self.num_m_tiles = torch.empty(1, **i32)
+        self.counts_kept = torch.empty(n_local, **i32)
+        self.max_m_tiles = cap_rows // 128
+
+
+def plan_capacity_rows(n_slots: int, n_local: int) -> int:
+    """Worst-case rows of the padded layout: every slot kept plus up to 127 padding rows per expert."""
+    return (n_slots + n_local * 127 + 127) // 128 * 128
+
+
+_scratch: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def _scratch_i32(device: torch.device, words: int) -> torch.Tensor:
+    key = (device.index or 0, 0)
+    t = _scratch.get(key)
+    if t is None or t.numel() < words:
+        t = torch.empty(max(words, 1 << 16), device=device, dtype=torch.int32)
+        _scratch[key] = t
+    return t
+
+
+def moe_plan(topk_idx: torch.Tensor, num_experts: int, expert_lo: int = 0, n_local: Optional[int] = None,
+             capacity: int = 0, cap_rows: Optional[int] = None) -> MoEPlan:
+    """Build the row plan for ``topk_idx`` [N, K] (int32).  ``capacity`` > 0 enables per-(expert, k) FCFS dropping."""
+    ext = _ext.ext()
+    N, K = topk_idx.shape
+    n_local = num_experts if n_local is None else n_local
+    if cap_rows is None:
+        cap_rows = plan_capacity_rows(N * K, n_local)
+    plan = MoEPlan(N, K, n_local, cap_rows, topk_idx.device)
+    per_k = capacity > 0
+    words = ext.moe_plan_scratch_words(N * K, n_local, K, per_k)
+    ext.moe_plan(topk_idx, K, num_experts, expert_lo, n_local, per_k, capacity, plan.slot_row, plan.row_slot,
+                 plan.group_offsets, plan.tile_group, plan.num_m_tiles, plan.counts_kept,
+                 _scratch_i32(topk_idx.device, words))
+    return plan
+
+
+def gather_rows(src: torch.Tensor, plan: MoEPlan, slot_scale: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if out is None:
+        out = torch.empty(plan.cap_rows, src.shape[1], device=src.device, dtype=torch.bfloat16)
+    _ext.ext().gather_rows(src, plan.row_slot, plan.K, slot_scale, out, plan.num_m_tiles)
+    return out
+
+
+def combine_rows(rows: torch.Tensor, plan: MoEPlan, w: Optional[torch.Tensor], out: Optional[torch.Tensor] = None
+                 ) -> torch.Tensor:
+    if out is None:
+        out = torch.empty(plan.n_tokens, rows.shape[1], device=rows.device, dtype=torch.bfloat16)
+    _ext.ext().combine_rows(rows, plan.slot_row, w, out, plan.K)
+    return out
+
+
+def combine_bwd_w(rows: torch.Tensor, plan: MoEPlan, dy: torch.Tensor) -> torch.Tensor:
+    dw = torch.empty(plan.n_tokens, plan.K, device=rows.device, dtype=torch.float32)
+    _ext.ext().combine_bwd_w(rows, plan.slot_row, dy, dw, plan.K)
+    return dw

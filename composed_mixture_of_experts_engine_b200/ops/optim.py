@@ -1,0 +1,230 @@
+"""Fused AdamW over flat parameter buffers, with global-norm clipping and optional optimizer-state sharding.
+
+The reference trains with ``torch.optim.AdamW(betas=(0.9, 0.95))`` + ``clip_grad_norm_`` on FSDP2-wrapped
+parameters (train.py:207-212, 322-323; pkg/distributed/data_parallel.py:40-98: bf16 compute parameters,
+fp32 reduction).  Here the same mixed-precision contract (bf16 parameters in the model, fp32 master copy and
+moments in the optimizer) is one kernel launch per parameter group:
+
+* parameters are re-pointed into one flat bf16 buffer per group, gradients into one flat buffer
+  (bf16 for autograd-produced gradients, fp32 ``main_grad`` for the expert weights whose gradients the grouped
+  GEMM kernels accumulate directly);
+* the global gradient norm is a device scalar (sum-of-squares kernel), so clipping needs no host round trip;
+* with data parallelism the flat gradient is reduce-scattered, the update runs on this rank's shard only, and
+  the updated bf16 parameters are all-gathered (ZeRO-style sharding of master weights and moments).  Expert
+  parameters are reduced over the ranks that hold the same experts only.
+
+``build_optimizer`` returns ``torch.optim.AdamW`` for CPU / fp32 models (the reference behaviour).
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Dict, Iterable, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from . import _ext
+
+
+def _align(n: int, a: int) -> int:
+    return (n + a - 1) // a * a
+
+
+class _FlatGroup:
+    """One flat bf16 parameter buffer + gradient buffer + (sharded) fp32 master / moments."""
+
+    def __init__(self, name: str, params: List[nn.Parameter], grad_dtype: torch.dtype, weight_decay_mask: List[bool],
+                 shard_group=None):
+        self.name, self.params = name, params
+        dev = params[0].device
+        self.shard_group = shard_group
+        self.shard_world = dist.get_world_size(shard_group) if shard_group is not None else 1
+        self.shard_rank = dist.get_rank(shard_group) if shard_group is not None else 0
+        offs, total = [], 0
+        for p in params:
+            offs.append(total)
+            total += _align(p.numel(), 8)
+        self.numel = _align(total, 8 * 16 * self.shard_world)
+        self.offsets = offs
+        self.flat_p = torch.zeros(self.numel, device=dev, dtype=torch.bfloat16)
+        self.flat_g = torch.zeros(self.numel, device=dev, dtype=grad_dtype)
+        self.decay = weight_decay_mask
+        for p, off in zip(params, offs):
+            n = p.numel()
+            self.flat_p[off:off + n].copy_(p.data.reshape(-1))
+            p.data = self.flat_p[off:off + n].view(p.shape)
+            gview = self.flat_g[off:off + n].view(p.shape)
+            if grad_dtype == torch.float32:
+                p.main_grad = gview
+                p.grad = None
+            else:
+                p.grad = gview
+        self.shard_numel = self.numel // self.shard_world
+        lo = self.shard_rank * self.shard_numel
+        self.shard_lo = lo
+        self.master = self.flat_p[lo:lo + self.shard_numel].float()
+        self.m = torch.zeros_like(self.master)
+        self.v = torch.zeros_like(self.master)
+        # per-element decay is applied per segment: split the shard into decay / no-decay runs
+        self._segments = self._build_segments()
+        self.g_shard_f32: Optional[torch.Tensor] = None
+
+    def _build_segments(self) -> List[Tuple[int, int, bool]]:
+        """(start, end, decay) runs inside this rank's shard, in shard-local coordinates."""
+        segs: List[Tuple[int, int, bool]] = []
+        lo, hi = self.shard_lo, self.shard_lo + self.shard_numel
+        bounds = self.offsets + [self.numel]
+        for i, d in enumerate(self.decay):
+            a, b = max(bounds[i], lo), min(bounds[i + 1], hi)
+            if a >= b:
+                continue
+            if segs and segs[-1][2] == d and segs[-1][1] == a - lo:
+                segs[-1] = (segs[-1][0], b - lo, d)
+            else:
+                segs.append((a - lo, b - lo, d))
+        return segs
+
+    def reassign_grads(self) -> None:
+        """Point ``p.grad`` back into the flat buffer (something set it to None or to a fresh tensor)."""
+        if self.flat_g.dtype == torch.float32:
+            return
+        for p, off in zip(self.params, self.offsets):
+            view = self.flat_g[off:off + p.numel()].view(p.shape)
+            if p.grad is None:
+                p.grad = view
+            elif p.grad.data_ptr() != view.data_ptr():
+                view.add_(p.grad.to(view.dtype))
+                p.grad = view
+
+
+class FusedAdamW:
+    """AdamW (decoupled decay) on flat buffers; one ``adamw`` kernel launch per decay run of each group."""
+
+    def __init__(self, groups: List[_FlatGroup], lr: float, betas=(0.9, 0.95), eps: float = 1e-8,
+                 weight_decay: float = 0.1, max_grad_norm: float = 0.0, norm_groups: Iterable = ()):
+        self.groups = groups
+        self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
+        self.max_grad_norm = max_grad_norm
+        self.step_count = 0
+        dev = groups[0].flat_p.device
+        self.sumsq = torch.zeros(1, device=dev, dtype=torch.float32)
+        self.last_grad_norm_sq: Optional[torch.Tensor] = None
+        self._norm_groups = list(norm_groups)  # process groups over which the squared norm is summed
+        self.param_groups = [{"lr": lr, "params": [p for g in groups for p in g.params]}]
+
+    # -- torch.optim-like surface ----------------------------------------------------------------
+    def zero_grad(self, set_to_none: bool = False) -> None:
+        for g in self.groups:
+            g.flat_g.zero_()
+
+    def state_dict(self) -> Dict:
+        return {
+            "step": self.step_count,
+            "groups": {g.name: {"master": g.master, "m": g.m, "v": g.v, "shard_rank": g.shard_rank,
+                                "shard_world": g.shard_world} for g in self.groups},
+            "param_groups": [{"lr": self.lr, "betas": self.betas, "eps": self.eps,
+                              "weight_decay": self.weight_decay}],
+            "state": {},
+        }
+
+    def load_state_dict(self, sd: Dict) -> None:
+        self.step_count = int(sd.get("step", 0))
+        for g in self.groups:
+            src = sd["groups"].get(g.name)
+            if src is None:
+                continue
+            for name in ("master", "m", "v"):
+                getattr(g, name).copy_(src[name].to(getattr(g, name).device))
+            self._publish_params(g)
+
+    # -- step ------------------------------------------------------------------------------------
+    def _reduce_grads(self, g: _FlatGroup) -> torch.Tensor:
+        """Returns this rank's gradient shard (averaged over the shard group)."""
+        if g.shard_world == 1:
+            return g.flat_g
+        from ..parallel import symm_dp
+
+        return symm_dp.reduce_scatter_grads(g)
+
+    def _publish_params(self, g: _FlatGroup) -> None:
+        """After an update of the shard: make every rank's flat bf16 parameter buffer whole again."""
+        if g.shard_world == 1:
+            return
+        from ..parallel import symm_dp
+
+        symm_dp.all_gather_params(g)
+
+    @torch.no_grad()
+    def step(self, lr: Optional[float] = None) -> None:
+        ext = _ext.ext()
+        if lr is not None:
+            self.lr = lr
+            self.param_groups[0]["lr"] = lr
+        self.step_count += 1
+        shards = []
+        self.sumsq.zero_()
+        for g in self.groups:
+            g.reassign_grads()
+            gs = self._reduce_grads(g)
+            shards.append(gs)
+            if self.max_grad_norm > 0:
+                ext.sumsq(gs, self.sumsq)
+        if self.max_grad_norm > 0:
+            for pg in self._norm_groups:
+                if pg is not None:
+                    dist.all_reduce(self.sumsq, group=pg)
+        self.last_grad_norm_sq = self.sumsq.clone() if self.max_grad_norm > 0 else None
+        b1, b2 = self.betas
+        for g, gs in zip(self.groups, shards):
+            sharded = g.shard_world > 1
+            p16_base = g.flat_p[g.shard_lo:g.shard_lo + g.shard_numel]
+            for a, b, decay in g._segments:
+                ext.adamw(g.master[a:b], p16_base[a:b], g.m[a:b], g.v[a:b], gs[a:b], self.lr, b1, b2, self.eps,
+                          self.weight_decay if decay else 0.0, self.step_count, 1.0, self.max_grad_norm,
+                          self.sumsq if self.max_grad_norm > 0 else None, not sharded)
+            if sharded:
+                g.flat_g.zero_()
+                self._publish_params(g)
+
+    def grad_norm(self) -> float:
+        """Global gradient norm of the last step (one device read)."""
+        return float(self.last_grad_norm_sq.sqrt()) if self.last_grad_norm_sq is not None else 0.0
+
+
+def _no_decay(name: str, p: nn.Parameter) -> bool:
+    return p.dim() <= 1 or name.endswith(".bias") or "norm" in name.lower()
+
+
+def build_optimizer(model: nn.Module, lr: float, weight_decay: float = 0.1, betas=(0.9, 0.95), eps: float = 1e-8,
+                    max_grad_norm: float = 0.0, topology=None):
+    """FusedAdamW for CUDA bf16 models, ``torch.optim.AdamW`` otherwise."""
+    params = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+    on_device = all(p.is_cuda and p.dtype == torch.bfloat16 for _, p in params)
+    if not on_device:
+        decay = [p for n, p in params if not _no_decay(n, p)]
+        no_decay = [p for n, p in params if _no_decay(n, p)]
+        return torch.optim.AdamW(
+            [{"params": decay, "weight_decay": weight_decay}, {"params": no_decay, "weight_decay": 0.0}],
+            lr=lr, betas=betas, eps=eps)
+
+    from ..parallel.mesh import dp_process_group, edp_process_group
+
+    expert = [(n, p) for n, p in params if getattr(p, "is_expert_param", False)]
+    dense = [(n, p) for n, p in params if not getattr(p, "is_expert_param", False)]
+    dp_group = expert_dp_group = None
+    if topology is not None and dist.is_initialized() and topology.dp_size > 1:
+        dp_group = dp_process_group(topology)
+        expert_dp_group = edp_process_group(topology)
+    groups: List[_FlatGroup] = []
+    if dense:
+        groups.append(_FlatGroup("dense", [p for _, p in dense], torch.bfloat16,
+                                 [not _no_decay(n, p) for n, p in dense], shard_group=dp_group))
+    if expert:
+        groups.append(_FlatGroup("expert", [p for _, p in expert], torch.float32, [True] * len(expert),
+                                 shard_group=expert_dp_group))
+    norm_groups = []
+    if topology is not None and dist.is_initialized() and topology.world_size > 1:
+        norm_groups = [dist.group.WORLD]
+    return FusedAdamW(groups, lr, betas, eps, weight_decay, max_grad_norm, norm_groups)

@@ -62,6 +62,7 @@ class ModelConfig(BaseModel):
     rope_theta: float = Field(10000.0)
     aux_loss_coeff: float = Field(0.0, description="Weight of the load-balance loss E * sum_i f_i P_i.")
     norm_eps: float = Field(1e-5)
+    init_std: float = Field(0.0, description="Std of the normal init of all matrices (0: each module's default).")
 
     @model_validator(mode="after")
     def _check(self) -> "ModelConfig":
