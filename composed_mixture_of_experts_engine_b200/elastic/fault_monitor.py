@@ -686,7 +686,7 @@ class ElasticTrainerHarness:
         base = old_model(min(rep))
         with torch.no_grad():
             for name, dst in sd.items():
-                if name.endswith(".w13") or name.endswith(".w2"):
+                if name.rsplit(".", 1)[-1] in ("w13", "w2"):
                     for j, e in enumerate(mine):
                         owner = next(r for r in range(old_ep) if e in old_probe.experts_on_rank(num_experts, r))
                         local = old_probe.experts_on_rank(num_experts, owner).index(e)

@@ -58,7 +58,11 @@ def build_model_from_config(cfg, topology, arch: Optional[str] = None) -> nn.Mod
         arch = getattr(cfg.model, "arch", "toy_moe")
     cls = ModelRegistry.get(arch)
     log.info("Building model '%s' (%s) on %s", arch, cls.__qualname__, topology.device)
-    return cls(cfg, topology).to(topology.device)
+    import torch
+
+    with torch.device(topology.device):  # parameters are created (and initialised) on the target device
+        model = cls(cfg, topology)
+    return model.to(topology.device)
 
 
 def list_registered_models() -> "list[str]":

@@ -1,0 +1,194 @@
+"""Worker functions for the multi-process (gloo, CPU) tests.  Each takes (rank, world, port, queue, *args)."""
+
+from __future__ import annotations
+
+import os
+import sys
+import traceback
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+
+def _init(rank: int, world: int, port: int):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      GLOO_SOCKET_IFNAME="lo")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+
+
+def run(fn_name: str, rank: int, world: int, port: int, queue, args):
+    import torch
+    import torch.distributed as dist
+
+    torch.set_num_threads(1)
+    try:
+        _init(rank, world, port)
+        out = globals()[fn_name](rank, world, *args)
+        queue.put((rank, "ok", out))
+    except Exception:
+        queue.put((rank, "error", traceback.format_exc()))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------------------------------
+def ep_layer(rank, world, capacity_dropping):
+    """Expert-parallel layer on `world` ranks: output and gradients vs the single-rank layer holding all experts."""
+    import torch
+
+    from composed_mixture_of_experts_engine_b200.parallel import DistributedMoELayer, build_topology
+
+    H, F, E, K, N = 16, 32, 8, 2, 24
+    topo = build_topology(1, world, device_type="cpu")
+    torch.manual_seed(0)
+    full = DistributedMoELayer(H, F, E, K, capacity_factor=0.25, capacity_dropping=capacity_dropping)
+    layer = DistributedMoELayer(H, F, E, K, topology=topo, capacity_factor=0.25, capacity_dropping=capacity_dropping)
+    mine = topo.experts_on_this_rank(E)
+    with torch.no_grad():
+        layer.router.gate_w.copy_(full.router.gate_w)
+        layer.w13.copy_(full.w13[mine[0]:mine[-1] + 1])
+        layer.w2.copy_(full.w2[mine[0]:mine[-1] + 1])
+    torch.manual_seed(100 + rank)  # every rank routes its own tokens
+    x = torch.randn(N, H, requires_grad=True)
+    y = layer(x)
+    y.pow(2).sum().backward()
+    x2 = x.detach().clone().requires_grad_(True)
+    y2 = full(x2)
+    y2.pow(2).sum().backward()
+    # expert-weight gradients: the sharded layer sees the tokens of ALL ranks; sum the oracle over ranks
+    import torch.distributed as dist
+
+    g13 = full.w13.grad.clone()
+    dist.all_reduce(g13)
+    return {
+        "y": float((y - y2).abs().max()),
+        "dx": float((x.grad - x2.grad).abs().max()),
+        "dw13": float((layer.w13.grad - g13[mine[0]:mine[-1] + 1]).abs().max()),
+        "dgate": float((layer.router.gate_w.grad - full.router.gate_w.grad).abs().max()),
+        "dropped": layer.last_dropped_token_fraction,
+    }
+
+
+def tp_linears(rank, world):
+    """Column -> SiLU -> Row over tp=world vs the unsharded computation, forward and backward."""
+    import torch
+    import torch.nn.functional as F
+
+    from composed_mixture_of_experts_engine_b200.parallel import (ColumnParallelLinear, RowParallelLinear,
+                                                                  build_topology)
+
+    topo = build_topology(1, 1, tp_size=world, device_type="cpu")
+    torch.manual_seed(0)
+    Wc, Wr = torch.randn(32, 16), torch.randn(16, 32)
+    col = ColumnParallelLinear(16, 32, bias=False, topology=topo, gather_output=False)
+    row = RowParallelLinear(32, 16, bias=False, topology=topo)
+    sh = 32 // world
+    with torch.no_grad():
+        col.weight.copy_(Wc[rank * sh:(rank + 1) * sh])
+        row.weight.copy_(Wr[:, rank * sh:(rank + 1) * sh])
+    x = torch.randn(3, 5, 16, requires_grad=True)
+    y = row(F.silu(col(x)))
+    y.sum().backward()
+    x2 = x.detach().clone().requires_grad_(True)
+    y2 = F.linear(F.silu(F.linear(x2, Wc)), Wr)
+    y2.sum().backward()
+    gathered = ColumnParallelLinear(16, 32, bias=True, topology=topo, gather_output=True)
+    with torch.no_grad():
+        gathered.weight.copy_(Wc[rank * sh:(rank + 1) * sh])
+    full_out = gathered(x.detach())
+    return {"y": float((y - y2).abs().max()), "dx": float((x.grad - x2.grad).abs().max()),
+            "gather": float((full_out - F.linear(x.detach(), Wc)).abs().max()),
+            "row_full_input": float((row(F.silu(F.linear(x.detach(), Wc))) - y2.detach()).abs().max())}
+
+
+def sp_linears(rank, world):
+    """Sequence-parallel column/row pair: all-gather -> GEMM and GEMM -> reduce-scatter vs unsharded."""
+    import torch
+    import torch.nn.functional as F
+
+    from composed_mixture_of_experts_engine_b200.parallel import (ColumnParallelLinear, RowParallelLinear,
+                                                                  build_topology, gather_from_sequence_parallel,
+                                                                  scatter_to_sequence_parallel)
+
+    topo = build_topology(1, 1, tp_size=world, device_type="cpu")
+    torch.manual_seed(0)
+    Wc, Wr = torch.randn(32, 16), torch.randn(16, 32)
+    x_full = torch.randn(2, 8, 16)
+    col = ColumnParallelLinear(16, 32, bias=False, topology=topo, gather_output=False, sequence_parallel=True)
+    row = RowParallelLinear(32, 16, bias=False, topology=topo, sequence_parallel=True)
+    sh = 32 // world
+    with torch.no_grad():
+        col.weight.copy_(Wc[rank * sh:(rank + 1) * sh])
+        row.weight.copy_(Wr[:, rank * sh:(rank + 1) * sh])
+    x = x_full.clone().requires_grad_(True)
+    xs = scatter_to_sequence_parallel(x, topo)
+    ys = row(F.silu(col(xs)))
+    y = gather_from_sequence_parallel(ys, topo)
+    y.sum().backward()
+    x2 = x_full.clone().requires_grad_(True)
+    y2 = F.linear(F.silu(F.linear(x2, Wc)), Wr)
+    y2.sum().backward()
+    fused = scatter_to_sequence_parallel(x_full, topo, next_weight=Wc)
+    S = 8 // world
+    return {"shape": list(xs.shape), "y": float((y - y2).abs().max()), "dx": float((x.grad - x2.grad).abs().max()),
+            "fused": float((fused - F.linear(x_full[:, rank * S:(rank + 1) * S], Wc)).abs().max())}
+
+
+def pp_1f1b(rank, world, m):
+    """`world` pipeline stages, each y = W_s x: outputs and the input/weight gradients vs the chained computation."""
+    import torch
+    import torch.nn as nn
+
+    from composed_mixture_of_experts_engine_b200.parallel import PipelineStage, build_topology
+
+    topo = build_topology(1, 1, pp_size=world, device_type="cpu")
+    torch.manual_seed(0)
+    Ws = [torch.randn(6, 6) / 2 for _ in range(world)]
+    mod = nn.Linear(6, 6, bias=False)
+    with torch.no_grad():
+        mod.weight.copy_(Ws[rank])
+    stage = PipelineStage(rank, world, mod, topo)
+    mbs = [torch.randn(3, 6) for _ in range(m)]  # same seed on every rank
+    outs, losses = stage.run_1f1b_distributed(mbs if rank == 0 else [], loss_fn=lambda o: o.pow(2).sum(),
+                                              num_microbatches=m, activation_shape=(3, 6),
+                                              activation_dtype=torch.float32, device=torch.device("cpu"))
+    ref_w = [w.clone().requires_grad_(True) for w in Ws]
+    total = 0
+    ref_outs = []
+    for x in mbs:
+        h = x
+        for w in ref_w:
+            h = h @ w.t()
+        ref_outs.append(h)
+        total = total + h.pow(2).sum()
+    total.backward()
+    res = {"dw": float((mod.weight.grad - ref_w[rank].grad).abs().max()), "n_out": len(outs), "n_loss": len(losses)}
+    if rank == world - 1:
+        res["out"] = max(float((a - b).abs().max()) for a, b in zip(outs, ref_outs))
+    return res
+
+
+def trainer_steps(rank, world, config_path, steps):
+    """The public Trainer on `world` gloo ranks (dp = ep = world, ep carved from dp)."""
+    import torch
+
+    from composed_mixture_of_experts_engine_b200.engine import Trainer
+    from composed_mixture_of_experts_engine_b200.utils.config import MoEConfig
+
+    cfg = MoEConfig.from_yaml(config_path)
+    tr = Trainer(cfg, device_type="cpu")
+    gen = torch.Generator().manual_seed(rank)
+    ids, tgt = tr.synthetic_batch(gen, pinned=False)
+    losses = [float(tr.train_step(ids, tgt)) for _ in range(steps)]
+    gate = tr.model.blocks[0].moe.router.gate_w.detach().clone()
+    import torch.distributed as dist
+
+    ref = gate.clone()
+    dist.broadcast(ref, src=0)
+    return {"losses": losses, "gate_sync": float((gate - ref).abs().max()), "ep": tr.topology.ep_size,
+            "local_experts": tr.model.blocks[0].moe.local_expert_ids}

@@ -1,0 +1,107 @@
+"""Config tree: YAML files load, validators fire, env overrides coerce, YAML round trip, legacy shim.
+Mirrors the coverage of the reference's tests/test_config.py."""
+
+import os
+import warnings
+from pathlib import Path
+
+import pytest
+
+from composed_mixture_of_experts_engine_b200.utils.config import (ConfigValidationError, MoEConfig,
+                                                                  _apply_env_overrides, _coerce_env_value,
+                                                                  load_config)
+
+pytestmark = pytest.mark.cpu
+CONFIGS = Path(__file__).resolve().parent.parent / "configs"
+
+
+@pytest.mark.parametrize("name", ["default", "smoke", "large_scale", "olmoe_1b7b", "mixtral_8x7b", "cpu_smoke_ep2",
+                                  "smoke_gpu"])
+def test_shipped_yaml_loads(name):
+    cfg = MoEConfig.from_yaml(CONFIGS / f"{name}.yaml")
+    assert cfg.model.top_k <= cfg.model.num_experts
+    assert cfg.parallelism.world_size >= 1
+
+
+def test_reference_default_values():
+    cfg = MoEConfig.from_yaml(CONFIGS / "default.yaml")
+    assert (cfg.model.hidden_dim, cfg.model.num_layers, cfg.model.num_experts, cfg.model.top_k) == (4096, 32, 64, 2)
+    assert cfg.model.ffn_dim == 14336 and cfg.model.vocab_size == 128256 and cfg.model.dtype == "bfloat16"
+    assert cfg.parallelism.world_size == 64
+    assert cfg.model.arch == "toy_moe"  # the reference architecture stays the default
+
+
+def test_defaults_without_file():
+    cfg = MoEConfig()
+    assert cfg.training.warmup_steps == 2000 and cfg.checkpoint.retention == 8
+
+
+@pytest.mark.parametrize("section,field,value,needle", [
+    ("model", "top_k", 128, "top_k"),
+    ("model", "hidden_dim", 30, "divisible by 8"),
+    ("model", "dtype", "int8", "dtype"),
+    ("training", "warmup_steps", 10**9, "warmup_steps"),
+    ("checkpoint", "remote_uri", "http://x", "remote_uri"),
+    ("elastic", "min_nodes", 10**6, "min_nodes"),
+])
+def test_validators(section, field, value, needle):
+    with pytest.raises(ConfigValidationError) as ei:
+        MoEConfig.from_dict({section: {field: value}})
+    assert needle in str(ei.value)
+
+
+def test_missing_file_and_bad_yaml(tmp_path):
+    with pytest.raises(FileNotFoundError):
+        MoEConfig.from_yaml(tmp_path / "nope.yaml")
+    p = tmp_path / "list.yaml"
+    p.write_text("- a\n- b\n")
+    with pytest.raises(ConfigValidationError):
+        MoEConfig.from_yaml(p)
+
+
+def test_env_overrides(monkeypatch):
+    monkeypatch.setenv("MOE_TRAINING__LEARNING_RATE", "1e-5")
+    monkeypatch.setenv("MOE_MODEL__HIDDEN_DIM", "1024")
+    monkeypatch.setenv("MOE_MODEL__CAPACITY_DROPPING", "true")
+    monkeypatch.setenv("MOE_NOSUCH__FIELD", "1")
+    cfg = MoEConfig.from_dict({"model": {}, "training": {}})
+    assert cfg.training.learning_rate == pytest.approx(1e-5) and isinstance(cfg.training.learning_rate, float)
+    assert cfg.model.hidden_dim == 1024 and cfg.model.capacity_dropping is True
+
+
+def test_coerce():
+    assert _coerce_env_value("16") == 16 and _coerce_env_value("1e-5") == 1e-5
+    assert _coerce_env_value("false") is False and _coerce_env_value("null") is None
+    assert _coerce_env_value("bfloat16") == "bfloat16"
+    out = _apply_env_overrides({"model": {"top_k": 2}}, {"MOE_MODEL__TOP_K": "4", "OTHER": "x"})
+    assert out["model"]["top_k"] == 4
+
+
+def test_yaml_round_trip(tmp_path):
+    cfg = MoEConfig.from_yaml(CONFIGS / "olmoe_1b7b.yaml")
+    cfg.to_yaml(tmp_path / "out.yaml")
+    assert MoEConfig.from_yaml(tmp_path / "out.yaml").to_dict() == cfg.to_dict()
+
+
+def test_legacy_shim_and_raw_warning():
+    legacy = load_config(CONFIGS / "smoke.yaml")
+    assert legacy.model["hidden_dim"] == 32 and legacy.raw["training"]["max_steps"] == 2
+    typed = legacy.typed()
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        _ = typed.raw
+    assert any(issubclass(x.category, DeprecationWarning) for x in w)
+
+
+def test_ep_from_dp_world_size():
+    cfg = MoEConfig.from_dict({"parallelism": dict(data_parallel=8, expert_parallel=8, ep_from_dp=True)})
+    assert cfg.parallelism.world_size == 8
+    with pytest.raises(ConfigValidationError):
+        MoEConfig.from_dict({"parallelism": dict(data_parallel=6, expert_parallel=4, ep_from_dp=True)})
+
+
+def test_gqa_validation():
+    cfg = MoEConfig.from_dict({"model": dict(hidden_dim=4096, num_heads=32, num_kv_heads=8)})
+    assert cfg.model.resolved_head_dim == 128 and cfg.model.resolved_num_kv_heads == 8
+    with pytest.raises(ConfigValidationError):
+        MoEConfig.from_dict({"model": dict(hidden_dim=4096, num_heads=32, num_kv_heads=5)})

@@ -1,0 +1,251 @@
+"""Pipeline scheduling in one process, object stores, asynchronous checkpointer, state machine, harness
+(reference: tests/test_pipeline_parallel.py, test_elastic.py, test_elastic_v02.py)."""
+
+import json
+import os
+import threading
+import time
+
+import pytest
+import torch
+import torch.nn as nn
+
+from composed_mixture_of_experts_engine_b200.elastic import (CHECKPOINT_SCHEMA_VERSION, AsyncCheckpointer,
+                                                             ClusterStateMachine, ElasticConfig,
+                                                             ElasticTrainerHarness, LocalNVMeAdapter,
+                                                             _check_schema_compatibility, _largest_divisor_le)
+from composed_mixture_of_experts_engine_b200.parallel import ParallelTopology, PipelineStage, partition_layers
+
+pytestmark = pytest.mark.cpu
+
+
+# ---------------------------------------------------------------- pipeline
+@pytest.mark.parametrize("p,m", [(1, 1), (2, 4), (4, 2), (4, 8), (3, 0)])
+def test_run_1f1b_returns_one_grad_per_microbatch(p, m):
+    stage = PipelineStage(0, p, module=nn.Linear(4, 4))
+    mbs = [torch.randn(2, 4) for _ in range(m)]
+    grads = stage.run_1f1b(mbs)
+    assert len(grads) == m and all(g is not None and g.shape == (2, 4) for g in grads)
+
+
+def test_stage_position_and_errors():
+    s = PipelineStage(1, 3)
+    assert not s.is_first and not s.is_last and PipelineStage(0, 3).is_first and PipelineStage(2, 3).is_last
+    x = torch.randn(2, 2)
+    assert torch.equal(s.forward_step(x), x) and torch.equal(s.backward_step(x), x)
+    with pytest.raises(ValueError):
+        PipelineStage(3, 3)
+    with pytest.raises(RuntimeError):
+        s.run_1f1b_distributed([x])
+
+
+def test_partition_layers():
+    assert [list(r) for r in partition_layers(10, 4)] == [[0, 1, 2], [3, 4, 5], [6, 7], [8, 9]]
+    assert sum(len(r) for r in partition_layers(32, 2)) == 32
+
+
+# ---------------------------------------------------------------- object store
+def test_local_adapter_round_trip_and_atomicity(tmp_path):
+    st = LocalNVMeAdapter(str(tmp_path / "store"))
+    st.put("ckpts/step=000001/rank=000000.pt", b"hello")
+    st.put("ckpts/step=000001/rank=000000.meta.json", b"{}")
+    assert st.get("ckpts/step=000001/rank=000000.pt") == b"hello"
+    assert st.list("ckpts/") == ["ckpts/step=000001/rank=000000.meta.json", "ckpts/step=000001/rank=000000.pt"]
+    assert st.list("nothing/") == []
+    st.delete("ckpts/step=000001/rank=000000.pt")
+    st.delete("ckpts/step=000001/rank=000000.pt")  # idempotent
+    with pytest.raises(FileNotFoundError):
+        st.get("ckpts/step=000001/rank=000000.pt")
+    assert not list((tmp_path / "store").rglob("*.tmp"))
+
+
+def test_local_adapter_large_unaligned_payload(tmp_path):
+    st = LocalNVMeAdapter(str(tmp_path), chunk_bytes=1 << 20)
+    payload = os.urandom(5 * (1 << 20) + 1234)  # several chunks and an unaligned tail
+    st.put("big.bin", payload)
+    assert st.get("big.bin") == payload
+    st.put("empty.bin", b"")
+    assert st.get("empty.bin") == b""
+
+
+# ---------------------------------------------------------------- checkpointer
+def _model_and_opt():
+    torch.manual_seed(0)
+    m = nn.Sequential(nn.Linear(8, 8), nn.Linear(8, 4))
+    opt = torch.optim.AdamW(m.parameters(), lr=1e-2)
+    m(torch.randn(3, 8)).sum().backward()
+    opt.step()
+    return m, opt
+
+
+def test_save_load_bit_exact_and_meta(tmp_path):
+    m, opt = _model_and_opt()
+    ck = AsyncCheckpointer(LocalNVMeAdapter(str(tmp_path / "l")), LocalNVMeAdapter(str(tmp_path / "r")), workers=2)
+    ck.save(m, opt, 7, rank=3, extra_meta={"dp_size": 2})
+    ck.shutdown()
+    assert ck.last_commit_ms >= 0 and ck.latest_step() == 7
+    for tier in ("l", "r"):
+        assert (tmp_path / tier / "ckpts" / "step=000007" / "rank=000003.pt").exists()
+        meta = json.loads((tmp_path / tier / "ckpts" / "step=000007" / "rank=000003.meta.json").read_text())
+        assert {"schema_version", "step", "rank", "hostname", "ts", "moe_engine_version", "torch_version",
+                "dp_size"} <= set(meta)
+        assert meta["schema_version"] == CHECKPOINT_SCHEMA_VERSION == 2
+    m2, opt2 = _model_and_opt()
+    with torch.no_grad():
+        for p in m2.parameters():
+            p.add_(1.0)
+    ck2 = AsyncCheckpointer(LocalNVMeAdapter(str(tmp_path / "l")), None, workers=1)
+    meta = ck2.load(m2, opt2, 7, rank=3)
+    ck2.shutdown()
+    assert meta["step"] == 7
+    for a, b in zip(m.parameters(), m2.parameters()):
+        assert torch.equal(a, b)
+    s1, s2 = opt.state_dict()["state"], opt2.state_dict()["state"]
+    assert all(torch.equal(s1[k]["exp_avg"], s2[k]["exp_avg"]) for k in s1)
+    obj = torch.load(tmp_path / "l" / "ckpts" / "step=000007" / "rank=000003.pt", weights_only=False)
+    assert set(obj) == {"model", "optim"} and {"state", "param_groups"} <= set(obj["optim"])
+
+
+def test_retention_and_remote_fallback(tmp_path):
+    m, opt = _model_and_opt()
+    local, remote = LocalNVMeAdapter(str(tmp_path / "l")), LocalNVMeAdapter(str(tmp_path / "r"))
+    ck = AsyncCheckpointer(local, remote, retention=2, workers=1)
+    for s in range(1, 6):
+        ck.save(m, opt, s)
+    ck.shutdown()
+    steps = {int(k.split("step=")[1][:6]) for k in local.list("ckpts/")}
+    assert steps == {4, 5} and ck.latest_step() == 5
+    # wipe the local tier: load falls back to the remote tier and re-hydrates the local one
+    for k in local.list("ckpts/"):
+        local.delete(k)
+    m2, _ = _model_and_opt()
+    ck2 = AsyncCheckpointer(local, remote, workers=1)
+    ck2.load(m2, None, 5)
+    ck2.shutdown()
+    assert "ckpts/step=000005/rank=000000.pt" in local.list("ckpts/")
+
+
+def test_save_does_not_wait_for_slow_storage(tmp_path):
+    class Slow(LocalNVMeAdapter):
+        def put(self, key, payload):
+            time.sleep(0.3)
+            super().put(key, payload)
+
+    m, opt = _model_and_opt()
+    ck = AsyncCheckpointer(Slow(str(tmp_path)), None, workers=1)
+    t0 = time.perf_counter()
+    ck.save(m, opt, 1)
+    assert time.perf_counter() - t0 < 0.25  # enqueue only
+    ck.shutdown(drain=True)
+    assert ck.latest_step() == 1
+
+
+def test_worker_survives_a_failing_store(tmp_path):
+    class Flaky(LocalNVMeAdapter):
+        n = 0
+
+        def put(self, key, payload):
+            Flaky.n += 1
+            if Flaky.n == 1:
+                raise OSError("injected storage failure")
+            super().put(key, payload)
+
+    m, opt = _model_and_opt()
+    ck = AsyncCheckpointer(Flaky(str(tmp_path)), None, workers=1)
+    ck.save(m, opt, 1)
+    ck.save(m, opt, 2)
+    ck.shutdown()
+    assert isinstance(ck.last_error, OSError) and ck.latest_step() == 2
+
+
+# ---------------------------------------------------------------- state machine / harness
+def test_state_machine_phases_and_reshard():
+    topo = ParallelTopology(world_size=8, rank=0, dp_size=1, ep_size=8)
+    sm = ClusterStateMachine(topo)
+    assert sm.phase == "running" and sm.heartbeat() == [] and sm.alive_ranks() == list(range(8))
+    sm.begin_recovery()
+    assert sm.phase == "draining"
+    plan = sm.reshard(ParallelTopology(world_size=6, rank=0, dp_size=1, ep_size=6), 64)
+    assert sm.phase == "recovering" and sorted(sum(plan.values(), [])) == list(range(64))
+    assert [len(v) for v in plan.values()] == [11, 11, 11, 11, 10, 10]
+    sm.mark_resumed()
+    assert sm.phase == "resumed"
+    rb = sm._rebalance_experts([5, 1, 3], None, 7)
+    assert rb == {1: [0, 3, 6], 3: [1, 4], 5: [2, 5]} and sm._rebalance_experts([], None, 4) == {}
+
+
+def test_store_heartbeat_detects_a_silent_rank():
+    class FakeStore(dict):
+        def set(self, k, v):
+            self[k] = v
+
+        def get(self, k):
+            return self[k]
+
+    store = FakeStore()
+    topo0 = ParallelTopology(world_size=2, rank=0, dp_size=2, ep_size=1)
+    topo1 = ParallelTopology(world_size=2, rank=1, dp_size=2, ep_size=1)
+    a = ClusterStateMachine(topo0, drop_grace_s=0.05, store=store)
+    b = ClusterStateMachine(topo1, drop_grace_s=0.05, store=store)
+    dropped = []
+    a.register_on_drop(dropped.extend)
+    b.heartbeat()
+    assert a.heartbeat() == []
+    time.sleep(0.08)  # rank 1 never beats again
+    assert a.heartbeat() == [1] and dropped == [1] and a.alive_ranks() == [0]
+    assert a.heartbeat() == []  # reported once
+    a.mark_dead([0, 1])
+    assert a.alive_ranks() == []
+
+
+@pytest.mark.parametrize("n,k,want", [(8, 8, 8), (6, 8, 6), (6, 4, 3), (7, 4, 1), (12, 5, 4), (1, 8, 1)])
+def test_largest_divisor(n, k, want):
+    assert _largest_divisor_le(n, k) == want
+
+
+def test_schema_check_never_raises():
+    for v in (1, 2, 3):
+        _check_schema_compatibility({"schema_version": v})
+    _check_schema_compatibility({})
+
+
+def test_harness_checkpoint_meta_and_signal_handlers_from_thread(tmp_path):
+    topo = ParallelTopology(world_size=1, rank=0, dp_size=1, ep_size=1)
+    h = ElasticTrainerHarness(ElasticConfig(str(tmp_path / "l"), "file://" + str(tmp_path / "r"), async_workers=1), topo)
+    err = []
+    t = threading.Thread(target=lambda: (h.install_signal_handlers(), err.append(None)))
+    t.start()
+    t.join()
+    assert err == [None]
+    m, opt = _model_and_opt()
+    h.checkpoint(m, opt, 3)
+    assert h.health_check() == []
+    h.shutdown()
+    meta = json.loads((tmp_path / "r" / "ckpts" / "step=000003" / "rank=000000.meta.json").read_text())
+    assert meta["dp_size"] == 1 and meta["ep_size"] == 1 and meta["world_size"] == 1
+
+
+def test_resharded_load_re_owns_experts(tmp_path):
+    """Files written under ep=2 are loaded into an ep=1 model: every expert row comes from its old owner."""
+    from composed_mixture_of_experts_engine_b200.parallel import DistributedMoELayer
+
+    torch.manual_seed(0)
+    full = DistributedMoELayer(8, 16, 4, 2)
+    store = LocalNVMeAdapter(str(tmp_path / "l"))
+    ck = AsyncCheckpointer(store, None, workers=1)
+    for r in range(2):
+        topo = ParallelTopology(world_size=2, rank=r, dp_size=1, ep_size=2)
+        part = DistributedMoELayer(8, 16, 4, 2, topology=topo)
+        with torch.no_grad():
+            part.w13.copy_(full.w13[2 * r:2 * r + 2])
+            part.w2.copy_(full.w2[2 * r:2 * r + 2])
+            part.router.gate_w.copy_(full.router.gate_w)
+        ck.save(part, None, 9, rank=r, extra_meta={"ep_size": 2, "dp_size": 1, "world_size": 2})
+    ck.shutdown()
+    new_topo = ParallelTopology(world_size=1, rank=0, dp_size=1, ep_size=1)
+    h = ElasticTrainerHarness(ElasticConfig(str(tmp_path / "l"), None, async_workers=1), new_topo)
+    fresh = DistributedMoELayer(8, 16, 4, 2)
+    h.load_resharded(fresh, 9, {"ep_size": 2, "dp_size": 1, "world_size": 2}, new_topo, 4)
+    h.shutdown()
+    assert torch.equal(fresh.w13, full.w13) and torch.equal(fresh.w2, full.w2)
+    assert torch.equal(fresh.router.gate_w, full.router.gate_w)

@@ -1,0 +1,92 @@
+"""Telemetry envelope, sinks and thread safety (reference: tests/test_telemetry.py)."""
+
+import json
+import sys
+import threading
+import types
+
+import pytest
+
+import composed_mixture_of_experts_engine_b200.telemetry.logger as L
+from composed_mixture_of_experts_engine_b200.telemetry.logger import (PhaseTimer, PrometheusExporter, StepRecord,
+                                                                      StructuredLogger, WandBSink, overlap_ratio)
+
+pytestmark = pytest.mark.cpu
+
+ENVELOPE = {"step", "loss", "mfu", "tokens_per_sec", "kernel", "collective", "memory", "infra", "routing",
+            "wall_clock_ms", "sparse_mfu", "dead_expert_count", "routing_efficiency", "active_experts",
+            "dropped_token_fraction", "rank", "ts"}
+
+
+def test_envelope_keys_and_routing_mirror(tmp_path):
+    lg = StructuredLogger(str(tmp_path / "a" / "step.jsonl"), rank=3, also_stdout=False, wandb_enabled=False)
+    lg.emit(StepRecord(step=1, loss=2.5, mfu=0.3, tokens_per_sec=100.0, sparse_mfu=0.01, dead_expert_count=2,
+                       routing={"expert_load_imbalance": 1.2}))
+    lg.close()
+    lg.close()  # idempotent
+    rec = json.loads((tmp_path / "a" / "step.jsonl").read_text().strip())
+    assert set(rec) == ENVELOPE and rec["rank"] == 3
+    assert rec["routing"]["sparse_mfu"] == 0.01 and rec["routing"]["dead_expert_count"] == 2
+    assert rec["routing"]["expert_load_imbalance"] == 1.2
+
+
+def test_concurrent_emit(tmp_path):
+    lg = StructuredLogger(str(tmp_path / "s.jsonl"), rank=1, also_stdout=False, wandb_enabled=False)
+    threads = [threading.Thread(target=lambda i=i: lg.emit(StepRecord(i, 1.0, 0.1, 1.0))) for i in range(100)]
+    [t.start() for t in threads]
+    [t.join() for t in threads]
+    lg.close()
+    lines = (tmp_path / "s.jsonl").read_text().strip().splitlines()
+    assert sorted(json.loads(l)["step"] for l in lines) == list(range(100))
+
+
+def test_stdout_only_rank0(tmp_path, capsys):
+    for rank in (0, 1):
+        lg = StructuredLogger(str(tmp_path / f"r{rank}.jsonl"), rank=rank, also_stdout=True, wandb_enabled=False)
+        lg.emit(StepRecord(7, 1.0, 0.1, 1.0))
+        lg.close()
+    out = capsys.readouterr().out.strip().splitlines()
+    assert len(out) == 1 and json.loads(out[0])["rank"] == 0
+
+
+def test_wandb_gating(monkeypatch):
+    calls = []
+    fake = types.SimpleNamespace(init=lambda **kw: calls.append(("init", kw)), log=lambda p, step: calls.append(("log", p, step)),
+                                 finish=lambda: calls.append(("finish",)), run=None,
+                                 config=types.SimpleNamespace(update=lambda c, allow_val_change: calls.append(("cfg", c))))
+    monkeypatch.setattr(L, "_wandb_lib", fake)
+    monkeypatch.setattr(L, "_HAS_WANDB", True)
+    monkeypatch.delenv("WANDB_API_KEY", raising=False)
+    assert not WandBSink(rank=0).active
+    monkeypatch.setenv("WANDB_API_KEY", "k")
+    assert not WandBSink(rank=1).active and not WandBSink(rank=0, enabled=False).active
+    sink = WandBSink(rank=0, init_kwargs={"project": "p"})
+    assert sink.active and calls[0] == ("init", {"project": "p"})
+    sink.log(StepRecord(3, 1.5, 0.2, 9.0, collective={"all_to_all_dispatch_ms": 0.4, "name": "x"}))
+    kind, payload, step = calls[-1]
+    assert kind == "log" and step == 3 and payload["collective/all_to_all_dispatch_ms"] == 0.4
+    assert "collective/name" not in payload and payload["routing/sparse_mfu"] == 0.0
+    sink.log_config({"a": 1})
+    sink.finish()
+    assert not sink.active
+
+
+def test_prometheus_disabled_off_rank0():
+    exp = PrometheusExporter(port=0, rank=1)
+    exp.update(StepRecord(0, 1.0, 0.1, 1.0))  # no-op, must not raise
+
+
+def test_phase_timer_cpu_and_overlap():
+    t = PhaseTimer()
+    with t.phase("a"):
+        sum(range(1000))
+    with t.phase("a"):
+        pass
+    got = t.resolve()
+    assert got["a"] > 0 and t.resolve() == {}
+    off = PhaseTimer(enabled=False)
+    with off.phase("x"):
+        pass
+    assert off.resolve() == {}
+    assert overlap_ratio(1.0, 2.0, 2.0) == 1.0 and overlap_ratio(1.0, 2.0, 3.0) == 0.0
+    assert overlap_ratio(0.0, 1.0, 1.0) == 0.0 and overlap_ratio(2.0, 2.0, 3.0) == 0.5
