@@ -1,0 +1,171 @@
+"""Single-kernel cases for timing and for profiler captures.
+
+    python benchmarks/kernel_cases.py <case> [--iters N] [--small]
+
+Each case builds its inputs (larger than the 126 MB L2, a few GB at most), warms up, then times ``iters``
+launches with CUDA events (an L2-sized buffer is overwritten between launches) and prints one JSON line with the
+achieved bandwidth / throughput and the fraction of the measured peaks (MEASURED_PEAKS.json).  The same command
+line under ``ncu -k regex:<kernel> -c 1`` captures one launch of the case.
+
+Cases: adamw, rmsnorm, router (config-2 shape: T16384 d4096 E64 top2), gemm_dense, grouped_fwd1, grouped_fwd2,
+grouped_dgrad, grouped_wgrad, gather, combine.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+from composed_mixture_of_experts_engine_b200.ops import _ext, kernels  # noqa: E402
+from composed_mixture_of_experts_engine_b200.ops.kernels import (EPI_SWIGLU_BWD, EPI_SWIGLU_FWD, GEMM_GROUPED_K,  # noqa: E402
+                                                                 GEMM_GROUPED_M)
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def time_launches(fn, iters: int, warm: int = 3):
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warm):
+        fn()
+    times = []
+    for _ in range(iters):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def uniform_plan(rows: int, experts: int):
+    tiles = rows // 128
+    tg = (torch.arange(tiles, device="cuda", dtype=torch.int32) // (tiles // experts)).contiguous()
+    nt = torch.tensor([tiles], device="cuda", dtype=torch.int32)
+    go = (torch.arange(experts + 1, device="cuda", dtype=torch.int32) * (rows // experts)).contiguous()
+    return tg, nt, go, tiles
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--small", action="store_true", help="quarter-size inputs (for multi-pass profiler captures)")
+    args = ap.parse_args()
+    ext = _ext.ext()
+    hbm, tflops_peak, how = peaks()
+    dev = "cuda"
+    bf = torch.bfloat16
+    out = {"case": args.case, "peaks": how}
+    shrink = 4 if args.small else 1
+
+    if args.case == "adamw":
+        n = (1 << 28) // shrink
+        p, m, v = (torch.randn(n, device=dev) for _ in range(3))
+        g = torch.randn(n, device=dev)
+        p16 = torch.empty(n, device=dev, dtype=bf)
+        ms = time_launches(lambda: ext.adamw(p, p16, m, v, g, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1, 1.0, 0.0, None, True),
+                           args.iters)
+        nbytes = n * (8 + 8 + 8 + 8 + 2)
+        out.update(ms=ms, gbs=nbytes / ms / 1e6, frac_of_hbm=nbytes / ms / 1e6 / hbm, elements=n)
+    elif args.case == "rmsnorm":
+        rows, H = 32768 // shrink, 2048
+        x = torch.randn(rows, H, device=dev, dtype=bf)
+        w = torch.ones(H, device=dev, dtype=bf)
+        y, dx = torch.empty_like(x), torch.empty_like(x)
+        rstd = torch.empty(rows, device=dev)
+        dw = torch.zeros(H, device=dev)
+        f = time_launches(lambda: ext.rmsnorm_fwd(x, w, y, rstd, 1e-5), args.iters)
+        b = time_launches(lambda: ext.rmsnorm_bwd(y, x, w, rstd, dx, dw), args.iters)
+        nb = rows * H * 2
+        out.update(fwd_ms=f, fwd_gbs=2 * nb / f / 1e6, fwd_frac=2 * nb / f / 1e6 / hbm, bwd_ms=b,
+                   bwd_gbs=3 * nb / b / 1e6, bwd_frac=3 * nb / b / 1e6 / hbm)
+    elif args.case == "router":
+        N, H, E, K = 16384 // (2 if args.small else 1), 4096, 64, 2
+        x = torch.randn(N, H, device=dev, dtype=bf)
+        w = (torch.randn(H, E, device=dev) * 0.02).to(bf)
+        from composed_mixture_of_experts_engine_b200.ops.moe_router import fused_router_forward
+
+        ms = time_launches(lambda: fused_router_forward(x, w, K), max(args.iters, 20))
+        nbytes = N * H * 2 + H * E * 2 + N * E * 4 + N * K * 8 + N * 4
+        out.update(ms=ms, gbs=nbytes / ms / 1e6, frac_of_hbm=nbytes / ms / 1e6 / hbm, tokens_per_s=N / ms * 1e3)
+    elif args.case == "gemm_dense":
+        M = N = K = 8192 // (2 if args.small else 1)
+        A = torch.randn(M, K, device=dev, dtype=bf)
+        B = torch.randn(N, K, device=dev, dtype=bf)
+        D = torch.empty(M, N, device=dev, dtype=bf)
+        ms = time_launches(lambda: kernels.gemm(A, B, D, M=M, N=N, K=K), args.iters)
+        lib = time_launches(lambda: torch.matmul(A, B.t(), out=D), args.iters)
+        fl = 2 * M * N * K
+        out.update(ms=ms, tflops=fl / ms / 1e9, frac_of_peak=fl / ms / 1e9 / tflops_peak, cublas_ms=lib,
+                   cublas_tflops=fl / lib / 1e9)
+    elif args.case.startswith("grouped_") or args.case in ("gather", "combine"):
+        E, H, F = 64, 2048, 1024
+        R = 65536 // shrink
+        tg, nt, go, tiles = uniform_plan(R, E)
+        X = torch.randn(R, H, device=dev, dtype=bf)
+        W13 = (torch.randn(E, 2 * F, H, device=dev) * 0.02).to(bf)
+        W2 = (torch.randn(E, H, F, device=dev) * 0.02).to(bf)
+        Hact = torch.randn(R, F, device=dev, dtype=bf)
+        GU = torch.randn(R, 2 * F, device=dev, dtype=bf)
+        Y = torch.randn(R, H, device=dev, dtype=bf)
+        common = dict(groups=E, tile_group=tg, num_m_tiles=nt, max_m_tiles=tiles)
+        if args.case == "grouped_fwd1":
+            fn = lambda: kernels.gemm(X, W13.view(-1, H), Hact, mode=GEMM_GROUPED_M, epilogue=EPI_SWIGLU_FWD, N=F, K=H,
+                                      b_group_rows=2 * F, split_n=F, aux_out=GU, **common)
+            fl = 2 * R * 2 * F * H
+        elif args.case == "grouped_fwd2":
+            fn = lambda: kernels.gemm(Hact, W2.view(-1, F), Y, mode=GEMM_GROUPED_M, N=H, K=F, b_group_rows=H, **common)
+            fl = 2 * R * F * H
+        elif args.case == "grouped_dgrad":
+            dGU = torch.empty_like(GU)
+            fn = lambda: kernels.gemm(Y, W2.view(-1, F), dGU, mode=GEMM_GROUPED_M, epilogue=EPI_SWIGLU_BWD, N=F, K=H,
+                                      b_mn=True, b_group_rows=H, aux_in=GU, **common)
+            fl = 2 * R * F * H
+        elif args.case == "grouped_wgrad":
+            dW13 = torch.zeros(E, 2 * F, H, device=dev)
+            fn = lambda: kernels.gemm(GU, X, dW13, mode=GEMM_GROUPED_K, M=2 * F, N=H, a_mn=True, b_mn=True, groups=E,
+                                      group_offsets=go, d_group_stride=2 * F * H, accumulate=True)
+            fl = 2 * R * 2 * F * H
+        else:
+            N, K = R // 8, 8
+            idx = torch.stack([torch.randperm(E, device=dev)[:K] for _ in range(N)]).to(torch.int32)
+            plan = kernels.moe_plan(idx, E)
+            src = torch.randn(N, H, device=dev, dtype=bf)
+            rows = torch.randn(plan.cap_rows, H, device=dev, dtype=bf)
+            wts = torch.rand(N, K, device=dev)
+            if args.case == "gather":
+                fn = lambda: kernels.gather_rows(src, plan, out=rows)
+            else:
+                yv = torch.empty(N, H, device=dev, dtype=bf)
+                fn = lambda: kernels.combine_rows(rows, plan, wts, out=yv)
+            ms = time_launches(fn, args.iters)
+            nbytes = (N * K + N) * H * 2
+            out.update(ms=ms, gbs=nbytes / ms / 1e6, frac_of_hbm=nbytes / ms / 1e6 / hbm)
+            print(json.dumps(out))
+            return
+        ms = time_launches(fn, args.iters)
+        out.update(ms=ms, tflops=fl / ms / 1e9, frac_of_peak=fl / ms / 1e9 / tflops_peak, rows=R)
+    else:
+        raise SystemExit(f"unknown case {args.case}")
+    kernels.check_status(torch.device("cuda", 0))
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

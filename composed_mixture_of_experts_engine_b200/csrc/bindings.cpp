@@ -232,7 +232,8 @@ int64_t moe_plan_scratch_words(int64_t n_slots, int64_t n_local, int64_t K, bool
 }
 void moe_plan(const Tensor& topk_idx, int64_t K, int64_t num_experts, int64_t expert_lo, int64_t n_local,
               bool per_k_bins, int64_t capacity, Tensor& slot_row, Tensor& row_slot, Tensor& group_offsets,
-              Tensor& tile_group, Tensor& num_m_tiles, Tensor& counts_kept, Tensor& scratch) {
+              Tensor& tile_group, Tensor& num_m_tiles, Tensor& counts_kept, Tensor& scratch,
+              const OptTensor& overflow) {
   const c10::cuda::CUDAGuard guard(topk_idx.device());
   TORCH_CHECK(topk_idx.scalar_type() == at::kInt && topk_idx.is_contiguous());
   cmoe::MoePlanArgs a;
@@ -256,6 +257,7 @@ void moe_plan(const Tensor& topk_idx, int64_t K, int64_t num_experts, int64_t ex
   a.num_m_tiles = num_m_tiles.data_ptr<int>();
   a.counts_kept = counts_kept.data_ptr<int>();
   a.scratch = scratch.data_ptr<int>();
+  a.overflow = opt_ptr<int>(overflow);
   check_cuda(cmoe::launch_moe_plan(a, cur_stream()), "moe_plan");
 }
 void gather_rows(const Tensor& src, const Tensor& row_slot, int64_t slot_div, const OptTensor& slot_scale, Tensor& out,

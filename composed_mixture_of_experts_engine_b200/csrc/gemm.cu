@@ -143,12 +143,14 @@ __device__ __forceinline__ void store_row_chunk(void* D, long long ldd, int d_fp
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
       if (col + j < n_limit) {  // N is a multiple of 8, so groups of 4 are all-in or all-out
-        float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
         if (accumulate) {
-          const float4 old = *reinterpret_cast<const float4*>(dst + j);
-          o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+          // fire-and-forget vector reduction: the add happens in L2, the SM never waits for the old value
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j), "f"(v[j]), "f"(v[j + 1]),
+                       "f"(v[j + 2]), "f"(v[j + 3])
+                       : "memory");
+        } else {
+          *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
         }
-        *reinterpret_cast<float4*>(dst + j) = o;
       }
     }
   } else {

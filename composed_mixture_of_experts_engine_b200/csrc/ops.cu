@@ -45,44 +45,48 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 // ------------------------------------------------------------------------------------ RMSNorm
-constexpr int RN_THREADS = 256;
-constexpr int RN_MAX_VEC = 4;  // up to H = 256 * 8 * 4 = 8192 columns kept in registers
+// One CTA of 128 threads per row; each thread keeps VEC vectors of 8 columns in registers
+// (VEC = 1, 2, 4, 8 covers H <= 1024, 2048, 4096, 8192).  Small CTAs keep 16 rows in flight per SM.
+constexpr int RN_THREADS = 128;
 
+template <int VEC>
 __global__ void __launch_bounds__(RN_THREADS) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
                                                                  const __nv_bfloat16* __restrict__ w,
                                                                  __nv_bfloat16* __restrict__ y,
                                                                  float* __restrict__ rstd, long long rows, int H,
                                                                  float eps) {
   __shared__ float red[RN_THREADS / 32];
-  const long long row = blockIdx.x;
-  const __nv_bfloat16* xr = x + row * H;
-  float v[RN_MAX_VEC][8];
-  float ss = 0.f;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const __nv_bfloat16* xr = x + row * H;
+    float v[VEC][8];
+    float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < RN_MAX_VEC; ++i) {
-    const int c = (i * RN_THREADS + threadIdx.x) * 8;
-    if (c < H) {
-      load8(xr + c, v[i]);
+    for (int i = 0; i < VEC; ++i) {
+      const int c = (i * RN_THREADS + threadIdx.x) * 8;
+      if (c < H) {
+        load8(xr + c, v[i]);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+        for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+      }
     }
-  }
-  ss = block_sum<RN_THREADS>(ss, red);
-  const float r = rsqrtf(ss / H + eps);
-  if (threadIdx.x == 0 && rstd) rstd[row] = r;
+    ss = block_sum<RN_THREADS>(ss, red);
+    const float r = rsqrtf(ss / H + eps);
+    if (threadIdx.x == 0 && rstd) rstd[row] = r;
 #pragma unroll
-  for (int i = 0; i < RN_MAX_VEC; ++i) {
-    const int c = (i * RN_THREADS + threadIdx.x) * 8;
-    if (c < H) {
-      float wv[8], o[8];
-      load8(w + c, wv);
+    for (int i = 0; i < VEC; ++i) {
+      const int c = (i * RN_THREADS + threadIdx.x) * 8;
+      if (c < H) {
+        float wv[8], o[8];
+        load8(w + c, wv);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = v[i][j] * r * wv[j];
-      store8(y + row * H + c, o);
+        for (int j = 0; j < 8; ++j) o[j] = v[i][j] * r * wv[j];
+        store8(y + row * H + c, o);
+      }
     }
   }
 }
 
+template <int VEC>
 __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
                                                                  const __nv_bfloat16* __restrict__ x,
                                                                  const __nv_bfloat16* __restrict__ w,
@@ -90,20 +94,23 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
                                                                  __nv_bfloat16* __restrict__ dx, float* __restrict__ dw,
                                                                  long long rows, int H) {
   __shared__ float red[RN_THREADS / 32];
-  float wv[RN_MAX_VEC][8], dwacc[RN_MAX_VEC][8];
+  float wv[VEC][8], dwacc[VEC][8];
 #pragma unroll
-  for (int i = 0; i < RN_MAX_VEC; ++i) {
+  for (int i = 0; i < VEC; ++i) {
     const int c = (i * RN_THREADS + threadIdx.x) * 8;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+    for (int j = 0; j < 8; ++j) {
+      dwacc[i][j] = 0.f;
+      wv[i][j] = 0.f;
+    }
     if (c < H) load8(w + c, wv[i]);
   }
   for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
     const float r = rstd[row];
-    float xh[RN_MAX_VEC][8], g[RN_MAX_VEC][8];
+    float xh[VEC][8], g[VEC][8];
     float dot = 0.f;
 #pragma unroll
-    for (int i = 0; i < RN_MAX_VEC; ++i) {
+    for (int i = 0; i < VEC; ++i) {
       const int c = (i * RN_THREADS + threadIdx.x) * 8;
       if (c < H) {
         float xv[8], dv[8];
@@ -120,7 +127,7 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
     }
     dot = block_sum<RN_THREADS>(dot, red) / H;
 #pragma unroll
-    for (int i = 0; i < RN_MAX_VEC; ++i) {
+    for (int i = 0; i < VEC; ++i) {
       const int c = (i * RN_THREADS + threadIdx.x) * 8;
       if (c < H) {
         float o[8];
@@ -132,7 +139,7 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
   }
   if (dw) {
 #pragma unroll
-    for (int i = 0; i < RN_MAX_VEC; ++i) {
+    for (int i = 0; i < VEC; ++i) {
       const int c = (i * RN_THREADS + threadIdx.x) * 8;
       if (c < H) {
 #pragma unroll
@@ -178,41 +185,52 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ t, const float* __restri
 __global__ void adamw_kernel(const AdamWArgs a) {
   float gs = a.grad_scale;
   if (a.max_norm > 0.f && a.sumsq != nullptr) {
-    const float norm = sqrtf(*a.sumsq) * a.grad_scale;
+    const float norm = sqrtf(*a.sumsq);  // sumsq already refers to the scaled gradients
     gs *= fminf(1.f, a.max_norm / (norm + 1e-6f));
   }
   const float inv_bc1 = 1.f / a.bias_corr1;
   const float inv_sqrt_bc2 = rsqrtf(a.bias_corr2);
   const long long n4 = a.n / 4;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  float4* __restrict__ p32v = reinterpret_cast<float4*>(a.p32);
+  float4* __restrict__ mv = reinterpret_cast<float4*>(a.m);
+  float4* __restrict__ vv4 = reinterpret_cast<float4*>(a.v);
+  uint2* __restrict__ p16v = reinterpret_cast<uint2*>(a.p16);
+  float4* __restrict__ g32v = reinterpret_cast<float4*>(const_cast<void*>(a.grad));
+  uint2* __restrict__ g16v = reinterpret_cast<uint2*>(const_cast<void*>(a.grad));
+  const float decay = 1.f - a.lr * a.weight_decay;
+  const float omb1 = 1.f - a.beta1, omb2 = 1.f - a.beta2;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4; i += stride) {
-    float4 p = reinterpret_cast<const float4*>(a.p32)[i];
-    float4 m = reinterpret_cast<const float4*>(a.m)[i];
-    float4 v = reinterpret_cast<const float4*>(a.v)[i];
+    // all loads first (streaming: nothing here is read twice), then the math, then the stores
+    const float4 p = __ldcs(p32v + i);
+    const float4 m = __ldcs(mv + i);
+    const float4 v = __ldcs(vv4 + i);
     float g[4];
     if (a.grad_is_bf16) {
-      const uint2 raw = reinterpret_cast<const uint2*>(a.grad)[i];
+      const uint2 raw = __ldcs(g16v + i);
       const float2 g0 = unpack_bf16x2(raw.x), g1 = unpack_bf16x2(raw.y);
       g[0] = g0.x; g[1] = g0.y; g[2] = g1.x; g[3] = g1.y;
-      if (a.zero_grad) reinterpret_cast<uint2*>(const_cast<void*>(a.grad))[i] = make_uint2(0u, 0u);
     } else {
-      const float4 raw = reinterpret_cast<const float4*>(a.grad)[i];
+      const float4 raw = __ldcs(g32v + i);
       g[0] = raw.x; g[1] = raw.y; g[2] = raw.z; g[3] = raw.w;
-      if (a.zero_grad) reinterpret_cast<float4*>(const_cast<void*>(a.grad))[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     float pp[4] = {p.x, p.y, p.z, p.w}, mm[4] = {m.x, m.y, m.z, m.w}, vv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float gj = g[j] * gs;
-      mm[j] = a.beta1 * mm[j] + (1.f - a.beta1) * gj;
-      vv[j] = a.beta2 * vv[j] + (1.f - a.beta2) * gj * gj;
+      mm[j] = a.beta1 * mm[j] + omb1 * gj;
+      vv[j] = a.beta2 * vv[j] + omb2 * gj * gj;
       const float denom = sqrtf(vv[j]) * inv_sqrt_bc2 + a.eps;
-      pp[j] = pp[j] * (1.f - a.lr * a.weight_decay) - a.lr * (mm[j] * inv_bc1) / denom;
+      pp[j] = pp[j] * decay - a.lr * (mm[j] * inv_bc1) * __frcp_rn(denom);
     }
-    reinterpret_cast<float4*>(a.p32)[i] = make_float4(pp[0], pp[1], pp[2], pp[3]);
-    reinterpret_cast<float4*>(a.m)[i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
-    reinterpret_cast<float4*>(a.v)[i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
-    if (a.p16) reinterpret_cast<uint2*>(a.p16)[i] = make_uint2(pack_bf16x2(pp[0], pp[1]), pack_bf16x2(pp[2], pp[3]));
+    __stcs(p32v + i, make_float4(pp[0], pp[1], pp[2], pp[3]));
+    __stcs(mv + i, make_float4(mm[0], mm[1], mm[2], mm[3]));
+    __stcs(vv4 + i, make_float4(vv[0], vv[1], vv[2], vv[3]));
+    if (a.p16) p16v[i] = make_uint2(pack_bf16x2(pp[0], pp[1]), pack_bf16x2(pp[2], pp[3]));
+    if (a.zero_grad) {
+      if (a.grad_is_bf16) __stcs(g16v + i, make_uint2(0u, 0u));
+      else __stcs(g32v + i, make_float4(0.f, 0.f, 0.f, 0.f));
+    }
   }
   // tail (n not a multiple of 4)
   const long long tail0 = n4 * 4;
@@ -395,8 +413,12 @@ __global__ void __launch_bounds__(1024) moe_plan_scan_kernel(const MoePlanArgs a
         bin_base[e * kb + k] = off + cnt;
         cnt += bin_total[e * kb + k];
       }
+      // rows that do not fit the buffer are dropped by the assign pass (and counted in `overflow`)
+      const long long room = a.cap_rows - off;
+      if (cnt > room) cnt = room > 0 ? static_cast<int>(room) : 0;
       a.counts_kept[e] = cnt;
       off += (cnt + 127) / 128 * 128;
+      if (off > a.cap_rows) off = static_cast<int>(a.cap_rows / 128 * 128);
     }
     a.group_offsets[a.n_local] = off;
     *a.num_m_tiles = off / 128;
@@ -431,6 +453,10 @@ __global__ void __launch_bounds__(PLAN_WARPS * 32) moe_plan_assign_kernel(const 
     if (bin >= 0) {
       const int rank = hist[bin] + __popc(peers & ((1u << lane) - 1u));
       if (a.capacity <= 0 || rank < a.capacity) row = bin_base[bin] + rank;
+      if (row >= a.cap_rows) {  // the row buffer is full: drop the slot and report it
+        row = -1;
+        if (a.overflow) atomicAdd(a.overflow, 1);
+      }
     }
     __syncwarp();
     if (bin >= 0 && (peers & ((1u << lane) - 1u)) == 0u) hist[bin] += __popc(peers);
@@ -534,22 +560,43 @@ inline unsigned grid_for(long long work_items, int per_block, int max_blocks) {
 
 }  // namespace
 
+inline int rn_vec_for(int H) {
+  const int per = RN_THREADS * 8;
+  const int need = (H + per - 1) / per;
+  return need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
+}
+
 cudaError_t launch_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int H, float eps,
                                cudaStream_t stream) {
-  if (H % 8 != 0 || H > RN_THREADS * 8 * RN_MAX_VEC || rows <= 0) return cudaErrorInvalidValue;
-  rmsnorm_fwd_kernel<<<static_cast<unsigned>(rows), RN_THREADS, 0, stream>>>(
-      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(w),
-      reinterpret_cast<__nv_bfloat16*>(y), rstd, rows, H, eps);
+  if (H % 8 != 0 || H > RN_THREADS * 8 * 8 || rows <= 0) return cudaErrorInvalidValue;
+  const unsigned grid = grid_for(rows, 1, 148 * 32);
+  auto xb = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto wb = reinterpret_cast<const __nv_bfloat16*>(w);
+  auto yb = reinterpret_cast<__nv_bfloat16*>(y);
+  switch (rn_vec_for(H)) {
+    case 1: rmsnorm_fwd_kernel<1><<<grid, RN_THREADS, 0, stream>>>(xb, wb, yb, rstd, rows, H, eps); break;
+    case 2: rmsnorm_fwd_kernel<2><<<grid, RN_THREADS, 0, stream>>>(xb, wb, yb, rstd, rows, H, eps); break;
+    case 4: rmsnorm_fwd_kernel<4><<<grid, RN_THREADS, 0, stream>>>(xb, wb, yb, rstd, rows, H, eps); break;
+    default: rmsnorm_fwd_kernel<8><<<grid, RN_THREADS, 0, stream>>>(xb, wb, yb, rstd, rows, H, eps); break;
+  }
   return cudaGetLastError();
 }
 
 cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw,
                                long long rows, int H, int num_sms, cudaStream_t stream) {
-  if (H % 8 != 0 || H > RN_THREADS * 8 * RN_MAX_VEC || rows <= 0) return cudaErrorInvalidValue;
-  const unsigned grid = grid_for(rows, 1, (num_sms > 0 ? num_sms : 148) * 4);
-  rmsnorm_bwd_kernel<<<grid, RN_THREADS, 0, stream>>>(
-      reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x),
-      reinterpret_cast<const __nv_bfloat16*>(w), rstd, reinterpret_cast<__nv_bfloat16*>(dx), dw, rows, H);
+  if (H % 8 != 0 || H > RN_THREADS * 8 * 8 || rows <= 0) return cudaErrorInvalidValue;
+  // every CTA ends with H atomics into dw: enough CTAs to hide the row latency, few enough to keep those cheap
+  const unsigned grid = grid_for(rows, 1, (num_sms > 0 ? num_sms : 148) * 8);
+  auto dyb = reinterpret_cast<const __nv_bfloat16*>(dy);
+  auto xb = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto wb = reinterpret_cast<const __nv_bfloat16*>(w);
+  auto dxb = reinterpret_cast<__nv_bfloat16*>(dx);
+  switch (rn_vec_for(H)) {
+    case 1: rmsnorm_bwd_kernel<1><<<grid, RN_THREADS, 0, stream>>>(dyb, xb, wb, rstd, dxb, dw, rows, H); break;
+    case 2: rmsnorm_bwd_kernel<2><<<grid, RN_THREADS, 0, stream>>>(dyb, xb, wb, rstd, dxb, dw, rows, H); break;
+    case 4: rmsnorm_bwd_kernel<4><<<grid, RN_THREADS, 0, stream>>>(dyb, xb, wb, rstd, dxb, dw, rows, H); break;
+    default: rmsnorm_bwd_kernel<8><<<grid, RN_THREADS, 0, stream>>>(dyb, xb, wb, rstd, dxb, dw, rows, H); break;
+  }
   return cudaGetLastError();
 }
 

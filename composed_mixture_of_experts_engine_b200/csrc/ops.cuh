@@ -24,8 +24,9 @@ cudaError_t launch_rope(void* t, const float* cos_tab, const float* sin_tab, lon
 // ---- fused AdamW ---------------------------------------------------------------------------
 // Decoupled weight decay; p32 is the fp32 master copy, p16 (optional) the bf16 copy that the model
 // computes with.  grad is fp32 or bf16.  The gradient is first multiplied by
-//   grad_scale * min(1, max_norm / (sqrt(*sumsq) * grad_scale + 1e-6))      (max_norm <= 0: no clipping)
-// where sumsq is a device scalar produced by launch_sumsq over the same (unscaled) gradients.
+//   grad_scale * min(1, max_norm / (sqrt(*sumsq) + 1e-6))      (max_norm <= 0: no clipping)
+// where sumsq is a device scalar holding the squared global norm of the already scaled gradients
+// (launch_sumsq over the raw gradients, times grad_scale^2, summed over all parameter groups).
 struct AdamWArgs {
   float* p32 = nullptr;
   void* p16 = nullptr;
@@ -81,6 +82,7 @@ struct MoePlanArgs {
   int* num_m_tiles = nullptr;
   int* counts_kept = nullptr;
   int* scratch = nullptr;
+  int* overflow = nullptr;  // optional counter: slots dropped because cap_rows was too small for the routing
 };
 size_t moe_plan_scratch_words(long long n_slots, int n_local, int K, int per_k_bins);
 cudaError_t launch_moe_plan(const MoePlanArgs& a, cudaStream_t stream);

@@ -193,7 +193,7 @@ class Trainer:
                     g["lr"] = lr
                 self._reduce_grads_library()
                 if self.cfg.training.grad_clip > 0:
-                    torch.nn.utils.clip_grad_norm_(self.model.parameters(), self.cfg.training.grad_clip)
+                    self._clip_grads_library(self.cfg.training.grad_clip)
                 self.optimizer.step()
                 self.optimizer.zero_grad(set_to_none=True)
         self.step_index += 1
@@ -217,6 +217,36 @@ class Trainer:
             elif dp_group is not None:
                 dist.all_reduce(p.grad, group=dp_group)
                 p.grad.div_(topo.dp_size)
+
+    def _clip_grads_library(self, max_norm: float) -> None:
+        """Global-norm clipping where every rank arrives at the same norm: replicated parameters count once,
+        expert shards are summed over the ranks that hold different experts (and pipeline stages)."""
+        topo = self.topology
+        dense_sq = torch.zeros((), dtype=torch.float64, device=self.device)
+        expert_sq = torch.zeros((), dtype=torch.float64, device=self.device)
+        for p in self.model.parameters():
+            if p.grad is None:
+                continue
+            sq = p.grad.detach().double().pow(2).sum()
+            if getattr(p, "is_expert_param", False):
+                expert_sq += sq
+            else:
+                dense_sq += sq
+        if dist.is_initialized() and topo.world_size > 1:
+            from .parallel.mesh import ep_process_group, pp_process_group
+
+            if topo.ep_size > 1:
+                dist.all_reduce(expert_sq, group=ep_process_group(topo))
+            total = dense_sq + expert_sq
+            if topo.pp_size > 1:
+                dist.all_reduce(total, group=pp_process_group(topo))
+        else:
+            total = dense_sq + expert_sq
+        coef = float(max_norm / (total.sqrt() + 1e-6))
+        if coef < 1.0:
+            for p in self.model.parameters():
+                if p.grad is not None:
+                    p.grad.mul_(coef)
 
     def _pipeline_step(self, ids: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         m = self.cfg.parallelism.pipeline_microbatches or self.accum

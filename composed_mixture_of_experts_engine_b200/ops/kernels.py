@@ -140,6 +140,29 @@ def linear_tn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = No
     return out
 
 
+_overflow: Dict[int, torch.Tensor] = {}
+
+
+def overflow_counter(device: torch.device) -> torch.Tensor:
+    """Per-device counter of (token, slot) pairs that a row plan had to drop because its buffer was too small."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _overflow.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _overflow[idx] = t
+    return t
+
+
+def ep_buffer_rows(n_slots_expected: int, n_local: int, worst_case: int) -> int:
+    """Row capacity of expert-parallel buffers: the expected rows times ``CMOE_EP_BUFFER_FACTOR`` (default 1.5)
+    plus tile padding, never more than the worst case.  Slots beyond it are dropped and counted."""
+    import os
+
+    factor = float(os.environ.get("CMOE_EP_BUFFER_FACTOR", "1.5"))
+    want = int(n_slots_expected * factor) + n_local * 128
+    return min(plan_capacity_rows(worst_case, n_local), (want + 127) // 128 * 128)
+
+
 class MoEPlan:
     """Device-resident description of one expert-sorted, 128-row-padded row layout."""
 
@@ -188,7 +211,7 @@ def moe_plan(topk_idx: torch.Tensor, num_experts: int, expert_lo: int = 0, n_loc
     words = ext.moe_plan_scratch_words(N * K, n_local, K, per_k)
     ext.moe_plan(topk_idx, K, num_experts, expert_lo, n_local, per_k, capacity, plan.slot_row, plan.row_slot,
                  plan.group_offsets, plan.tile_group, plan.num_m_tiles, plan.counts_kept,
-                 _scratch_i32(topk_idx.device, words))
+                 _scratch_i32(topk_idx.device, words), overflow_counter(topk_idx.device))
     return plan
 
 

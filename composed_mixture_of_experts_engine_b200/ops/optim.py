@@ -69,7 +69,7 @@ class _FlatGroup:
         self.v = torch.zeros_like(self.master)
         # per-element decay is applied per segment: split the shard into decay / no-decay runs
         self._segments = self._build_segments()
-        self.g_shard_f32: Optional[torch.Tensor] = None
+        self.grad_scale = 1.0  # extra factor on this group's gradients (1/ep for expert weights, see build_optimizer)
 
     def _build_segments(self) -> List[Tuple[int, int, bool]]:
         """(start, end, decay) runs inside this rank's shard, in shard-local coordinates."""
@@ -110,6 +110,7 @@ class FusedAdamW:
         self.step_count = 0
         dev = groups[0].flat_p.device
         self.sumsq = torch.zeros(1, device=dev, dtype=torch.float32)
+        self._tmp = torch.zeros(1, device=dev, dtype=torch.float32)
         self.last_grad_norm_sq: Optional[torch.Tensor] = None
         self._norm_groups = list(norm_groups)  # process groups over which the squared norm is summed
         self.param_groups = [{"lr": lr, "params": [p for g in groups for p in g.params]}]
@@ -165,12 +166,15 @@ class FusedAdamW:
         self.step_count += 1
         shards = []
         self.sumsq.zero_()
+        tmp = self._tmp
         for g in self.groups:
             g.reassign_grads()
             gs = self._reduce_grads(g)
             shards.append(gs)
             if self.max_grad_norm > 0:
-                ext.sumsq(gs, self.sumsq)
+                tmp.zero_()
+                ext.sumsq(gs, tmp)
+                self.sumsq.add_(tmp, alpha=g.grad_scale ** 2)
         if self.max_grad_norm > 0:
             for pg in self._norm_groups:
                 if pg is not None:
@@ -182,7 +186,7 @@ class FusedAdamW:
             p16_base = g.flat_p[g.shard_lo:g.shard_lo + g.shard_numel]
             for a, b, decay in g._segments:
                 ext.adamw(g.master[a:b], p16_base[a:b], g.m[a:b], g.v[a:b], gs[a:b], self.lr, b1, b2, self.eps,
-                          self.weight_decay if decay else 0.0, self.step_count, 1.0, self.max_grad_norm,
+                          self.weight_decay if decay else 0.0, self.step_count, g.grad_scale, self.max_grad_norm,
                           self.sumsq if self.max_grad_norm > 0 else None, not sharded)
             if sharded:
                 g.flat_g.zero_()
@@ -224,6 +228,10 @@ def build_optimizer(model: nn.Module, lr: float, weight_decay: float = 0.1, beta
     if expert:
         groups.append(_FlatGroup("expert", [p for _, p in expert], torch.float32, [True] * len(expert),
                                  shard_group=expert_dp_group))
+        # an expert's gradient already sums the contributions of the `ep` ranks whose tokens it served; the
+        # objective is the mean over all data-parallel ranks, so 1/ep is still missing after the edp average
+        if topology is not None and dist.is_initialized() and topology.ep_size > 1:
+            groups[-1].grad_scale = 1.0 / topology.ep_size
     norm_groups = []
     if topology is not None and dist.is_initialized() and topology.world_size > 1:
         norm_groups = [dist.group.WORLD]

@@ -278,7 +278,7 @@ class DistributedMoELayer(nn.Module):
             idx32 = self.router.last_idx32 if self.router.last_idx32 is not None else idx.to(torch.int32)
             with self._timer.phase("experts"):
                 y = OF.local_moe(flat, gate_w, idx32, self.w13, self.w2, cap, self._last_plan_holder)
-        elif device_path and ep_active and self._peer_path_ok():
+        elif device_path and ep_active:
             from . import symm_ep
 
             self._dropped_host = None if cap > 0 else 0.0

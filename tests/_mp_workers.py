@@ -12,21 +12,26 @@ if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
 
-def _init(rank: int, world: int, port: int):
+def _init(rank: int, world: int, port: int, backend: str = "gloo"):
+    import torch
     import torch.distributed as dist
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
-                      GLOO_SOCKET_IFNAME="lo")
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+                      LOCAL_RANK=str(rank), GLOO_SOCKET_IFNAME="lo")
+    if backend == "nccl":
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    else:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
 
 
-def run(fn_name: str, rank: int, world: int, port: int, queue, args):
+def run(fn_name: str, rank: int, world: int, port: int, queue, args, backend: str = "gloo"):
     import torch
     import torch.distributed as dist
 
     torch.set_num_threads(1)
     try:
-        _init(rank, world, port)
+        _init(rank, world, port, backend)
         out = globals()[fn_name](rank, world, *args)
         queue.put((rank, "ok", out))
     except Exception:
@@ -192,3 +197,75 @@ def trainer_steps(rank, world, config_path, steps):
     dist.broadcast(ref, src=0)
     return {"losses": losses, "gate_sync": float((gate - ref).abs().max()), "ep": tr.topology.ep_size,
             "local_experts": tr.model.blocks[0].moe.local_expert_ids}
+
+
+# -------------------------------------------------------------------------------------------------- GPU workers
+def gpu_ep_layer(rank, world, transport):
+    """bf16 expert-parallel layer on `world` GPUs vs the same layer with all experts on one GPU."""
+    import torch
+    import torch.distributed as dist
+
+    os.environ["CMOE_EP_TRANSPORT"] = transport
+    from composed_mixture_of_experts_engine_b200.ops.kernels import check_status
+    from composed_mixture_of_experts_engine_b200.parallel import DistributedMoELayer, build_topology
+
+    H, F, E, K, N = 256, 512, 16, 4, 1024
+    topo = build_topology(1, world, device_type="cuda")
+    dev = topo.device
+    torch.manual_seed(0)
+    full = DistributedMoELayer(H, F, E, K, dtype=torch.bfloat16).to(dev)
+    layer = DistributedMoELayer(H, F, E, K, topology=topo, dtype=torch.bfloat16).to(dev)
+    mine = topo.experts_on_this_rank(E)
+    with torch.no_grad():
+        layer.router.gate_w.copy_(full.router.gate_w)
+        layer.w13.copy_(full.w13[mine[0]:mine[-1] + 1])
+        layer.w2.copy_(full.w2[mine[0]:mine[-1] + 1])
+    out = {}
+    for it in range(2):  # twice: buffers and flags are reused
+        torch.manual_seed(100 + rank + 10 * it)
+        x = torch.randn(N, H, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        dy = torch.randn(N, H, device=dev, dtype=torch.bfloat16)
+        for l in (layer, full):
+            l.zero_grad(set_to_none=True)
+        y = layer(x)
+        y.backward(dy)
+        x2 = x.detach().clone().requires_grad_(True)
+        y2 = full(x2)
+        y2.backward(dy)
+        g13 = full.w13.grad.float().clone()
+        dist.all_reduce(g13)
+        rel = lambda a, b: float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
+        out[f"y{it}"] = rel(y, y2)
+        out[f"dx{it}"] = rel(x.grad, x2.grad)
+        out[f"dw13_{it}"] = rel(layer.w13.grad, g13[mine[0]:mine[-1] + 1])
+        out[f"dgate{it}"] = rel(layer.router.gate_w.grad, full.router.gate_w.grad)
+    check_status(dev)
+    return out
+
+
+def gpu_trainer(rank, world, transport, steps):
+    """Trainer on `world` GPUs (dp = ep = world, sharded optimizer): finite decreasing loss, replicas in sync."""
+    import torch
+    import torch.distributed as dist
+
+    os.environ["CMOE_EP_TRANSPORT"] = transport
+    from composed_mixture_of_experts_engine_b200.engine import Trainer
+    from composed_mixture_of_experts_engine_b200.ops.kernels import check_status
+    from composed_mixture_of_experts_engine_b200.utils.config import MoEConfig
+
+    cfg = MoEConfig.from_dict({
+        "model": dict(arch="moe_decoder", hidden_dim=256, num_layers=2, num_heads=4, num_experts=8, top_k=2,
+                      ffn_dim=256, vocab_size=2048, sequence_length=256, dtype="bfloat16", aux_loss_coeff=0.01,
+                      init_std=0.02),
+        "training": dict(micro_batch_size=2, gradient_accumulation_steps=2, max_steps=100, warmup_steps=0,
+                         learning_rate=1e-3),
+        "parallelism": dict(data_parallel=world, expert_parallel=world, ep_from_dp=True)})
+    tr = Trainer(cfg)
+    ids, tgt = tr.synthetic_batch(torch.Generator().manual_seed(rank))
+    losses = [float(tr.train_step(ids, tgt)) for _ in range(steps)]
+    check_status(tr.device)
+    w = tr.model.blocks[0].attn.wqkv.weight.detach().float().clone()
+    ref = w.clone()
+    dist.broadcast(ref, src=0)
+    return {"losses": losses, "sync": float((w - ref).abs().max()), "ep": tr.topology.ep_size,
+            "n_local": len(tr.model.blocks[0].moe.local_expert_ids)}

@@ -371,7 +371,7 @@ def test_moe_plan_gather_combine(ext, N, K, E, cap):
     nt = torch.empty(1, device="cuda", dtype=torch.int32)
     kept = torch.empty(E, device="cuda", dtype=torch.int32)
     scratch = torch.empty(ext.moe_plan_scratch_words(N * K, E, K, per_k), device="cuda", dtype=torch.int32)
-    ext.moe_plan(idx, K, E, 0, E, per_k, cap, slot_row, row_slot, goffs, tg, nt, kept, scratch)
+    ext.moe_plan(idx, K, E, 0, E, per_k, cap, slot_row, row_slot, goffs, tg, nt, kept, scratch, None)
     torch.cuda.synchronize()
     idx_c, sr, rs, go = idx.cpu().long(), slot_row.cpu(), row_slot.cpu(), goffs.cpu()
     # reference layout on the CPU

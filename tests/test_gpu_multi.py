@@ -1,0 +1,57 @@
+"""Multi-GPU paths (one process per GPU, NCCL): expert parallelism on the device path and the sharded optimizer.
+
+Runs only where at least two CUDA devices are visible.  Oracles are single-GPU computations of the same math."""
+
+import math
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from tests import _mp_workers
+from tests.conftest import find_free_port
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _spawn_gpu(fn_name, world, *args, timeout=600):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = find_free_port()
+    procs = [ctx.Process(target=_mp_workers.run, args=(fn_name, r, world, port, q, args, "nccl")) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = {}
+    try:
+        for _ in range(world):
+            rank, status, payload = q.get(timeout=timeout)
+            assert status == "ok", f"rank {rank} failed:\n{payload}"
+            results[rank] = payload
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    return results
+
+
+def _world():
+    n = torch.cuda.device_count()
+    return 4 if n >= 4 else 2
+
+
+@pytest.mark.parametrize("transport", ["nccl", "auto"])
+def test_ep_layer_matches_single_gpu(transport):
+    res = _spawn_gpu("gpu_ep_layer", _world(), transport)
+    for r, out in res.items():
+        for k, v in out.items():
+            tol = 6e-2 if k.startswith("dgate") else 3e-2
+            assert v < tol, (r, k, v, out)
+
+
+@pytest.mark.parametrize("transport", ["nccl", "auto"])
+def test_trainer_multi_gpu(transport):
+    res = _spawn_gpu("gpu_trainer", _world(), transport, 8)
+    for r, out in res.items():
+        assert all(math.isfinite(l) for l in out["losses"]) and out["losses"][-1] < out["losses"][0]
+        assert out["sync"] == 0.0 and out["ep"] == _world()

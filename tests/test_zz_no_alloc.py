@@ -55,7 +55,7 @@ def test_noalloc_plan_matches_regular_entry_point(N, K, E, cap):
         want = _outputs(N * K, E, cap_rows)
         scratch = torch.empty(ext.moe_plan_scratch_words(N * K, E, K, bool(per_k)), device="cuda", dtype=torch.int32)
         ext.moe_plan(idx, K, E, 0, E, bool(per_k), cap, want["slot_row"], want["row_slot"], want["group_offsets"],
-                     want["tile_group"], want["num_m_tiles"], want["counts_kept"], scratch)
+                     want["tile_group"], want["num_m_tiles"], want["counts_kept"], scratch, None)
         got = _outputs(N * K, E, cap_rows)
         err = ctypes.c_int(0)
         rc = lib.cmoe_moe_plan_noalloc(idx.data_ptr(), N * K, K, E, 0, E, per_k, cap, cap_rows,
