@@ -6,6 +6,7 @@
 
 #include <optional>
 #include <string>
+#include <vector>
 
 #include "gemm.cuh"
 #include "ops.cuh"
@@ -31,7 +32,7 @@ T* opt_ptr(const OptTensor& t) {
 }
 
 // ------------------------------------------------------------------------------------------ GEMM
-void gemm(const Tensor& A, const Tensor& B, Tensor& D, int64_t mode, int64_t epilogue, int64_t M, int64_t N, int64_t K,
+cmoe::GemmArgs gemm_args(const Tensor& A, const Tensor& B, Tensor& D, int64_t mode, int64_t epilogue, int64_t M, int64_t N, int64_t K,
           bool a_mn, bool b_mn, int64_t groups, int64_t b_group_rows, int64_t split_n, const OptTensor& tile_group,
           const OptTensor& num_m_tiles, int64_t max_m_tiles, const OptTensor& group_offsets, int64_t d_group_stride,
           bool accumulate, const OptTensor& aux_in, const OptTensor& aux_out, const OptTensor& ready_flags,
@@ -41,7 +42,6 @@ void gemm(const Tensor& A, const Tensor& B, Tensor& D, int64_t mode, int64_t epi
   check_bf16_2d(B, "B");
   TORCH_CHECK(D.is_cuda() && D.dim() >= 2 && D.stride(-1) == 1, "D must be CUDA with unit inner stride");
   TORCH_CHECK(D.scalar_type() == at::kBFloat16 || D.scalar_type() == at::kFloat, "D must be bf16 or fp32");
-  const c10::cuda::CUDAGuard guard(A.device());
   cmoe::GemmArgs g;
   g.A = A.data_ptr();
   g.a_rows = A.size(0);
@@ -84,7 +84,45 @@ void gemm(const Tensor& A, const Tensor& B, Tensor& D, int64_t mode, int64_t epi
   g.ready_target = static_cast<uint32_t>(ready_target);
   g.status = opt_ptr<int>(status);
   g.timeout_ns = static_cast<unsigned long long>(timeout_ns);
+  return g;
+}
+
+void gemm(const Tensor& A, const Tensor& B, Tensor& D, int64_t mode, int64_t epilogue, int64_t M, int64_t N, int64_t K,
+          bool a_mn, bool b_mn, int64_t groups, int64_t b_group_rows, int64_t split_n, const OptTensor& tile_group,
+          const OptTensor& num_m_tiles, int64_t max_m_tiles, const OptTensor& group_offsets, int64_t d_group_stride,
+          bool accumulate, const OptTensor& aux_in, const OptTensor& aux_out, const OptTensor& ready_flags,
+          int64_t ready_stride, int64_t ready_count, int64_t ready_target, const OptTensor& status,
+          int64_t timeout_ns) {
+  const c10::cuda::CUDAGuard guard(A.device());
+  cmoe::GemmArgs g = gemm_args(A, B, D, mode, epilogue, M, N, K, a_mn, b_mn, groups, b_group_rows, split_n, tile_group,
+                               num_m_tiles, max_m_tiles, group_offsets, d_group_stride, accumulate, aux_in, aux_out,
+                               ready_flags, ready_stride, ready_count, ready_target, status, timeout_ns);
   check_cuda(cmoe::launch_gemm(g, cur_stream()), "launch_gemm");
+}
+
+// grouped-M GEMM whose A rows are pulled from peer buffers by the kernel itself (fused expert-parallel dispatch)
+void gemm_pull(const Tensor& A, const Tensor& B, Tensor& D, int64_t epilogue, int64_t N, int64_t K, bool b_mn,
+               int64_t groups, int64_t b_group_rows, int64_t split_n, const Tensor& tile_group,
+               const Tensor& num_m_tiles, int64_t max_m_tiles, const OptTensor& aux_in, const OptTensor& aux_out,
+               const Tensor& row_slot, const std::vector<int64_t>& src_ptrs, int64_t slots_per_src, int64_t pull_K,
+               const OptTensor& slot_scale, int64_t ld_src, Tensor& tile_ready, int64_t epoch, const OptTensor& status,
+               int64_t timeout_ns) {
+  const c10::cuda::CUDAGuard guard(A.device());
+  cmoe::GemmArgs g = gemm_args(A, B, D, cmoe::GEMM_GROUPED_M, epilogue, 0, N, K, false, b_mn, groups, b_group_rows,
+                               split_n, tile_group, num_m_tiles, max_m_tiles, std::nullopt, 0, false, aux_in, aux_out,
+                               std::nullopt, 0, 0, 0, status, timeout_ns);
+  TORCH_CHECK(!src_ptrs.empty() && src_ptrs.size() <= static_cast<size_t>(cmoe::kMaxPeers), "peer table size");
+  for (size_t i = 0; i < src_ptrs.size(); ++i) g.pull_src.ptr[i] = reinterpret_cast<void*>(src_ptrs[i]);
+  TORCH_CHECK(row_slot.scalar_type() == at::kInt && row_slot.numel() >= A.size(0));
+  TORCH_CHECK(tile_ready.scalar_type() == at::kInt && tile_ready.numel() >= max_m_tiles);
+  g.pull_row_slot = row_slot.data_ptr<int>();
+  g.pull_slots_per_src = slots_per_src;
+  g.pull_K = static_cast<int>(pull_K);
+  g.pull_slot_scale = slot_scale.has_value() ? slot_scale->data_ptr<float>() : nullptr;
+  g.pull_ld_src = ld_src;
+  g.tile_ready = reinterpret_cast<uint32_t*>(tile_ready.data_ptr<int>());
+  g.pull_epoch = static_cast<uint32_t>(epoch);
+  check_cuda(cmoe::launch_gemm(g, cur_stream()), "launch_gemm(pull)");
 }
 
 // ------------------------------------------------------------------------------------------ router
@@ -298,6 +336,7 @@ void register_ep(pybind11::module_& m);
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "sm_100a kernels of the composed MoE engine";
   m.def("gemm", &gemm);
+  m.def("gemm_pull", &gemm_pull);
   m.def("router_fwd", &router_fwd);
   m.def("router_bwd", &router_bwd);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);

@@ -33,6 +33,7 @@ constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int CHUNK_BYTES = 64 * BK * 2;  // one 64 x 64 bf16 box (MN-major operands) = 8 KiB
 constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS_PULL = 320;  // + four row-pull warps (fused expert-parallel dispatch)
 constexpr int TMEM_COLS = 2 * BN;  // 512: two accumulators
 constexpr int GROUP_M_SWIZZLE = 8;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
@@ -57,6 +58,18 @@ struct KParams {
   int* status;
   unsigned long long timeout_ns;
   int n_cols_per_tile;  // output columns covered by one tile (256, or 128 with the SwiGLU forward)
+  // fused dispatch: rows of A are pulled from peers by the extra warps
+  const int* pull_row_slot;
+  PeerTable pull_src;
+  long long pull_slots_per_src;
+  int pull_K;
+  const float* pull_slot_scale;
+  long long pull_ld_src;
+  __nv_bfloat16* pull_dst;
+  long long pull_ld_dst;
+  int pull_cols;
+  uint32_t* tile_ready;
+  uint32_t pull_epoch;
 };
 
 struct Tile {
@@ -190,7 +203,7 @@ __device__ __forceinline__ void load_row_chunk_bf16(const __nv_bfloat16* src, fl
 }
 
 template <int EPI>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS_PULL, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const KParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -255,6 +268,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (p.ready_flags != nullptr) {
           const uint32_t* f = p.ready_flags + (long long)ti.group * p.ready_stride;
           for (int s = 0; s < p.ready_count; ++s) flag_wait_ge(f + s, p.ready_target, wc);
+        }
+        if (p.pull_row_slot != nullptr) {
+          // the rows of this tile are written by the pull warps of some CTA of this launch
+          flag_wait_ge(p.tile_ready + ti.m0 / BM, p.pull_epoch, wc);
+          asm volatile("fence.proxy.async.global;" ::: "memory");  // generic-proxy writes -> TMA reads
         }
         for (int kb = 0; kb < ti.k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, wc, ST_TIMEOUT_SMEM_EMPTY)) break;
@@ -323,6 +341,56 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (*abort_flag) break;
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------------ row-pull warps (fused dispatch)
+    if (p.pull_row_slot != nullptr) {
+      const int pw = warp - 6;  // 0..3: each warp brings in 32 of the 128 rows of a tile
+      for (int mt = blockIdx.x; mt < m_tiles; mt += gridDim.x) {
+        if (p.tile_group[mt] >= 0) {
+          for (int i = 0; i < 32; ++i) {
+            const long long r = static_cast<long long>(mt) * BM + pw * 32 + i;
+            const int slot = p.pull_row_slot[r];
+            __nv_bfloat16* o = p.pull_dst + r * p.pull_ld_dst;
+            if (slot < 0) {
+              for (int c = lane * 8; c < p.pull_cols; c += 256)
+                *reinterpret_cast<uint4*>(o + c) = make_uint4(0u, 0u, 0u, 0u);
+              continue;
+            }
+            const int src_rank = static_cast<int>(slot / p.pull_slots_per_src);
+            const long long tok = (slot - src_rank * p.pull_slots_per_src) / p.pull_K;
+            const __nv_bfloat16* s =
+                reinterpret_cast<const __nv_bfloat16*>(p.pull_src.ptr[src_rank]) + tok * p.pull_ld_src;
+            const float sc = p.pull_slot_scale ? p.pull_slot_scale[slot] : 1.f;
+            for (int c0 = lane * 8; c0 < p.pull_cols; c0 += 1024) {
+              uint4 v[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (c0 + j * 256 < p.pull_cols) v[j] = *reinterpret_cast<const uint4*>(s + c0 + j * 256);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (c0 + j * 256 < p.pull_cols) {
+                  if (p.pull_slot_scale) {
+                    const float2 a = unpack_bf16x2(v[j].x), b = unpack_bf16x2(v[j].y), c = unpack_bf16x2(v[j].z),
+                                 d = unpack_bf16x2(v[j].w);
+                    v[j].x = pack_bf16x2(a.x * sc, a.y * sc);
+                    v[j].y = pack_bf16x2(b.x * sc, b.y * sc);
+                    v[j].z = pack_bf16x2(c.x * sc, c.y * sc);
+                    v[j].w = pack_bf16x2(d.x * sc, d.y * sc);
+                  }
+                  *reinterpret_cast<uint4*>(o + c0 + j * 256) = v[j];
+                }
+              }
+            }
+          }
+        }
+        __threadfence();
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (threadIdx.x == 6 * 32) {
+          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.tile_ready + mt), "r"(p.pull_epoch) : "memory");
+        }
       }
     }
   } else {
@@ -540,7 +608,8 @@ cudaError_t launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  gemm_kernel<EPI><<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, kp);
+  const int threads = kp.pull_row_slot != nullptr ? GEMM_THREADS_PULL : GEMM_THREADS;
+  gemm_kernel<EPI><<<grid, threads, SMEM_BYTES, stream>>>(tmA, tmB, kp);
   return cudaGetLastError();
 }
 
@@ -580,6 +649,20 @@ cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   kp.ld_aux_in = a.ld_aux_in;
   kp.aux_out = reinterpret_cast<__nv_bfloat16*>(a.aux_out);
   kp.ld_aux_out = a.ld_aux_out;
+  kp.pull_row_slot = a.pull_row_slot;
+  kp.pull_src = a.pull_src;
+  kp.pull_slots_per_src = a.pull_slots_per_src;
+  kp.pull_K = a.pull_K;
+  kp.pull_slot_scale = a.pull_slot_scale;
+  kp.pull_ld_src = a.pull_ld_src;
+  kp.pull_dst = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(a.A));
+  kp.pull_ld_dst = a.a_ld;
+  kp.pull_cols = static_cast<int>(a.a_cols);
+  kp.tile_ready = a.tile_ready;
+  kp.pull_epoch = a.pull_epoch;
+  if (a.pull_row_slot != nullptr &&
+      (a.mode != GEMM_GROUPED_M || a.a_mn || a.tile_ready == nullptr || a.a_cols % 8 != 0))
+    return cudaErrorInvalidValue;
   kp.ready_flags = a.ready_flags;
   kp.ready_stride = a.ready_stride;
   kp.ready_count = a.ready_count;

@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "ep.cuh"
+
 namespace cmoe {
 
 enum GemmMode : int {
@@ -66,6 +68,22 @@ struct GemmArgs {
   int ready_stride = 0;
   int ready_count = 0;
   uint32_t ready_target = 0;
+
+  // Fused expert-parallel dispatch (grouped-M only).  When pull_row_slot is set, four extra warps per CTA fill
+  // the rows of A themselves before the tiles that need them run: row r of A is the token row
+  // (slot % pull_slots_per_src) / pull_K of rank slot / pull_slots_per_src (slot = pull_row_slot[r]), read with
+  // plain loads from that rank's buffer in pull_src (peer memory over NVLink, or local), times pull_slot_scale[slot]
+  // if given; padding rows are zero filled.  tile_ready[m] (uint32, this GPU's memory) is set to pull_epoch when
+  // 128-row tile m is complete, and the TMA producer of every tile waits (bounded) for it.  The transfer of later
+  // tiles overlaps the MMAs of earlier ones.
+  const int* pull_row_slot = nullptr;
+  PeerTable pull_src = {};
+  long long pull_slots_per_src = 0;
+  int pull_K = 1;
+  const float* pull_slot_scale = nullptr;
+  long long pull_ld_src = 0;
+  uint32_t* tile_ready = nullptr;
+  uint32_t pull_epoch = 0;
 
   int* status = nullptr;  // device int, set to a StatusCode when a wait ran out
   unsigned long long timeout_ns = 0;  // 0: default

@@ -169,10 +169,11 @@ class MoEPlan:
     __slots__ = ("n_tokens", "K", "n_local", "cap_rows", "slot_row", "row_slot", "group_offsets", "tile_group",
                  "num_m_tiles", "counts_kept", "max_m_tiles")
 
-    def __init__(self, n_tokens: int, K: int, n_local: int, cap_rows: int, device: torch.device):
+    def __init__(self, n_tokens: int, K: int, n_local: int, cap_rows: int, device: torch.device,
+                 slot_row: Optional[torch.Tensor] = None):
         self.n_tokens, self.K, self.n_local, self.cap_rows = n_tokens, K, n_local, cap_rows
         i32 = dict(device=device, dtype=torch.int32)
-        self.slot_row = torch.empty(n_tokens * K, **i32)
+        self.slot_row = slot_row if slot_row is not None else torch.empty(n_tokens * K, **i32)
         self.row_slot = torch.empty(cap_rows, **i32)
         self.group_offsets = torch.empty(n_local + 1, **i32)
         self.tile_group = torch.empty(cap_rows // 128, **i32)
@@ -199,14 +200,15 @@ def _scratch_i32(device: torch.device, words: int) -> torch.Tensor:
 
 
 def moe_plan(topk_idx: torch.Tensor, num_experts: int, expert_lo: int = 0, n_local: Optional[int] = None,
-             capacity: int = 0, cap_rows: Optional[int] = None) -> MoEPlan:
+             capacity: int = 0, cap_rows: Optional[int] = None, slot_row_out: Optional[torch.Tensor] = None
+             ) -> MoEPlan:
     """Build the row plan for ``topk_idx`` [N, K] (int32).  ``capacity`` > 0 enables per-(expert, k) FCFS dropping."""
     ext = _ext.ext()
     N, K = topk_idx.shape
     n_local = num_experts if n_local is None else n_local
     if cap_rows is None:
         cap_rows = plan_capacity_rows(N * K, n_local)
-    plan = MoEPlan(N, K, n_local, cap_rows, topk_idx.device)
+    plan = MoEPlan(N, K, n_local, cap_rows, topk_idx.device, slot_row=slot_row_out)
     per_k = capacity > 0
     words = ext.moe_plan_scratch_words(N * K, n_local, K, per_k)
     ext.moe_plan(topk_idx, K, num_experts, expert_lo, n_local, per_k, capacity, plan.slot_row, plan.row_slot,
@@ -235,3 +237,30 @@ def combine_bwd_w(rows: torch.Tensor, plan: MoEPlan, dy: torch.Tensor) -> torch.
     dw = torch.empty(plan.n_tokens, plan.K, device=rows.device, dtype=torch.float32)
     _ext.ext().combine_bwd_w(rows, plan.slot_row, dy, dw, plan.K)
     return dw
+
+
+_tile_ready: Dict[int, torch.Tensor] = {}
+_pull_epoch: Dict[int, int] = {}
+
+
+def gemm_pull(A: torch.Tensor, B: torch.Tensor, D: torch.Tensor, plan: MoEPlan, *, epilogue: int, N: int, K: int,
+              groups: int, b_group_rows: int, src_ptrs, slots_per_src: int, pull_K: int, ld_src: int,
+              b_mn: bool = False, split_n: int = 0, aux_in: Optional[torch.Tensor] = None,
+              aux_out: Optional[torch.Tensor] = None, slot_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Grouped GEMM whose A rows (``plan.row_slot`` -> token rows of the ranks in ``src_ptrs``) are brought in by
+    extra warps of the same kernel, tile by tile (fused expert-parallel dispatch).  ``A`` is the destination
+    buffer of the pulled rows as well as the GEMM operand."""
+    idx = A.device.index or 0
+    ready = _tile_ready.get(idx)
+    if ready is None or ready.numel() < plan.max_m_tiles:
+        ready = torch.zeros(max(plan.max_m_tiles, 16384), device=A.device, dtype=torch.int32)
+        _tile_ready[idx] = ready
+        _pull_epoch[idx] = 0
+    _pull_epoch[idx] = (_pull_epoch[idx] + 1) % (1 << 30)
+    if _pull_epoch[idx] == 0:  # wrapped: start over with clean flags
+        ready.zero_()
+        _pull_epoch[idx] = 1
+    _ext.ext().gemm_pull(A, B, D, epilogue, N, K, b_mn, groups, b_group_rows, split_n, plan.tile_group,
+                         plan.num_m_tiles, plan.max_m_tiles, aux_in, aux_out, plan.row_slot, list(src_ptrs),
+                         slots_per_src, pull_K, slot_scale, ld_src, ready, _pull_epoch[idx], status_word(A.device), 0)
+    return D

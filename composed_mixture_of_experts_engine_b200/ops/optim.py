@@ -36,7 +36,7 @@ class _FlatGroup:
     """One flat bf16 parameter buffer + gradient buffer + (sharded) fp32 master / moments."""
 
     def __init__(self, name: str, params: List[nn.Parameter], grad_dtype: torch.dtype, weight_decay_mask: List[bool],
-                 shard_group=None):
+                 shard_group=None, topology=None, axis: str = "dp"):
         self.name, self.params = name, params
         dev = params[0].device
         self.shard_group = shard_group
@@ -48,8 +48,16 @@ class _FlatGroup:
             total += _align(p.numel(), 8)
         self.numel = _align(total, 8 * 16 * self.shard_world)
         self.offsets = offs
-        self.flat_p = torch.zeros(self.numel, device=dev, dtype=torch.bfloat16)
-        self.flat_g = torch.zeros(self.numel, device=dev, dtype=grad_dtype)
+        self.peer = None
+        if self.shard_world > 1:
+            from ..parallel import symm_dp
+
+            self.peer = symm_dp.make_peer(topology, axis, name, self.numel, grad_dtype)
+        if self.peer is not None:  # buffers in symmetric memory: peers reduce / push straight from them
+            self.flat_p, self.flat_g = self.peer.flat_p, self.peer.flat_g
+        else:
+            self.flat_p = torch.zeros(self.numel, device=dev, dtype=torch.bfloat16)
+            self.flat_g = torch.zeros(self.numel, device=dev, dtype=grad_dtype)
         self.decay = weight_decay_mask
         for p, off in zip(params, offs):
             n = p.numel()
@@ -224,10 +232,11 @@ def build_optimizer(model: nn.Module, lr: float, weight_decay: float = 0.1, beta
     groups: List[_FlatGroup] = []
     if dense:
         groups.append(_FlatGroup("dense", [p for _, p in dense], torch.bfloat16,
-                                 [not _no_decay(n, p) for n, p in dense], shard_group=dp_group))
+                                 [not _no_decay(n, p) for n, p in dense], shard_group=dp_group, topology=topology,
+                                 axis="dp"))
     if expert:
         groups.append(_FlatGroup("expert", [p for _, p in expert], torch.float32, [True] * len(expert),
-                                 shard_group=expert_dp_group))
+                                 shard_group=expert_dp_group, topology=topology, axis="edp"))
         # an expert's gradient already sums the contributions of the `ep` ranks whose tokens it served; the
         # objective is the mean over all data-parallel ranks, so 1/ep is still missing after the edp average
         if topology is not None and dist.is_initialized() and topology.ep_size > 1:

@@ -23,7 +23,10 @@ _DISABLED_REASON: Optional[str] = None
 
 
 def _axis_group(topo: ParallelTopology, axis: str):
-    return {"ep": ep_process_group, "tp": tp_process_group, "dp": dp_process_group}[axis](topo)
+    from .mesh import edp_process_group
+
+    return {"ep": ep_process_group, "tp": tp_process_group, "dp": dp_process_group,
+            "edp": edp_process_group}[axis](topo)
 
 
 def enabled_for(topo: Optional[ParallelTopology], axis: str) -> bool:
@@ -32,7 +35,8 @@ def enabled_for(topo: Optional[ParallelTopology], axis: str) -> bool:
         return False
     if os.environ.get("CMOE_DISABLE_PEER_KERNELS", "0") == "1" or _DISABLED_REASON is not None:
         return False
-    size = {"ep": topo.ep_size, "tp": topo.tp_size, "dp": topo.dp_size}[axis]
+    size = {"ep": topo.ep_size, "tp": topo.tp_size, "dp": topo.dp_size,
+            "edp": len(topo.axis_ranks("edp"))}[axis]
     if size <= 1 or topo.device.type != "cuda":
         return False
     if dist.get_backend() != "nccl":
@@ -75,6 +79,14 @@ class SymmGroup:
         if buf is not None and buf.local.numel() >= nbytes:
             return buf
         nbytes = (nbytes + 4095) // 4096 * 4096
+        try:  # older torch versions want the group registered first; newer ones ignore / deprecate the call
+            import warnings
+
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore")
+                symm_mem.enable_symm_mem_for_group(self.group.group_name)
+        except Exception:
+            pass
         t = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
         handle = symm_mem.rendezvous(t, self.group)
         buf = SymmBuffer(t, handle, self.world)

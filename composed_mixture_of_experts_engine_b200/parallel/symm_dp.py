@@ -47,3 +47,55 @@ def all_gather_params(g) -> None:
         parts = [torch.empty_like(shard) for _ in range(g.shard_world)]
         dist.all_gather(parts, shard.clone(), group=g.shard_group)
         g.flat_p.copy_(torch.cat(parts))
+
+
+class DPPeer:
+    """Peer-memory transport of one flat parameter group: its gradient and parameter buffers live in symmetric
+    memory of the shard group, so that the reduce-scatter is one pull kernel (fp32 accumulation, cast and 1/world
+    scale fused) and the parameter all-gather is one push kernel."""
+
+    def __init__(self, topo, axis: str, name: str, numel: int, grad_dtype: torch.dtype):
+        from ..ops import _ext, kernels
+
+        self.sg = symm.group_for(topo, axis)
+        self.rank, self.world = self.sg.rank, self.sg.world
+        gbytes = numel * (2 if grad_dtype == torch.bfloat16 else 4)
+        self.pbuf = self.sg.alloc(f"dp.{name}.params.{numel}", numel * 2)
+        self.gbuf = self.sg.alloc(f"dp.{name}.grads.{numel}", gbytes)
+        self.flat_p = self.pbuf.view(torch.bfloat16, numel)
+        self.flat_g = self.gbuf.view(grad_dtype, numel)
+        self.flat_p.zero_()
+        self.flat_g.zero_()
+        self.p_ptrs = [int(p) for p in self.pbuf.handle.buffer_ptrs]
+        self.g_ptrs = [int(p) for p in self.gbuf.handle.buffer_ptrs]
+        self.flag_ptrs = [int(p) for p in self.sg.flags.handle.buffer_ptrs]
+        self.device = topo.device
+        self._ext, self._kernels = _ext, kernels
+
+    def barrier(self) -> None:
+        self.sg.epoch += 1
+        self._ext.ext().peer_barrier(self.flag_ptrs, self.rank, self.sg.epoch, self._kernels.status_word(self.device), 0)
+
+    def reduce_scatter(self, g, out: torch.Tensor) -> torch.Tensor:
+        self.barrier()  # every rank has finished writing its gradients
+        self._ext.ext().reduce_scatter_cast(self.g_ptrs, g.flat_g.dtype == torch.bfloat16, g.shard_lo, g.shard_numel,
+                                            1.0 / self.world, out)
+        self.barrier()  # every rank has finished reading: the gradient buffers may be cleared
+        return out
+
+    def all_gather(self, g) -> None:
+        self._ext.ext().push_shard(self.p_ptrs, self.rank, g.shard_lo, g.shard_numel, g.flat_p)
+        self.barrier()  # all shards have landed everywhere before the next forward reads the parameters
+
+
+def make_peer(topo, axis: str, name: str, numel: int, grad_dtype: torch.dtype):
+    """A :class:`DPPeer` when the peer-memory path is usable along ``axis``, else ``None`` (library collectives)."""
+    import os
+
+    if topo is None or os.environ.get("CMOE_DP_TRANSPORT", "auto") == "nccl":
+        return None
+    from . import symm_peer
+
+    if not symm_peer.available(topo, axis):
+        return None
+    return DPPeer(topo, axis, name, numel, grad_dtype)

@@ -1,7 +1,225 @@
-"""Peer-memory (NVLink P2P) transport for the expert-parallel MoE: placeholder until the kernels are bound."""
+"""Peer-memory (NVLink P2P) transport of the expert-parallel MoE.
+
+Per layer call, on one stream, with no host round trip:
+
+    forward   publish x / idx / w in symmetric buffers            (local copies)
+              barrier
+              pull every rank's idx and w (a few hundred KB)       peer_allgather
+              row plan of the local experts over all ranks' slots  moe_plan  (slot -> row table lands in symmetric memory)
+              pull the rows that route here, expert-sorted         gather_rows_peer   <- the dispatch, P2P loads over NVLink
+              grouped SwiGLU GEMMs (tcgen05), yp into a symmetric buffer
+              barrier
+              y[t] = sum_k w * yp[owner][row]                      combine_rows_peer  <- the combine, P2P loads
+    backward  publish dy; barrier; d(gate) by dot products against the owners' yp rows; pull dy rows (scaled by
+              the gate weights); grouped backward GEMMs, dxp into a symmetric buffer; barrier; dx[t] = sum_k dxp
+
+Nothing is gathered that is not needed, nothing is reduced in bf16, and no buffer is materialised twice (the
+library transport all-gathers x and reduce-scatters a [ep*T, H] partial result).  Barriers are flag words in
+symmetric memory with a bounded wait; a peer that never arrives turns into a ``KernelTimeoutError`` at the next
+``check_status``, not a hang.
+
+Buffer reuse: x / idx / w / dy / dxp staging buffers are shared by all layers (the barrier that follows their
+last remote read orders it before the next local write); yp and the slot->row table live per layer because the
+backward pass of the layer reads them from the peers again.
+"""
 
 from __future__ import annotations
 
+import os
+from typing import Dict, List, Optional
 
-def available(topology, axis: str) -> bool:
-    return False
+import torch
+import torch.distributed as dist
+
+from ..ops import _ext
+from ..ops import functional as OF
+from ..ops import kernels
+from . import symm
+from .mesh import ParallelTopology
+
+_FAILED: Optional[str] = None
+
+
+def available(topology: Optional[ParallelTopology], axis: str) -> bool:
+    if _FAILED is not None or not symm.enabled_for(topology, axis):
+        return False
+    if topology.pp_size > 1:
+        return False  # several microbatches of one layer are in flight under 1F1B; per-layer buffers assume one
+    size = {"ep": topology.ep_size, "tp": topology.tp_size, "dp": topology.dp_size,
+            "edp": len(topology.axis_ranks("edp"))}[axis]
+    return 1 < size <= 16
+
+
+def _fused() -> bool:
+    """Dispatch inside the grouped GEMM (default) or as a separate pull kernel (``CMOE_EP_FUSED=0``)."""
+    return os.environ.get("CMOE_EP_FUSED", "1") != "0"
+
+
+class _EPContext:
+    """Symmetric buffers, flag words and the barrier epoch of one expert-parallel group."""
+
+    def __init__(self, topo: ParallelTopology):
+        self.topo = topo
+        self.group = symm.group_for(topo, "ep")
+        self.rank, self.world = self.group.rank, self.group.world
+        self.flags = self.group.flags
+        self.flag_ptrs = [int(p) for p in self.flags.handle.buffer_ptrs]
+        self.epoch = 0
+        self._shared: Dict[str, symm.SymmBuffer] = {}
+        self._layer: Dict[tuple, symm.SymmBuffer] = {}
+        self.expert_rank: Dict[int, torch.Tensor] = {}
+
+    def barrier(self) -> None:
+        self.epoch += 1
+        _ext.ext().peer_barrier(self.flag_ptrs, self.rank, self.epoch, kernels.status_word(self.topo.device), 0)
+
+    def shared(self, name: str, nbytes: int) -> symm.SymmBuffer:
+        buf = self._shared.get(name)
+        if buf is None or buf.local.numel() < nbytes:
+            buf = self.group.alloc(f"ep.shared.{name}.{nbytes}", nbytes)
+            self._shared[name] = buf
+        return buf
+
+    def per_layer(self, layer_key: int, name: str, nbytes: int) -> symm.SymmBuffer:
+        key = (layer_key, name)
+        buf = self._layer.get(key)
+        if buf is None or buf.local.numel() < nbytes:
+            buf = self.group.alloc(f"ep.layer{layer_key}.{name}.{nbytes}", nbytes)
+            self._layer[key] = buf
+        return buf
+
+    def expert_rank_table(self, num_experts: int) -> torch.Tensor:
+        t = self.expert_rank.get(num_experts)
+        if t is None:
+            owner = []
+            for r in range(self.world):
+                owner += [r] * len(self.topo.experts_on_rank(num_experts, r))
+            t = torch.tensor(owner, dtype=torch.int32, device=self.topo.device)
+            self.expert_rank[num_experts] = t
+        return t
+
+
+_CONTEXTS: Dict[tuple, _EPContext] = {}
+_LAYER_KEYS: Dict[int, int] = {}
+
+
+def _context(topo: ParallelTopology) -> _EPContext:
+    key = tuple(topo.axis_ranks("ep"))
+    ctx = _CONTEXTS.get(key)
+    if ctx is None:
+        ctx = _EPContext(topo)
+        _CONTEXTS[key] = ctx
+    return ctx
+
+
+def _layer_key(layer) -> int:
+    """Creation-ordered index of the layer (the same on every rank, which the collective allocations need)."""
+    k = _LAYER_KEYS.get(id(layer))
+    if k is None:
+        k = len(_LAYER_KEYS)
+        _LAYER_KEYS[id(layer)] = k
+    return k
+
+
+def _ptrs(buf: symm.SymmBuffer) -> List[int]:
+    return [int(p) for p in buf.handle.buffer_ptrs]
+
+
+class _EPMoEPeer(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gate_w32, idx32, w13, w2, pc: _EPContext, lkey: int, expert_lo, num_experts, capacity,
+                holder):
+        ext = _ext.ext()
+        T, H = x.shape
+        K = idx32.shape[1]
+        ep, n_local = pc.world, w13.shape[0]
+        dev = x.device
+        cap_rows = kernels.ep_buffer_rows(T * K, n_local, ep * T * K)
+
+        xs = pc.shared("x", T * H * 2)
+        ids = pc.shared("idx", T * K * 4)
+        ws = pc.shared("w", T * K * 4)
+        xs.view(torch.bfloat16, T * H).view(T, H).copy_(x)
+        ids.view(torch.int32, T * K).copy_(idx32.reshape(-1))
+        ws.view(torch.float32, T * K).copy_(gate_w32.reshape(-1))
+        pc.barrier()
+
+        idx_all = torch.empty(ep * T, K, device=dev, dtype=torch.int32)
+        w_all = torch.empty(ep * T, K, device=dev, dtype=torch.float32)
+        ext.peer_allgather(_ptrs(ids), T * K * 4, idx_all)
+        ext.peer_allgather(_ptrs(ws), T * K * 4, w_all)
+        srow = pc.per_layer(lkey, "slot_row", ep * T * K * 4)
+        plan = kernels.moe_plan(idx_all, num_experts, expert_lo=expert_lo, n_local=n_local, capacity=capacity * ep,
+                                cap_rows=cap_rows, slot_row_out=srow.view(torch.int32, ep * T * K))
+        xp = torch.empty(cap_rows, H, device=dev, dtype=torch.bfloat16)
+        yps = pc.per_layer(lkey, "yp", cap_rows * H * 2)
+        yp = yps.view(torch.bfloat16, cap_rows * H).view(cap_rows, H)
+        if _fused():
+            # the dispatch runs inside the first grouped GEMM: rows stream in over NVLink tile by tile
+            pull = dict(src_ptrs=_ptrs(xs), slots_per_src=T * K, pull_K=K, ld_src=H)
+            hact, gu, _ = OF.grouped_swiglu_forward(xp, w13, w2, plan, yp_out=yp, pull=pull)
+        else:
+            ext.gather_rows_peer(_ptrs(xs), T * K, K, plan.row_slot, None, xp, plan.num_m_tiles, H)
+            hact, gu, _ = OF.grouped_swiglu_forward(xp, w13, w2, plan, yp_out=yp)
+        pc.barrier()
+
+        y = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
+        erank = pc.expert_rank_table(num_experts)
+        ext.combine_rows_peer(_ptrs(yps), _ptrs(srow), idx32, erank, gate_w32, y, K, pc.rank * T * K, H)
+
+        ctx.save_for_backward(xp, hact, gu, w_all, w13, w2, idx32, gate_w32)
+        ctx.plan, ctx.pc, ctx.lkey, ctx.cap_rows = plan, pc, lkey, cap_rows
+        ctx.num_experts = num_experts
+        if holder is not None:
+            holder["plan"] = plan
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        ext = _ext.ext()
+        xp, hact, gu, w_all, w13, w2, idx32, gate_w32 = ctx.saved_tensors
+        plan, pc, lkey, cap_rows = ctx.plan, ctx.pc, ctx.lkey, ctx.cap_rows
+        T, K = idx32.shape
+        H = xp.shape[1]
+        dev = xp.device
+        dy = dy.contiguous()
+        dys = pc.shared("dy", T * H * 2)
+        dys.view(torch.bfloat16, T * H).view(T, H).copy_(dy)
+        pc.barrier()
+
+        yps = pc.per_layer(lkey, "yp", cap_rows * H * 2)
+        srow = pc.per_layer(lkey, "slot_row", pc.world * T * K * 4)
+        erank = pc.expert_rank_table(ctx.num_experts)
+        d_gate = None
+        if ctx.needs_input_grad[1]:
+            d_gate = torch.empty(T, K, device=dev, dtype=torch.float32)
+            ext.combine_bwd_w_peer(_ptrs(yps), _ptrs(srow), idx32, erank, dy, d_gate, K, pc.rank * T * K, H)
+        dyp = torch.empty(cap_rows, H, device=dev, dtype=torch.bfloat16)
+        dxs = pc.shared("dxp", cap_rows * H * 2)
+        dxp_buf = dxs.view(torch.bfloat16, cap_rows * H).view(cap_rows, H)
+        pull = None
+        if _fused():
+            pull = dict(src_ptrs=_ptrs(dys), slots_per_src=T * K, pull_K=K, ld_src=H, slot_scale=w_all.reshape(-1))
+        else:
+            ext.gather_rows_peer(_ptrs(dys), T * K, K, plan.row_slot, w_all.reshape(-1), dyp, plan.num_m_tiles, H)
+        dxp, dw13, dw2 = OF.grouped_swiglu_backward(dyp, xp, hact, gu, w13, w2, plan,
+                                                    need_dx=ctx.needs_input_grad[0], dxp_out=dxp_buf, pull=pull)
+        pc.barrier()
+        dx = None
+        if dxp is not None:
+            dx = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
+            ext.combine_rows_peer(_ptrs(dxs), _ptrs(srow), idx32, erank, None, dx, K, pc.rank * T * K, H)
+        return dx, d_gate, None, dw13, dw2, None, None, None, None, None, None
+
+
+def ep_moe(layer, flat: torch.Tensor, gate_w32: torch.Tensor, idx32: torch.Tensor, capacity: int, expert_lo: int
+           ) -> torch.Tensor:
+    global _FAILED
+    try:
+        pc = _context(layer.topology)
+    except Exception as exc:  # symmetric memory could not be set up: all ranks fall back together
+        _FAILED = f"{type(exc).__name__}: {exc}"
+        raise
+    with layer._timer.phase("experts"):
+        return _EPMoEPeer.apply(flat, gate_w32, idx32, layer.w13, layer.w2, pc, _layer_key(layer), expert_lo,
+                                layer.num_experts, capacity, layer._last_plan_holder)

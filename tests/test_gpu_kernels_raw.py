@@ -432,3 +432,38 @@ def test_moe_plan_gather_combine(ext, N, K, E, cap):
     ext.combine_bwd_w(xp, slot_row, dy, dw, K)
     ref_dw = (gathered * dy.float()[:, None, :]).sum(-1)
     assert torch.allclose(dw, ref_dw, atol=1e-2, rtol=1e-2)
+
+
+def test_gemm_with_fused_row_pull_matches_gather_then_gemm(ext, status):
+    """The grouped GEMM that pulls its own A rows (fused dispatch) vs gather_rows followed by the plain GEMM.
+    One GPU stands in for every rank: the "peer" table holds two local token buffers."""
+    from composed_mixture_of_experts_engine_b200.ops import kernels
+    from composed_mixture_of_experts_engine_b200.ops.kernels import EPI_SWIGLU_FWD as SWF
+
+    torch.manual_seed(12)
+    T, K, E, H, F = 1500, 4, 8, 512, 256
+    xs = [torch.randn(T, H, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+    x_all = torch.cat(xs)
+    idx = torch.stack([torch.randperm(E, device="cuda")[:K] for _ in range(2 * T)]).to(torch.int32)
+    plan = kernels.moe_plan(idx, E)
+    W13 = (torch.randn(E, 2 * F, H, device="cuda") / math.sqrt(H)).to(torch.bfloat16)
+    scale = torch.rand(2 * T * K, device="cuda")
+    for use_scale in (False, True):
+        sc = scale if use_scale else None
+        xp_ref = kernels.gather_rows(x_all, plan, slot_scale=sc)
+        h_ref = torch.empty(plan.cap_rows, F, device="cuda", dtype=torch.bfloat16)
+        gu_ref = torch.empty(plan.cap_rows, 2 * F, device="cuda", dtype=torch.bfloat16)
+        kernels.gemm(xp_ref, W13.view(-1, H), h_ref, mode=GROUPED_M, epilogue=SWF, N=F, K=H, groups=E,
+                     b_group_rows=2 * F, split_n=F, tile_group=plan.tile_group, num_m_tiles=plan.num_m_tiles,
+                     max_m_tiles=plan.max_m_tiles, aux_out=gu_ref)
+        xp = torch.full((plan.cap_rows, H), 9.0, device="cuda", dtype=torch.bfloat16)
+        h = torch.empty_like(h_ref)
+        gu = torch.empty_like(gu_ref)
+        kernels.gemm_pull(xp, W13.view(-1, H), h, plan, epilogue=SWF, N=F, K=H, groups=E, b_group_rows=2 * F,
+                          split_n=F, aux_out=gu, src_ptrs=[t.data_ptr() for t in xs], slots_per_src=T * K, pull_K=K,
+                          ld_src=H, slot_scale=sc)
+        torch.cuda.synchronize()
+        kernels.check_status(torch.device("cuda", 0))
+        n = int(plan.num_m_tiles) * 128
+        assert torch.equal(xp[:n], xp_ref[:n])
+        assert torch.equal(h[:n], h_ref[:n]) and torch.equal(gu[:n], gu_ref[:n])
