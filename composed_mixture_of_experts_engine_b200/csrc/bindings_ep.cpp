@@ -87,6 +87,15 @@ void reduce_scatter_cast(const std::vector<int64_t>& grads, bool grad_is_bf16, i
         "reduce_scatter_cast");
 }
 
+void reduce_rows_peer(const std::vector<int64_t>& rows, const OptTensor& row_map, Tensor& out, int64_t ld_rows) {
+  const c10::cuda::CUDAGuard guard(out.device());
+  TORCH_CHECK(out.dim() == 2 && out.stride(1) == 1 && out.scalar_type() == at::kBFloat16);
+  check(cmoe::launch_reduce_rows_peer(table(rows), static_cast<int>(rows.size()),
+                                      row_map.has_value() ? row_map->data_ptr<int>() : nullptr, out.data_ptr(),
+                                      out.size(0), static_cast<int>(out.size(1)), ld_rows, out.stride(0), stream()),
+        "reduce_rows_peer");
+}
+
 void push_shard(const std::vector<int64_t>& params, int64_t rank, int64_t shard_lo, int64_t n, const Tensor& anchor) {
   const c10::cuda::CUDAGuard guard(anchor.device());
   check(cmoe::launch_push_shard(table(params), static_cast<int>(rank), static_cast<int>(params.size()), shard_lo, n,
@@ -103,5 +112,6 @@ void register_ep(pybind11::module_& m) {
   m.def("combine_rows_peer", &combine_rows_peer);
   m.def("combine_bwd_w_peer", &combine_bwd_w_peer);
   m.def("reduce_scatter_cast", &reduce_scatter_cast);
+  m.def("reduce_rows_peer", &reduce_rows_peer);
   m.def("push_shard", &push_shard);
 }

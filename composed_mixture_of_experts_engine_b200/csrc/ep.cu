@@ -198,6 +198,30 @@ __global__ void __launch_bounds__(256) reduce_scatter_cast_kernel(const PeerTabl
   }
 }
 
+// one warp per output row
+__global__ void __launch_bounds__(256) reduce_rows_peer_kernel(const PeerTable rows, int world,
+                                                               const int* __restrict__ row_map,
+                                                               __nv_bfloat16* __restrict__ out, long long n_out, int H,
+                                                               long long ld_rows, long long ld_out) {
+  const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+  for (long long i = blockIdx.x * static_cast<long long>(warps) + (threadIdx.x >> 5); i < n_out;
+       i += static_cast<long long>(gridDim.x) * warps) {
+    const long long src_row = row_map ? row_map[i] : i;
+    for (int c = lane * 8; c < H; c += 256) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int r = 0; r < world; ++r) {
+        float f[8];
+        ld8(reinterpret_cast<const __nv_bfloat16*>(rows.ptr[r]) + src_row * ld_rows + c, f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += f[j];
+      }
+      st8(out + i * ld_out + c, acc);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256) push_shard_kernel(const PeerTable params, int rank, int world, long long shard_lo,
                                                          long long n_vec) {
   const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(params.ptr[rank]) + shard_lo);
@@ -276,6 +300,14 @@ cudaError_t launch_reduce_scatter_cast(const PeerTable& grads, int world, int gr
     reduce_scatter_cast_kernel<true><<<grid, 256, 0, stream>>>(grads, world, shard_lo, n, scale, out);
   else
     reduce_scatter_cast_kernel<false><<<grid, 256, 0, stream>>>(grads, world, shard_lo, n, scale, out);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_reduce_rows_peer(const PeerTable& rows, int world, const int* row_map, void* out, long long n_out,
+                                    int H, long long ld_rows, long long ld_out, cudaStream_t stream) {
+  if (world <= 0 || world > kMaxPeers || n_out <= 0 || H % 8 != 0) return cudaErrorInvalidValue;
+  reduce_rows_peer_kernel<<<blocks_for(n_out, 8, 148 * 8), 256, 0, stream>>>(
+      rows, world, row_map, reinterpret_cast<__nv_bfloat16*>(out), n_out, H, ld_rows, ld_out);
   return cudaGetLastError();
 }
 

@@ -46,6 +46,11 @@ cudaError_t launch_combine_bwd_w_peer(const PeerTable& rows, const PeerTable& sl
 cudaError_t launch_reduce_scatter_cast(const PeerTable& grads, int world, int grad_is_bf16, long long shard_lo,
                                        long long n, float scale, float* out, cudaStream_t stream);
 
+// out[i, :] = sum_r rows[r][row_map[i], :] for i < n_out (fp32 accumulation, bf16 out): the reduce-scatter of a
+// row-parallel linear, each rank pulling and summing the partial results of its own rows.
+cudaError_t launch_reduce_rows_peer(const PeerTable& rows, int world, const int* row_map, void* out, long long n_out,
+                                    int H, long long ld_rows, long long ld_out, cudaStream_t stream);
+
 // Parameter all-gather by push: copies n bf16 elements at offset shard_lo of the local flat buffer into the same
 // offset of every peer's flat buffer.
 cudaError_t launch_push_shard(const PeerTable& params, int rank, int world, long long shard_lo, long long n,

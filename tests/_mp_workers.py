@@ -269,3 +269,49 @@ def gpu_trainer(rank, world, transport, steps):
     dist.broadcast(ref, src=0)
     return {"losses": losses, "sync": float((w - ref).abs().max()), "ep": tr.topology.ep_size,
             "n_local": len(tr.model.blocks[0].moe.local_expert_ids)}
+
+
+def gpu_tp_sp(rank, world):
+    """Sequence-parallel column -> SiLU -> row pair over tp=world GPUs on the peer-memory path vs unsharded."""
+    import torch
+    import torch.nn.functional as F
+
+    from composed_mixture_of_experts_engine_b200.ops.kernels import check_status
+    from composed_mixture_of_experts_engine_b200.parallel import (ColumnParallelLinear, RowParallelLinear,
+                                                                  build_topology, gather_from_sequence_parallel,
+                                                                  scatter_to_sequence_parallel)
+
+    topo = build_topology(1, 1, tp_size=world, device_type="cuda")
+    dev = topo.device
+    torch.manual_seed(0)
+    B, S, Din, Dmid = 2, 512, 256, 512
+    Wc = (torch.randn(Dmid, Din, device=dev) / Din**0.5).to(torch.bfloat16)
+    Wr = (torch.randn(Din, Dmid, device=dev) / Dmid**0.5).to(torch.bfloat16)
+    x_full = torch.randn(B, S, Din, device=dev, dtype=torch.bfloat16)
+    col = ColumnParallelLinear(Din, Dmid, bias=False, topology=topo, gather_output=False, sequence_parallel=True,
+                               dtype=torch.bfloat16, device=dev)
+    row = RowParallelLinear(Dmid, Din, bias=False, topology=topo, sequence_parallel=True, dtype=torch.bfloat16,
+                            device=dev)
+    sh = Dmid // world
+    with torch.no_grad():
+        col.weight.copy_(Wc[rank * sh:(rank + 1) * sh])
+        row.weight.copy_(Wr[:, rank * sh:(rank + 1) * sh])
+    out = {}
+    for it in range(2):
+        x = x_full.clone().requires_grad_(True)
+        col.zero_grad(set_to_none=True)
+        row.zero_grad(set_to_none=True)
+        ys = row(F.silu(col(scatter_to_sequence_parallel(x, topo))))
+        y = gather_from_sequence_parallel(ys, topo)
+        y.float().pow(2).sum().backward()
+        x2 = x_full.clone().float().requires_grad_(True)
+        wc, wr = Wc.float().requires_grad_(True), Wr.float().requires_grad_(True)
+        y2 = F.linear(F.silu(F.linear(x2, wc)), wr)
+        y2.pow(2).sum().backward()
+        rel = lambda a, b: float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
+        out[f"y{it}"] = rel(y, y2)
+        out[f"dx{it}"] = rel(x.grad, x2.grad)
+        out[f"dwc{it}"] = rel(col.weight.grad, wc.grad[rank * sh:(rank + 1) * sh])
+        out[f"dwr{it}"] = rel(row.weight.grad, wr.grad[:, rank * sh:(rank + 1) * sh])
+    check_status(dev)
+    return out

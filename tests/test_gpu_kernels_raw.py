@@ -467,3 +467,25 @@ def test_gemm_with_fused_row_pull_matches_gather_then_gemm(ext, status):
         n = int(plan.num_m_tiles) * 128
         assert torch.equal(xp[:n], xp_ref[:n])
         assert torch.equal(h[:n], h_ref[:n]) and torch.equal(gu[:n], gu_ref[:n])
+
+
+def test_bounded_wait_reports_a_status_instead_of_hanging(ext):
+    """A barrier whose second participant never arrives: the wait runs out after a few milliseconds, the kernel
+    returns normally with status 5 (peer flag never written) and the context stays usable."""
+    import time
+
+    flags = torch.zeros(16, device="cuda", dtype=torch.int32)
+    status = torch.zeros(1, device="cuda", dtype=torch.int32)
+    ptrs = [flags.data_ptr(), flags.data_ptr()]  # "rank 1" is never launched, so word [1] stays 0
+    t0 = time.perf_counter()
+    ext.peer_barrier(ptrs, 0, 1, status, 5_000_000)  # 5 ms budget
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 2.0
+    assert int(status.item()) == 5 and int(flags[0]) == 1 and int(flags[1]) == 0
+    # the same barrier completes at once when the other word has been written
+    status.zero_()
+    flags[1] = 2
+    ext.peer_barrier(ptrs, 0, 2, status, 5_000_000)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0  # the context is alive

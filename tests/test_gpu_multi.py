@@ -23,8 +23,19 @@ def _spawn_gpu(fn_name, world, *args, timeout=600):
         p.start()
     results = {}
     try:
-        for _ in range(world):
-            rank, status, payload = q.get(timeout=timeout)
+        import queue as _queue
+        import time as _time
+
+        deadline = _time.time() + timeout
+        while len(results) < world:
+            try:
+                rank, status, payload = q.get(timeout=2.0)
+            except _queue.Empty:
+                dead = [p.pid for p in procs if p.exitcode not in (None, 0)]
+                assert not dead, f"worker process(es) {dead} died without reporting (exit codes " \
+                                 f"{[p.exitcode for p in procs]})"
+                assert _time.time() < deadline, "timed out waiting for the workers"
+                continue
             assert status == "ok", f"rank {rank} failed:\n{payload}"
             results[rank] = payload
     finally:
@@ -55,3 +66,10 @@ def test_trainer_multi_gpu(transport):
     for r, out in res.items():
         assert all(math.isfinite(l) for l in out["losses"]) and out["losses"][-1] < out["losses"][0]
         assert out["sync"] == 0.0 and out["ep"] == _world()
+
+
+def test_sequence_parallel_linears_on_peer_memory():
+    res = _spawn_gpu("gpu_tp_sp", 2)
+    for r, out in res.items():
+        for k, v in out.items():
+            assert v < 4e-2, (r, k, v, out)

@@ -26,8 +26,19 @@ def _spawn(fn_name, world, *args, timeout=240):
         p.start()
     results = {}
     try:
-        for _ in range(world):
-            rank, status, payload = q.get(timeout=timeout)
+        import queue as _queue
+        import time as _time
+
+        deadline = _time.time() + timeout
+        while len(results) < world:
+            try:
+                rank, status, payload = q.get(timeout=2.0)
+            except _queue.Empty:
+                dead = [p.pid for p in procs if p.exitcode not in (None, 0)]
+                assert not dead, f"worker process(es) {dead} died without reporting (exit codes " \
+                                 f"{[p.exitcode for p in procs]})"
+                assert _time.time() < deadline, "timed out waiting for the workers"
+                continue
             assert status == "ok", f"rank {rank} failed:\n{payload}"
             results[rank] = payload
     finally:
