@@ -9,7 +9,7 @@ For N > 1 launch one rank per GPU:
 Model and data (configs/olmoe_1b7b.yaml): vocab 50304, d_model 2048, 16 layers, 16 heads, seq 4096, 64 SwiGLU
 experts (F 1024) per layer, top-8, aux-loss coefficient 0.01, bf16 compute with fp32 master weights, AdamW,
 random-init weights N(0, 0.02), synthetic uniform-random token ids.  Weak scaling: every GPU processes 32
-sequences (131,072 tokens) per optimizer step as 16 microbatches of 2, so 8 GPUs make the 1M-token global batch;
+sequences (131,072 tokens) per optimizer step as 8 microbatches of 4, so 8 GPUs make the 1M-token global batch;
 parallelism is sharded data parallel dp=N with the expert-parallel group ep=N carved from it.
 
 Two timed regions of K steps each, both bracketed by a barrier and a device synchronisation and timed with CUDA
@@ -39,7 +39,7 @@ os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
 os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
 
 SEQS_PER_GPU = 32
-MICRO_BATCH = 2
+MICRO_BATCH = 4
 
 
 def parse_args():

@@ -202,6 +202,30 @@ __device__ __forceinline__ void load_row_chunk_bf16(const __nv_bfloat16* src, fl
   }
 }
 
+// 32 fp32 values of one row starting at column `col` (groups of 4 beyond n_limit are skipped)
+__device__ __forceinline__ void prefetch_f32_chunk(const float* row_ptr, int col, int n_limit, bool row_ok,
+                                                   float4 (&v)[8]) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (row_ok && col + j * 4 < n_limit) v[j] = *reinterpret_cast<const float4*>(row_ptr + col + j * 4);
+  }
+}
+
+// gate and up values (bf16) of one row for columns [col, col + 32): gate at row_ptr[col], up at row_ptr[N + col]
+__device__ __forceinline__ void prefetch_gu_chunk(const __nv_bfloat16* row_ptr, int col, int n, bool row_ok,
+                                                  uint4 (&g)[4], uint4 (&u)[4]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    g[j] = make_uint4(0u, 0u, 0u, 0u);
+    u[j] = make_uint4(0u, 0u, 0u, 0u);
+    if (row_ok && col + j * 8 < n) {
+      g[j] = *reinterpret_cast<const uint4*>(row_ptr + col + j * 8);
+      u[j] = *reinterpret_cast<const uint4*>(row_ptr + n + col + j * 8);
+    }
+  }
+}
+
 template <int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS_PULL, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const KParams p) {
@@ -426,17 +450,49 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const uint32_t t_acc = tmem_base + acc * BN + lane_base;
       if (ok) {
         if (EPI == EPI_STORE) {
+          if (p.accumulate && p.d_fp32) {
+            // D += acc in fp32: the old values of chunk c+1 are fetched while chunk c is being processed, so
+            // the global-load latency hides behind the TMEM read and the stores (software pipeline of depth 1)
+            float* drow = reinterpret_cast<float*>(Dg) + row * p.ldd;
+            float4 cur[8], nxt[8];
+            prefetch_f32_chunk(drow, ti.n0, p.N, row_ok, cur);
 #pragma unroll 1
-          for (int c = 0; c < BN / 32; ++c) {
-            if (ti.n0 + c * 32 >= p.N) break;  // uniform across the warp
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(t_acc + c * 32, r);
-            tmem_ld_wait();
-            if (row_ok) {
-              float v[32];
+            for (int c = 0; c < BN / 32; ++c) {
+              const int col = ti.n0 + c * 32;
+              if (col >= p.N) break;
+              uint32_t r[32];
+              tmem_ld_32x32b_x32(t_acc + c * 32, r);
+              prefetch_f32_chunk(drow, col + 32, p.N, row_ok, nxt);
+              tmem_ld_wait();
+              if (row_ok) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-              store_row_chunk(Dg, p.ldd, p.d_fp32, p.accumulate, row, ti.n0 + c * 32, p.N, v);
+                for (int j = 0; j < 8; ++j) {
+                  if (col + j * 4 < p.N) {
+                    float4 o = cur[j];
+                    o.x += __uint_as_float(r[4 * j]);
+                    o.y += __uint_as_float(r[4 * j + 1]);
+                    o.z += __uint_as_float(r[4 * j + 2]);
+                    o.w += __uint_as_float(r[4 * j + 3]);
+                    *reinterpret_cast<float4*>(drow + col + j * 4) = o;
+                  }
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) cur[j] = nxt[j];
+            }
+          } else {
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+              if (ti.n0 + c * 32 >= p.N) break;  // uniform across the warp
+              uint32_t r[32];
+              tmem_ld_32x32b_x32(t_acc + c * 32, r);
+              tmem_ld_wait();
+              if (row_ok) {
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                store_row_chunk(Dg, p.ldd, p.d_fp32, p.accumulate, row, ti.n0 + c * 32, p.N, v);
+              }
             }
           }
         } else if (EPI == EPI_SWIGLU_FWD) {
@@ -465,26 +521,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
           }
         } else {  // EPI_SWIGLU_BWD: acc = dH; D = [dGate | dUp] with row stride ldd (>= 2N)
+          const __nv_bfloat16* gurow = p.aux_in + row * p.ld_aux_in;
+          uint4 cg[4], cu[4], ng[4], nu[4];
+          prefetch_gu_chunk(gurow, ti.n0, p.N, row_ok, cg, cu);
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
             const int col = ti.n0 + c * 32;
             if (col >= p.N) break;
             uint32_t r[32];
             tmem_ld_32x32b_x32(t_acc + c * 32, r);
+            prefetch_gu_chunk(gurow, col + 32, p.N, row_ok, ng, nu);  // next chunk's gate/up while this one computes
             tmem_ld_wait();
             if (row_ok) {
               float g[32], u[32], dg[32], du[32];
-              const __nv_bfloat16* gu = p.aux_in + row * p.ld_aux_in + col;
-              if (col + 32 <= p.N) {
-                load_row_chunk_bf16(gu, g);
-                load_row_chunk_bf16(gu + p.N, u);
-              } else {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                  const bool in = (col + j) < p.N;
-                  g[j] = in ? __bfloat162float(gu[j]) : 0.f;
-                  u[j] = in ? __bfloat162float(gu[p.N + j]) : 0.f;
-                }
+              for (int j = 0; j < 4; ++j) {
+                const bool in = (col + j * 8) < p.N;  // N is a multiple of 8
+                const float2 g0 = unpack_bf16x2(cg[j].x), g1 = unpack_bf16x2(cg[j].y), g2 = unpack_bf16x2(cg[j].z),
+                             g3 = unpack_bf16x2(cg[j].w);
+                const float2 u0 = unpack_bf16x2(cu[j].x), u1 = unpack_bf16x2(cu[j].y), u2 = unpack_bf16x2(cu[j].z),
+                             u3 = unpack_bf16x2(cu[j].w);
+                g[8 * j] = in ? g0.x : 0.f; g[8 * j + 1] = in ? g0.y : 0.f; g[8 * j + 2] = in ? g1.x : 0.f;
+                g[8 * j + 3] = in ? g1.y : 0.f; g[8 * j + 4] = in ? g2.x : 0.f; g[8 * j + 5] = in ? g2.y : 0.f;
+                g[8 * j + 6] = in ? g3.x : 0.f; g[8 * j + 7] = in ? g3.y : 0.f;
+                u[8 * j] = in ? u0.x : 0.f; u[8 * j + 1] = in ? u0.y : 0.f; u[8 * j + 2] = in ? u1.x : 0.f;
+                u[8 * j + 3] = in ? u1.y : 0.f; u[8 * j + 4] = in ? u2.x : 0.f; u[8 * j + 5] = in ? u2.y : 0.f;
+                u[8 * j + 6] = in ? u3.x : 0.f; u[8 * j + 7] = in ? u3.y : 0.f;
               }
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
@@ -496,6 +558,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               }
               store_row_chunk(Dg, p.ldd, 0, 0, row, col, p.N, dg);
               store_row_chunk(reinterpret_cast<__nv_bfloat16*>(Dg) + p.N, p.ldd, 0, 0, row, col, p.N, du);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              cg[j] = ng[j];
+              cu[j] = nu[j];
             }
           }
         }
