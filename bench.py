@@ -51,6 +51,8 @@ def parse_args():
     ap.add_argument("--config", default=str(ROOT / "configs" / "olmoe_1b7b.yaml"))
     ap.add_argument("--micro-batch", type=int, default=MICRO_BATCH)
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
+    ap.add_argument("--tiny", action="store_true",
+                    help="self-test of the reference arm with toy dimensions (runs on CPU too); never a bench value")
     return ap.parse_args()
 
 
@@ -131,7 +133,8 @@ def barrier_sync():
 
     if dist.is_initialized():
         dist.barrier()
-    torch.cuda.synchronize()
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
 
 
 def timed_region(step_fn, steps: int, device) -> float:
@@ -139,6 +142,11 @@ def timed_region(step_fn, steps: int, device) -> float:
     import torch
 
     barrier_sync()
+    if not torch.cuda.is_available():  # only the toy self-test of the reference arm runs without a GPU
+        t0 = time.perf_counter()
+        for i in range(steps):
+            step_fn(i)
+        return max_over_ranks((time.perf_counter() - t0) * 1e3, device)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(steps):
@@ -258,8 +266,20 @@ def run_ours(args) -> dict:
     return out if rank == 0 else {}
 
 
+REFERENCE_DIMS = dict(hidden_dim=2048, num_layers=16, num_experts=64, top_k=8, capacity_factor=1.25, ffn_dim=1024,
+                      vocab_size=50304, sequence_length=4096, dtype="bfloat16")
+TINY_DIMS = dict(hidden_dim=64, num_layers=2, num_experts=4, top_k=2, capacity_factor=1.25, ffn_dim=128,
+                 vocab_size=512, sequence_length=32, dtype="bfloat16")
+
+
+def _is_oom(exc: BaseException) -> bool:
+    return "out of memory" in str(exc).lower()
+
+
 def run_reference(args) -> dict:
-    """The unmodified reference (baseline/_ref/pkg): its ToyMoEModel and train-loop recipe on the same shapes."""
+    """The unmodified reference (baseline/_ref/pkg) through its own public API, the way its train.py drives it:
+    build_topology -> build_model -> apply_fsdp2 -> torch AdamW, cross entropy on the logits, clip, step
+    (reference: train.py:188-325).  None of this repository's models, kernels or engine is on this path."""
     ref = ROOT / "baseline" / "_ref"
     if not (ref / "pkg").exists():
         return {"impl": "reference", "unavailable": "baseline/_ref is not installed (pip --target install missing)"}
@@ -268,52 +288,69 @@ def run_reference(args) -> dict:
     # the reference package is called `pkg`: make sure the one under baseline/_ref wins
     sys.path[:] = [p for p in sys.path if Path(p or ".").resolve() != ROOT]
     sys.path.insert(0, str(ref))
+    for name in [m for m in sys.modules if m == "pkg" or m.startswith("pkg.")]:
+        del sys.modules[name]
     try:
         import torch.distributed as dist
         from pkg.distributed import apply_fsdp2, build_topology
-        from pkg.models import build_model
+        from pkg.models.moe import build_model
         from pkg.utils.config import MoEConfig as RefConfig
 
+        if not str(Path(sys.modules["pkg"].__file__).resolve()).startswith(str(ref.resolve())):
+            return {"impl": "reference", "unavailable": "the reference package under baseline/_ref did not import"}
+        tiny = getattr(args, "tiny", False)
+        cuda = torch.cuda.is_available()
         world = int(os.environ.get("WORLD_SIZE", "1"))
         rank = int(os.environ.get("RANK", "0"))
         if world > 1:
-            torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
-            dist.init_process_group(backend="nccl", rank=rank, world_size=world)
-        accum = max(1, args.seqs_per_gpu // args.micro_batch)
-        cfg = RefConfig.from_dict({
-            "model": dict(hidden_dim=2048, num_layers=16, num_experts=64, top_k=8, capacity_factor=1.25, ffn_dim=1024,
-                          vocab_size=50304, sequence_length=4096, dtype="bfloat16"),
-            "training": dict(global_batch_size=args.micro_batch * accum * world, micro_batch_size=args.micro_batch,
-                             learning_rate=4e-4, weight_decay=0.1, grad_clip=1.0, max_steps=10000, warmup_steps=0,
-                             gradient_accumulation_steps=accum),
-            # the reference cannot run expert parallelism > 1 (its first all-to-all raises); data parallel only
-            "parallelism": dict(data_parallel=world, expert_parallel=1, tensor_parallel=1, pipeline_parallel=1),
-            "checkpoint": dict(local_dir="/tmp/ref-ckpt", remote_uri="file:///tmp/ref-remote"),
-        })
-        topo = build_topology(world, 1)
-        if torch.cuda.is_available() and topo.device.type == "cuda":
-            torch.cuda.set_device(topo.device if topo.device.index is not None else 0)
-        model = build_model(cfg, topo).to(topo.device)
-        model = apply_fsdp2(model, topo, mixed_precision_dtype=torch.bfloat16)
-        optim = torch.optim.AdamW(model.parameters(), lr=4e-4, weight_decay=0.1, betas=(0.9, 0.95))
+            if cuda:
+                torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+            dist.init_process_group(backend="nccl" if cuda else "gloo", rank=rank, world_size=world)
+        dims = dict(TINY_DIMS if tiny else REFERENCE_DIMS)
+        seqs = args.seqs_per_gpu
+        V, S = dims["vocab_size"], dims["sequence_length"]
+
+        def make_cfg(micro):
+            accum = max(1, seqs // micro)
+            return RefConfig.from_dict({
+                "model": dims,
+                "training": dict(global_batch_size=micro * accum * world, micro_batch_size=micro, learning_rate=4e-4,
+                                 weight_decay=0.1, grad_clip=1.0, max_steps=10000, warmup_steps=0,
+                                 gradient_accumulation_steps=accum),
+                # the reference cannot run expert parallelism > 1 (its first all-to-all raises); data parallel only
+                "parallelism": dict(data_parallel=world, expert_parallel=1, tensor_parallel=1, pipeline_parallel=1),
+                "checkpoint": dict(local_dir="/tmp/ref-ckpt", remote_uri="file:///tmp/ref-remote"),
+            })
+
+        cfg = make_cfg(args.micro_batch)
+        topo = build_topology(dp_size=world, ep_size=1, tp_size=1, pp_size=1, device_type="cuda" if cuda else "cpu")
         dev = topo.device
-        V, S, B = 50304, 4096, args.micro_batch
+        model = build_model(cfg, topo)
+        model = apply_fsdp2(model, topo, mixed_precision_dtype=torch.bfloat16 if dims["dtype"] == "bfloat16" else None)
+        optim = torch.optim.AdamW(model.parameters(), lr=4e-4, weight_decay=0.1, betas=(0.9, 0.95))
         gen = torch.Generator().manual_seed(1234 + rank)
-        host = [(torch.randint(0, V, (B * accum, S), generator=gen).pin_memory(),
-                 torch.randint(0, V, (B * accum, S), generator=gen).pin_memory()) for _ in range(2)]
+
+        def pinned(t):
+            return t.pin_memory() if cuda else t
+
+        host = [(pinned(torch.randint(0, V, (seqs, S), generator=gen)),
+                 pinned(torch.randint(0, V, (seqs, S), generator=gen))) for _ in range(2)]
         resident = [(a.to(dev), b.to(dev)) for a, b in host]
+        micro = [args.micro_batch]
 
         def step(ids_all, tgt_all):
+            B = micro[0]
+            accum = max(1, seqs // B)
+            optim.zero_grad(set_to_none=True)
             total = 0.0
             for a in range(accum):
                 ids, tgt = ids_all[a * B:(a + 1) * B], tgt_all[a * B:(a + 1) * B]
                 logits = model(ids)
-                loss = torch.nn.functional.cross_entropy(logits.float().view(-1, V), tgt.view(-1)) / accum
+                loss = torch.nn.functional.cross_entropy(logits.view(-1, V).float(), tgt.reshape(-1)) / accum
                 loss.backward()
                 total = total + loss.detach()
             torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
             optim.step()
-            optim.zero_grad(set_to_none=True)
             return total
 
         def dev_step(i):
@@ -326,24 +363,42 @@ def run_reference(args) -> dict:
             loss = step(a.to(dev, non_blocking=True), b.to(dev, non_blocking=True))
             losses.append(float(loss.item()))
 
-        for i in range(args.warmup):
+        # the reference's experts materialise per-expert activations; halve the micro-batch (same tokens per
+        # step, more accumulation) until one step fits
+        while True:
+            try:
+                dev_step(0)
+                break
+            except Exception as exc:
+                if not _is_oom(exc) or micro[0] == 1 or world > 1:
+                    raise
+                micro[0] //= 2
+                optim.zero_grad(set_to_none=True)
+                del exc
+                torch.cuda.empty_cache()
+        for i in range(1, args.warmup):
             dev_step(i)
-        torch.cuda.synchronize()
-        sampler = ClockSampler(torch.cuda.current_device())
-        sampler.start()
+        sampler = None
+        if cuda:
+            torch.cuda.synchronize()
+            sampler = ClockSampler(torch.cuda.current_device())
+            sampler.start()
         ms_dev = timed_region(dev_step, args.steps, dev)
         ms_e2e = timed_region(e2e_step, args.steps, dev)
-        clocks = sampler.stop()
-        tokens_step = B * accum * S * world
+        clocks = sampler.stop() if sampler is not None else {}
+        tokens_step = seqs * S * world
         out = {
             "metric": "moe_train_tokens_per_sec", "value": tokens_step / (ms_dev / args.steps / 1e3),
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic uniform-random token ids; reference default init",
+            "dtype": "bf16" if dims["dtype"] == "bfloat16" else "fp32",
+            "data": "synthetic uniform-random token ids; reference default init",
             "impl": "reference",
-            "config": {"model": "reference ToyMoEModel with OLMoE-1B-7B dimensions (it has no attention / RoPE)",
-                       "global_batch": B * accum * world, "seq_len": S,
-                       "parallelism": f"dp{world} (FSDP2), ep1: the reference cannot run ep>1"},
+            "config": {"model": "reference ToyMoEModel with OLMoE-1B-7B dimensions (it has no attention / RoPE)"
+                       if not tiny else "reference ToyMoEModel, tiny dimensions (self-test)",
+                       "global_batch": seqs * world, "micro_batch": micro[0], "seq_len": S,
+                       "parallelism": f"dp{world} (FSDP2), ep1: the reference cannot run ep>1",
+                       "l2": "inputs and weights far larger than L2"},
             "e2e": {"value": tokens_step / (ms_e2e / args.steps / 1e3), "unit": "tokens/s",
                     "h2d_bytes_per_step": int(2 * host[0][0].numel() * 8), "d2h_bytes_per_step": 4},
             "gpu_launches": 0, "clocks": clocks,
@@ -358,7 +413,7 @@ def main():
     args = parse_args()
     import torch
 
-    if not torch.cuda.is_available():
+    if not torch.cuda.is_available() and not (args.impl == "reference" and args.tiny):
         print(json.dumps({"impl": args.impl, "unavailable": "no CUDA device"}))
         return 0
     out = run_reference(args) if args.impl == "reference" else run_ours(args)

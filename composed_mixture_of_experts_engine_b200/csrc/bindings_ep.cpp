@@ -55,26 +55,28 @@ void gather_rows_peer(const std::vector<int64_t>& src, int64_t slots_per_src, in
 
 void combine_rows_peer(const std::vector<int64_t>& rows, const std::vector<int64_t>& slot_row, const Tensor& idx,
                        const Tensor& expert_rank, const OptTensor& w, Tensor& y, int64_t K, int64_t slot_base,
-                       int64_t ld_rows) {
+                       int64_t ld_rows, const OptTensor& local_rows) {
   const c10::cuda::CUDAGuard guard(y.device());
   TORCH_CHECK(y.dim() == 2 && y.stride(1) == 1 && y.scalar_type() == at::kBFloat16);
   TORCH_CHECK(idx.scalar_type() == at::kInt && idx.is_contiguous() && expert_rank.scalar_type() == at::kInt);
   check(cmoe::launch_combine_rows_peer(table(rows), table(slot_row), idx.data_ptr<int>(), expert_rank.data_ptr<int>(),
                                        w.has_value() ? w->data_ptr<float>() : nullptr, y.data_ptr(), y.size(0),
                                        static_cast<int>(K), static_cast<int>(y.size(1)), slot_base, ld_rows,
-                                       y.stride(0), stream()),
+                                       y.stride(0), local_rows.has_value() ? local_rows->data_ptr() : nullptr,
+                                       stream()),
         "combine_rows_peer");
 }
 
 void combine_bwd_w_peer(const std::vector<int64_t>& rows, const std::vector<int64_t>& slot_row, const Tensor& idx,
                         const Tensor& expert_rank, const Tensor& dy, Tensor& dw, int64_t K, int64_t slot_base,
-                        int64_t ld_rows) {
+                        int64_t ld_rows, const OptTensor& local_rows) {
   const c10::cuda::CUDAGuard guard(dy.device());
   TORCH_CHECK(dy.dim() == 2 && dy.stride(1) == 1 && dy.scalar_type() == at::kBFloat16);
   check(cmoe::launch_combine_bwd_w_peer(table(rows), table(slot_row), idx.data_ptr<int>(),
                                         expert_rank.data_ptr<int>(), dy.data_ptr(), dw.data_ptr<float>(), dy.size(0),
                                         static_cast<int>(K), static_cast<int>(dy.size(1)), slot_base, ld_rows,
-                                        dy.stride(0), stream()),
+                                        dy.stride(0), local_rows.has_value() ? local_rows->data_ptr() : nullptr,
+                                        stream()),
         "combine_bwd_w_peer");
 }
 

@@ -101,7 +101,8 @@ __global__ void __launch_bounds__(256) combine_rows_peer_kernel(const PeerTable 
                                                                 const float* __restrict__ w,
                                                                 __nv_bfloat16* __restrict__ y, long long n_tokens,
                                                                 int K, int H, long long slot_base, long long ld_rows,
-                                                                long long ld_y) {
+                                                                long long ld_y,
+                                                                const __nv_bfloat16* __restrict__ local_rows) {
   const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
   for (long long t = blockIdx.x * static_cast<long long>(warps) + (threadIdx.x >> 5); t < n_tokens;
        t += static_cast<long long>(gridDim.x) * warps) {
@@ -123,7 +124,11 @@ __global__ void __launch_bounds__(256) combine_rows_peer_kernel(const PeerTable 
         const float wk = __shfl_sync(0xffffffffu, my_w, k);
         if (row < 0) continue;
         float f[8];
-        ld8(reinterpret_cast<const __nv_bfloat16*>(rows.ptr[owner]) + static_cast<long long>(row) * ld_rows + c, f);
+        // rows pushed here by the owners' GEMM epilogues sit at [t*K + k]; otherwise pull from the owner
+        const __nv_bfloat16* src = local_rows ? local_rows + (t * K + k) * ld_rows
+                                              : reinterpret_cast<const __nv_bfloat16*>(rows.ptr[owner]) +
+                                                    static_cast<long long>(row) * ld_rows;
+        ld8(src + c, f);
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] += wk * f[j];
       }
@@ -138,7 +143,8 @@ __global__ void __launch_bounds__(256) combine_bwd_w_peer_kernel(const PeerTable
                                                                  const __nv_bfloat16* __restrict__ dy,
                                                                  float* __restrict__ dw, long long n_tokens, int K,
                                                                  int H, long long slot_base, long long ld_rows,
-                                                                 long long ld_dy) {
+                                                                 long long ld_dy,
+                                                                 const __nv_bfloat16* __restrict__ local_rows) {
   const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
   const long long n_slots = n_tokens * K;
   for (long long s = blockIdx.x * static_cast<long long>(warps) + (threadIdx.x >> 5); s < n_slots;
@@ -147,7 +153,9 @@ __global__ void __launch_bounds__(256) combine_bwd_w_peer_kernel(const PeerTable
     const int row = reinterpret_cast<const int*>(slot_row.ptr[owner])[slot_base + s];
     float acc = 0.f;
     if (row >= 0) {
-      const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(rows.ptr[owner]) + static_cast<long long>(row) * ld_rows;
+      const __nv_bfloat16* a = local_rows ? local_rows + s * ld_rows
+                                          : reinterpret_cast<const __nv_bfloat16*>(rows.ptr[owner]) +
+                                                static_cast<long long>(row) * ld_rows;
       const __nv_bfloat16* b = dy + (s / K) * ld_dy;
       for (int c = lane * 8; c < H; c += 256) {
         float fa[8], fb[8];
@@ -272,22 +280,23 @@ cudaError_t launch_gather_rows_peer(const PeerTable& src, long long slots_per_sr
 
 cudaError_t launch_combine_rows_peer(const PeerTable& rows, const PeerTable& slot_row, const int* idx,
                                      const int* expert_rank, const float* w, void* y, long long n_tokens, int K, int H,
-                                     long long slot_base, long long ld_rows, long long ld_y, cudaStream_t stream) {
+                                     long long slot_base, long long ld_rows, long long ld_y, const void* local_rows,
+                                     cudaStream_t stream) {
   if (H % 8 != 0 || n_tokens <= 0 || K <= 0 || K > 32) return cudaErrorInvalidValue;
   combine_rows_peer_kernel<<<blocks_for(n_tokens, 8, 148 * 8), 256, 0, stream>>>(
       rows, slot_row, idx, expert_rank, w, reinterpret_cast<__nv_bfloat16*>(y), n_tokens, K, H, slot_base, ld_rows,
-      ld_y);
+      ld_y, reinterpret_cast<const __nv_bfloat16*>(local_rows));
   return cudaGetLastError();
 }
 
 cudaError_t launch_combine_bwd_w_peer(const PeerTable& rows, const PeerTable& slot_row, const int* idx,
                                       const int* expert_rank, const void* dy, float* dw, long long n_tokens, int K,
                                       int H, long long slot_base, long long ld_rows, long long ld_dy,
-                                      cudaStream_t stream) {
+                                      const void* local_rows, cudaStream_t stream) {
   if (H % 8 != 0 || n_tokens <= 0 || K <= 0) return cudaErrorInvalidValue;
   combine_bwd_w_peer_kernel<<<blocks_for(n_tokens * K, 8, 148 * 8), 256, 0, stream>>>(
       rows, slot_row, idx, expert_rank, reinterpret_cast<const __nv_bfloat16*>(dy), dw, n_tokens, K, H, slot_base,
-      ld_rows, ld_dy);
+      ld_rows, ld_dy, reinterpret_cast<const __nv_bfloat16*>(local_rows));
   return cudaGetLastError();
 }
 

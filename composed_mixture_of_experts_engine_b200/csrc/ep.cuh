@@ -31,15 +31,18 @@ cudaError_t launch_gather_rows_peer(const PeerTable& src, long long slots_per_sr
 
 // y[t,:] = sum_k w[t,k] * rows[owner][slot_row[owner][slot_base + t*K + k], :], owner = expert_rank[idx[t,k]].
 // `rows` and `slot_row` are peer tables of the owners' result rows and row plans; w may be nullptr (weights 1).
+// With local_rows != nullptr the rows were already pushed to this rank (row t*K+k of local_rows, by the owners'
+// GEMM epilogues) and only the validity of each slot is looked up in the owners' plans.
 cudaError_t launch_combine_rows_peer(const PeerTable& rows, const PeerTable& slot_row, const int* idx,
                                      const int* expert_rank, const float* w, void* y, long long n_tokens, int K, int H,
-                                     long long slot_base, long long ld_rows, long long ld_y, cudaStream_t stream);
+                                     long long slot_base, long long ld_rows, long long ld_y, const void* local_rows,
+                                     cudaStream_t stream);
 
 // dw[t,k] = <dy[t,:], rows[owner][row(t,k), :]>  (0 where the slot was dropped)
 cudaError_t launch_combine_bwd_w_peer(const PeerTable& rows, const PeerTable& slot_row, const int* idx,
                                       const int* expert_rank, const void* dy, float* dw, long long n_tokens, int K,
                                       int H, long long slot_base, long long ld_rows, long long ld_dy,
-                                      cudaStream_t stream);
+                                      const void* local_rows, cudaStream_t stream);
 
 // Gradient reduce-scatter fused with cast and scale: out[i] = scale * sum_r float(grads[r][shard_lo + i]) for
 // i < n (fp32 out; grads are bf16 or fp32 flat buffers of every rank).

@@ -70,6 +70,10 @@ struct KParams {
   int pull_cols;
   uint32_t* tile_ready;
   uint32_t pull_epoch;
+  // fused scatter: per-row destination (rank, row) of the output
+  const int* row_dest;
+  PeerTable scatter_out;
+  long long scatter_ld;
 };
 
 struct Tile {
@@ -481,17 +485,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               for (int j = 0; j < 8; ++j) cur[j] = nxt[j];
             }
           } else {
+            // where this thread's row goes: D, or (fused scatter) a row of some rank's buffer
+            void* dst_base = Dg;
+            long long dst_ld = p.ldd, dst_row = row;
+            bool write = row_ok;
+            if (p.row_dest != nullptr && row_ok) {
+              const int dr = p.row_dest[2 * row], dq = p.row_dest[2 * row + 1];
+              write = dr >= 0;
+              dst_base = write ? p.scatter_out.ptr[dr] : Dg;
+              dst_ld = p.scatter_ld;
+              dst_row = dq;
+            }
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
               if (ti.n0 + c * 32 >= p.N) break;  // uniform across the warp
               uint32_t r[32];
               tmem_ld_32x32b_x32(t_acc + c * 32, r);
               tmem_ld_wait();
-              if (row_ok) {
+              if (write) {
                 float v[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                store_row_chunk(Dg, p.ldd, p.d_fp32, p.accumulate, row, ti.n0 + c * 32, p.N, v);
+                store_row_chunk(dst_base, dst_ld, p.d_fp32, p.accumulate, dst_row, ti.n0 + c * 32, p.N, v);
               }
             }
           }
@@ -729,6 +744,11 @@ cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   kp.pull_epoch = a.pull_epoch;
   if (a.pull_row_slot != nullptr &&
       (a.mode != GEMM_GROUPED_M || a.a_mn || a.tile_ready == nullptr || a.a_cols % 8 != 0))
+    return cudaErrorInvalidValue;
+  kp.row_dest = a.row_dest;
+  kp.scatter_out = a.scatter_out;
+  kp.scatter_ld = a.scatter_ld;
+  if (a.row_dest != nullptr && (a.epilogue != EPI_STORE || a.d_fp32 || a.accumulate || a.mode == GEMM_GROUPED_K))
     return cudaErrorInvalidValue;
   kp.ready_flags = a.ready_flags;
   kp.ready_stride = a.ready_stride;

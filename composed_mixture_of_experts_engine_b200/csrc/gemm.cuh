@@ -85,6 +85,14 @@ struct GemmArgs {
   uint32_t* tile_ready = nullptr;
   uint32_t pull_epoch = 0;
 
+  // Fused scatter (EPI_STORE, bf16, no accumulate).  When row_dest is set, output row r is not written to D but
+  // to rank row_dest[2r]'s buffer in scatter_out at row row_dest[2r+1] (leading dimension scatter_ld), with
+  // plain stores from the epilogue (peer memory over NVLink, or local); rows with rank < 0 are skipped.  This is
+  // the combine push of expert parallelism and the scatter half of a reduce-scatter.
+  const int* row_dest = nullptr;
+  PeerTable scatter_out = {};
+  long long scatter_ld = 0;
+
   int* status = nullptr;  // device int, set to a StatusCode when a wait ran out
   unsigned long long timeout_ns = 0;  // 0: default
   int num_sms = 0;                    // 0: query the current device

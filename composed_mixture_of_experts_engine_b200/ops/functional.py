@@ -171,7 +171,7 @@ def _weight_grad(a: torch.Tensor, b: torch.Tensor, param: torch.Tensor, M: int, 
 
 def grouped_swiglu_forward(xp: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, plan: MoEPlan,
                            ready: Optional[dict] = None, yp_out: Optional[torch.Tensor] = None,
-                           pull: Optional[dict] = None):
+                           pull: Optional[dict] = None, scatter: Optional[dict] = None):
     """(hact, gu, yp) for expert-sorted rows ``xp`` [cap_rows, H].  With ``pull`` (src_ptrs, slots_per_src, pull_K,
     ld_src) the first GEMM fills ``xp`` itself from the ranks' token buffers while it runs (fused dispatch)."""
     E, twoF, H = w13.shape
@@ -179,7 +179,9 @@ def grouped_swiglu_forward(xp: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor
     dev = xp.device
     hact = torch.empty(plan.cap_rows, Fdim, device=dev, dtype=torch.bfloat16)
     gu = torch.empty(plan.cap_rows, twoF, device=dev, dtype=torch.bfloat16)
-    yp = yp_out if yp_out is not None else torch.empty(plan.cap_rows, H, device=dev, dtype=torch.bfloat16)
+    yp = None
+    if scatter is None:
+        yp = yp_out if yp_out is not None else torch.empty(plan.cap_rows, H, device=dev, dtype=torch.bfloat16)
     kw = ready or {}
     if pull is not None:
         kernels.gemm_pull(xp, w13.view(E * twoF, H), hact, plan, epilogue=EPI_SWIGLU_FWD, N=Fdim, K=H, groups=E,
@@ -188,14 +190,18 @@ def grouped_swiglu_forward(xp: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor
         kernels.gemm(xp, w13.view(E * twoF, H), hact, mode=GEMM_GROUPED_M, epilogue=EPI_SWIGLU_FWD, N=Fdim, K=H,
                      groups=E, b_group_rows=twoF, split_n=Fdim, tile_group=plan.tile_group,
                      num_m_tiles=plan.num_m_tiles, max_m_tiles=plan.max_m_tiles, aux_out=gu, **kw)
-    kernels.gemm(hact, w2.view(E * H, Fdim), yp, mode=GEMM_GROUPED_M, N=H, K=Fdim, groups=E, b_group_rows=H,
-                 tile_group=plan.tile_group, num_m_tiles=plan.num_m_tiles, max_m_tiles=plan.max_m_tiles)
+    if scatter is not None:  # the result rows go straight to the ranks that own the tokens (fused combine push)
+        kernels.gemm_scatter(hact, w2.view(E * H, Fdim), N=H, K=Fdim, plan=plan, groups=E, b_group_rows=H, **scatter)
+    else:
+        kernels.gemm(hact, w2.view(E * H, Fdim), yp, mode=GEMM_GROUPED_M, N=H, K=Fdim, groups=E, b_group_rows=H,
+                     tile_group=plan.tile_group, num_m_tiles=plan.num_m_tiles, max_m_tiles=plan.max_m_tiles)
     return hact, gu, yp
 
 
 def grouped_swiglu_backward(dyp: torch.Tensor, xp: torch.Tensor, hact: torch.Tensor, gu: torch.Tensor,
                             w13: torch.Tensor, w2: torch.Tensor, plan: MoEPlan, need_dx: bool = True,
-                            dxp_out: Optional[torch.Tensor] = None, pull: Optional[dict] = None):
+                            dxp_out: Optional[torch.Tensor] = None, pull: Optional[dict] = None,
+                            scatter: Optional[dict] = None):
     """(dxp, dW13, dW2) of the grouped SwiGLU FFN; weight gradients go to ``main_grad`` when the parameters have one."""
     E, twoF, H = w13.shape
     Fdim = twoF // 2
@@ -209,10 +215,14 @@ def grouped_swiglu_backward(dyp: torch.Tensor, xp: torch.Tensor, hact: torch.Ten
                      max_m_tiles=plan.max_m_tiles, aux_in=gu)
     dxp = None
     if need_dx:
-        dxp = dxp_out if dxp_out is not None else torch.empty_like(xp)
-        kernels.gemm(dgu, w13.view(E * twoF, H), dxp, mode=GEMM_GROUPED_M, N=H, K=twoF, b_mn=True, groups=E,
-                     b_group_rows=twoF, tile_group=plan.tile_group, num_m_tiles=plan.num_m_tiles,
-                     max_m_tiles=plan.max_m_tiles)
+        if scatter is not None:  # dX rows are pushed to the token owners by the epilogue
+            kernels.gemm_scatter(dgu, w13.view(E * twoF, H), N=H, K=twoF, plan=plan, groups=E, b_group_rows=twoF,
+                                 b_mn=True, **scatter)
+        else:
+            dxp = dxp_out if dxp_out is not None else torch.empty_like(xp)
+            kernels.gemm(dgu, w13.view(E * twoF, H), dxp, mode=GEMM_GROUPED_M, N=H, K=twoF, b_mn=True, groups=E,
+                         b_group_rows=twoF, tile_group=plan.tile_group, num_m_tiles=plan.num_m_tiles,
+                         max_m_tiles=plan.max_m_tiles)
     dw2 = _weight_grad(dyp, hact, w2, H, Fdim, plan)
     dw13 = _weight_grad(dgu, xp, w13, twoF, H, plan)
     return dxp, dw13, dw2

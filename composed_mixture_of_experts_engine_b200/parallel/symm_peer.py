@@ -7,20 +7,25 @@ Per layer call, on one stream, with no host round trip:
               pull every rank's idx and w (a few hundred KB)       peer_allgather
               row plan of the local experts over all ranks' slots  moe_plan  (slot -> row table lands in symmetric memory)
               pull the rows that route here, expert-sorted         gather_rows_peer   <- the dispatch, P2P loads over NVLink
-              grouped SwiGLU GEMMs (tcgen05), yp into a symmetric buffer
+              grouped SwiGLU GEMMs (tcgen05); the epilogue of the second one stores every result row straight
+              into the buffer of the rank that owns the token            <- the combine transfer, P2P stores
               barrier
-              y[t] = sum_k w * yp[owner][row]                      combine_rows_peer  <- the combine, P2P loads
-    backward  publish dy; barrier; d(gate) by dot products against the owners' yp rows; pull dy rows (scaled by
-              the gate weights); grouped backward GEMMs, dxp into a symmetric buffer; barrier; dx[t] = sum_k dxp
+              y[t] = sum_k w * ycomb[t*K+k]                        combine_rows_peer on local rows
+    backward  publish dy; barrier; d(gate) by dot products against the local ycomb rows; pull dy rows (scaled by
+              the gate weights) inside the dgrad GEMM; the dX GEMM pushes its rows to the token owners; barrier;
+              dx[t] = sum_k dxcomb[t*K+k]
+
+``CMOE_EP_PUSH=0`` keeps the results on the expert's rank and lets the combine kernels pull them instead
+(``CMOE_EP_FUSED=0`` likewise turns the dispatch into a separate pull kernel).
 
 Nothing is gathered that is not needed, nothing is reduced in bf16, and no buffer is materialised twice (the
 library transport all-gathers x and reduce-scatters a [ep*T, H] partial result).  Barriers are flag words in
 symmetric memory with a bounded wait; a peer that never arrives turns into a ``KernelTimeoutError`` at the next
 ``check_status``, not a hang.
 
-Buffer reuse: x / idx / w / dy / dxp staging buffers are shared by all layers (the barrier that follows their
-last remote read orders it before the next local write); yp and the slot->row table live per layer because the
-backward pass of the layer reads them from the peers again.
+Buffer reuse: x / idx / w / dy / dx staging buffers are shared by all layers (a barrier always separates the last
+read of one use from the first write of the next); the result rows and the slot->row table live per layer
+because the backward pass of the layer reads them again.
 """
 
 from __future__ import annotations
@@ -48,6 +53,20 @@ def available(topology: Optional[ParallelTopology], axis: str) -> bool:
     size = {"ep": topology.ep_size, "tp": topology.tp_size, "dp": topology.dp_size,
             "edp": len(topology.axis_ranks("edp"))}[axis]
     return 1 < size <= 16
+
+
+def _push() -> bool:
+    """Result rows are pushed to the token owners by the GEMM epilogue (default) or pulled by the combine kernel."""
+    return os.environ.get("CMOE_EP_PUSH", "1") != "0"
+
+
+def _row_dest(row_slot: torch.Tensor, slots_per_rank: int) -> torch.Tensor:
+    """[rows, 2] int32 (rank, row) of every expert-sorted row's home: slot s belongs to rank s // slots_per_rank and
+    lands in row s % slots_per_rank of its buffer; padding rows (slot < 0) get rank -1."""
+    slot = row_slot.to(torch.int64)
+    rank = torch.where(slot >= 0, slot // slots_per_rank, torch.full_like(slot, -1))
+    row = torch.where(slot >= 0, slot % slots_per_rank, torch.zeros_like(slot))
+    return torch.stack([rank, row], dim=1).to(torch.int32).contiguous()
 
 
 def _fused() -> bool:
@@ -152,20 +171,30 @@ class _EPMoEPeer(torch.autograd.Function):
         plan = kernels.moe_plan(idx_all, num_experts, expert_lo=expert_lo, n_local=n_local, capacity=capacity * ep,
                                 cap_rows=cap_rows, slot_row_out=srow.view(torch.int32, ep * T * K))
         xp = torch.empty(cap_rows, H, device=dev, dtype=torch.bfloat16)
-        yps = pc.per_layer(lkey, "yp", cap_rows * H * 2)
-        yp = yps.view(torch.bfloat16, cap_rows * H).view(cap_rows, H)
+        push = _push()
+        erank = pc.expert_rank_table(num_experts)
+        y = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
+        if push:
+            ycs = pc.per_layer(lkey, "ycomb", T * K * H * 2)
+            row_dest = _row_dest(plan.row_slot, T * K)
+            kw = dict(scatter=dict(row_dest=row_dest, out_ptrs=_ptrs(ycs), out_ld=H))
+        else:
+            yps = pc.per_layer(lkey, "yp", cap_rows * H * 2)
+            row_dest = None
+            kw = dict(yp_out=yps.view(torch.bfloat16, cap_rows * H).view(cap_rows, H))
         if _fused():
             # the dispatch runs inside the first grouped GEMM: rows stream in over NVLink tile by tile
-            pull = dict(src_ptrs=_ptrs(xs), slots_per_src=T * K, pull_K=K, ld_src=H)
-            hact, gu, _ = OF.grouped_swiglu_forward(xp, w13, w2, plan, yp_out=yp, pull=pull)
+            kw["pull"] = dict(src_ptrs=_ptrs(xs), slots_per_src=T * K, pull_K=K, ld_src=H)
         else:
             ext.gather_rows_peer(_ptrs(xs), T * K, K, plan.row_slot, None, xp, plan.num_m_tiles, H)
-            hact, gu, _ = OF.grouped_swiglu_forward(xp, w13, w2, plan, yp_out=yp)
+        hact, gu, _ = OF.grouped_swiglu_forward(xp, w13, w2, plan, **kw)
         pc.barrier()
-
-        y = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
-        erank = pc.expert_rank_table(num_experts)
-        ext.combine_rows_peer(_ptrs(yps), _ptrs(srow), idx32, erank, gate_w32, y, K, pc.rank * T * K, H)
+        if push:
+            ext.combine_rows_peer(_ptrs(ycs), _ptrs(srow), idx32, erank, gate_w32, y, K, pc.rank * T * K, H,
+                                  ycs.view(torch.bfloat16, T * K * H).view(T * K, H))
+        else:
+            ext.combine_rows_peer(_ptrs(yps), _ptrs(srow), idx32, erank, gate_w32, y, K, pc.rank * T * K, H, None)
+        ctx.push, ctx.row_dest = push, row_dest
 
         ctx.save_for_backward(xp, hact, gu, w_all, w13, w2, idx32, gate_w32)
         ctx.plan, ctx.pc, ctx.lkey, ctx.cap_rows = plan, pc, lkey, cap_rows
@@ -187,28 +216,41 @@ class _EPMoEPeer(torch.autograd.Function):
         dys.view(torch.bfloat16, T * H).view(T, H).copy_(dy)
         pc.barrier()
 
-        yps = pc.per_layer(lkey, "yp", cap_rows * H * 2)
         srow = pc.per_layer(lkey, "slot_row", pc.world * T * K * 4)
         erank = pc.expert_rank_table(ctx.num_experts)
+        push = ctx.push
+        slot_base = pc.rank * T * K
         d_gate = None
         if ctx.needs_input_grad[1]:
             d_gate = torch.empty(T, K, device=dev, dtype=torch.float32)
-            ext.combine_bwd_w_peer(_ptrs(yps), _ptrs(srow), idx32, erank, dy, d_gate, K, pc.rank * T * K, H)
+            if push:  # the forward left this rank's result rows here: no NVLink traffic
+                ycs = pc.per_layer(lkey, "ycomb", T * K * H * 2)
+                ext.combine_bwd_w_peer(_ptrs(ycs), _ptrs(srow), idx32, erank, dy, d_gate, K, slot_base, H,
+                                       ycs.view(torch.bfloat16, T * K * H).view(T * K, H))
+            else:
+                yps = pc.per_layer(lkey, "yp", cap_rows * H * 2)
+                ext.combine_bwd_w_peer(_ptrs(yps), _ptrs(srow), idx32, erank, dy, d_gate, K, slot_base, H, None)
         dyp = torch.empty(cap_rows, H, device=dev, dtype=torch.bfloat16)
-        dxs = pc.shared("dxp", cap_rows * H * 2)
-        dxp_buf = dxs.view(torch.bfloat16, cap_rows * H).view(cap_rows, H)
-        pull = None
+        kw = {}
+        if push:
+            dxs = pc.shared("dxcomb", T * K * H * 2)
+            kw["scatter"] = dict(row_dest=ctx.row_dest, out_ptrs=_ptrs(dxs), out_ld=H)
+        else:
+            dxs = pc.shared("dxp", cap_rows * H * 2)
+            kw["dxp_out"] = dxs.view(torch.bfloat16, cap_rows * H).view(cap_rows, H)
         if _fused():
-            pull = dict(src_ptrs=_ptrs(dys), slots_per_src=T * K, pull_K=K, ld_src=H, slot_scale=w_all.reshape(-1))
+            kw["pull"] = dict(src_ptrs=_ptrs(dys), slots_per_src=T * K, pull_K=K, ld_src=H,
+                              slot_scale=w_all.reshape(-1))
         else:
             ext.gather_rows_peer(_ptrs(dys), T * K, K, plan.row_slot, w_all.reshape(-1), dyp, plan.num_m_tiles, H)
-        dxp, dw13, dw2 = OF.grouped_swiglu_backward(dyp, xp, hact, gu, w13, w2, plan,
-                                                    need_dx=ctx.needs_input_grad[0], dxp_out=dxp_buf, pull=pull)
+        need_dx = ctx.needs_input_grad[0]
+        _, dw13, dw2 = OF.grouped_swiglu_backward(dyp, xp, hact, gu, w13, w2, plan, need_dx=need_dx, **kw)
         pc.barrier()
         dx = None
-        if dxp is not None:
+        if need_dx:
             dx = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
-            ext.combine_rows_peer(_ptrs(dxs), _ptrs(srow), idx32, erank, None, dx, K, pc.rank * T * K, H)
+            local = dxs.view(torch.bfloat16, T * K * H).view(T * K, H) if push else None
+            ext.combine_rows_peer(_ptrs(dxs), _ptrs(srow), idx32, erank, None, dx, K, slot_base, H, local)
         return dx, d_gate, None, dw13, dw2, None, None, None, None, None, None
 
 
