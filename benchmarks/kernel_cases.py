@@ -66,6 +66,7 @@ def main():
     ap.add_argument("case")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--small", action="store_true", help="quarter-size inputs (for multi-pass profiler captures)")
+    ap.add_argument("--rows", type=int, default=65536, help="expert-sorted rows of the grouped cases")
     args = ap.parse_args()
     ext = _ext.ext()
     hbm, tflops_peak, how = peaks()
@@ -116,7 +117,7 @@ def main():
                    cublas_tflops=fl / lib / 1e9)
     elif args.case.startswith("grouped_") or args.case in ("gather", "combine"):
         E, H, F = 64, 2048, 1024
-        R = 65536 // shrink
+        R = args.rows // shrink
         tg, nt, go, tiles = uniform_plan(R, E)
         X = torch.randn(R, H, device=dev, dtype=bf)
         W13 = (torch.randn(E, 2 * F, H, device=dev) * 0.02).to(bf)
@@ -137,10 +138,17 @@ def main():
             fn = lambda: kernels.gemm(Y, W2.view(-1, F), dGU, mode=GEMM_GROUPED_M, epilogue=EPI_SWIGLU_BWD, N=F, K=H,
                                       b_mn=True, b_group_rows=H, aux_in=GU, **common)
             fl = 2 * R * F * H
-        elif args.case == "grouped_wgrad":
-            dW13 = torch.zeros(E, 2 * F, H, device=dev)
+        elif args.case in ("grouped_wgrad", "grouped_wgrad_store", "grouped_wgrad_bf16"):
+            # fp32 accumulate (what training runs), fp32 overwrite, bf16 overwrite: the last two bound the main loop
+            dW13 = torch.zeros(E, 2 * F, H, device=dev, dtype=bf if args.case.endswith("bf16") else torch.float32)
+            acc = args.case == "grouped_wgrad"
             fn = lambda: kernels.gemm(GU, X, dW13, mode=GEMM_GROUPED_K, M=2 * F, N=H, a_mn=True, b_mn=True, groups=E,
-                                      group_offsets=go, d_group_stride=2 * F * H, accumulate=True)
+                                      group_offsets=go, d_group_stride=2 * F * H, accumulate=acc)
+            fl = 2 * R * 2 * F * H
+        elif args.case == "grouped_dx":
+            dX = torch.empty_like(X)
+            fn = lambda: kernels.gemm(GU, W13.view(-1, H), dX, mode=GEMM_GROUPED_M, N=H, K=2 * F, b_mn=True,
+                                      b_group_rows=2 * F, **common)
             fl = 2 * R * 2 * F * H
         else:
             N, K = R // 8, 8

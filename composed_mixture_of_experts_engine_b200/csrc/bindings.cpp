@@ -215,9 +215,12 @@ void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tenso
   const c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(dy.is_contiguous() && x.is_contiguous() && dx.is_contiguous() && dw.scalar_type() == at::kFloat);
   const int H = static_cast<int>(x.size(-1));
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  const int64_t rows = x.numel() / H;
+  // scratch for the per-CTA column sums (stream-ordered caching allocation, no synchronisation)
+  Tensor partial = at::empty({cmoe::rmsnorm_bwd_partial_rows(rows, sms), H}, dw.options());
   check_cuda(cmoe::launch_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(),
-                                      dw.data_ptr<float>(), x.numel() / H, H,
-                                      at::cuda::getCurrentDeviceProperties()->multiProcessorCount, cur_stream()),
+                                      dw.data_ptr<float>(), partial.data_ptr<float>(), rows, H, sms, cur_stream()),
              "rmsnorm_bwd");
 }
 void rope(Tensor& t, const Tensor& cos_tab, const Tensor& sin_tab, int64_t seq, bool inverse) {

@@ -12,9 +12,14 @@
 //   warps 2..5  epilogue: each warp owns the TMEM lane quadrant (warp_id % 4)
 // Tile 128 x 256 x 64, 4 shared-memory stages (48 KiB each), two accumulators of 256 TMEM
 // columns so that the epilogue of tile i overlaps the main loop of tile i+1.
+// Plain results leave through a 32 KiB swizzled staging area and TMA: `cp.async.bulk.tensor` stores, or
+// `cp.reduce.async.bulk.tensor ... add` when the fp32 result accumulates into global memory (weight gradients),
+// so the SM never reads the old values; rows that scatter to other ranks are copied out of the staging area
+// with whole-row coalesced stores.
 #include "gemm.cuh"
 
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -36,7 +41,19 @@ constexpr int GEMM_THREADS = 192;
 constexpr int GEMM_THREADS_PULL = 320;  // + four row-pull warps (fused expert-parallel dispatch)
 constexpr int TMEM_COLS = 2 * BN;  // 512: two accumulators
 constexpr int GROUP_M_SWIZZLE = 8;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+// epilogue staging: two buffers of 128 rows x 128 bytes (32 fp32 or 64 bf16 columns) in the 128-byte swizzle, from
+// which finished pieces of a tile leave through TMA stores (or coalesced row copies when rows scatter to peers)
+constexpr int STAGING_BUF_BYTES = BM * 128;
+constexpr int STAGING_BYTES = 2 * STAGING_BUF_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int EPI_FIRST_THREAD = 64;  // warp 2, lane 0: issues the TMA stores of the epilogue
+
+enum OutMode : int {
+  OUT_DIRECT = 0,      // each thread stores its own row from registers
+  OUT_TMA_STORE = 1,   // staged in shared memory, written by TMA
+  OUT_TMA_REDUCE = 2,  // staged, added to global memory by TMA (fp32 accumulate)
+  OUT_SCATTER = 3,     // staged, then whole rows are copied to their (rank, row) homes with coalesced stores
+};
 
 struct KParams {
   int mode, M, N, K, groups;
@@ -74,6 +91,7 @@ struct KParams {
   const int* row_dest;
   PeerTable scatter_out;
   long long scatter_ld;
+  int out_mode;  // OutMode (EPI_STORE only)
 };
 
 struct Tile {
@@ -196,16 +214,6 @@ __device__ __forceinline__ void store_row_chunk(void* D, long long ldd, int d_fp
   }
 }
 
-__device__ __forceinline__ void load_row_chunk_bf16(const __nv_bfloat16* src, float (&v)[32]) {
-#pragma unroll
-  for (int j = 0; j < 32; j += 8) {
-    const uint4 x = *reinterpret_cast<const uint4*>(src + j);
-    const float2 a = unpack_bf16x2(x.x), b = unpack_bf16x2(x.y), c = unpack_bf16x2(x.z), d = unpack_bf16x2(x.w);
-    v[j] = a.x; v[j + 1] = a.y; v[j + 2] = b.x; v[j + 3] = b.y;
-    v[j + 4] = c.x; v[j + 5] = c.y; v[j + 6] = d.x; v[j + 7] = d.y;
-  }
-}
-
 // 32 fp32 values of one row starting at column `col` (groups of 4 beyond n_limit are skipped)
 __device__ __forceinline__ void prefetch_f32_chunk(const float* row_ptr, int col, int n_limit, bool row_ok,
                                                    float4 (&v)[8]) {
@@ -232,12 +240,14 @@ __device__ __forceinline__ void prefetch_gu_chunk(const __nv_bfloat16* row_ptr, 
 
 template <int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS_PULL, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const KParams p) {
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const __grid_constant__ CUtensorMap tmD, const KParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* stg = smem + STAGES * STAGE_BYTES;  // 1024-byte aligned, as the swizzle pattern needs
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + STAGING_BYTES);
   uint64_t* full_bar = bars;                 // [STAGES]
   uint64_t* empty_bar = bars + STAGES;       // [STAGES]
   uint64_t* tfull_bar = bars + 2 * STAGES;   // [2]
@@ -428,6 +438,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     int acc = 0;
     uint32_t acc_phase = 0;
+    uint32_t stage_ctr = 0;  // pieces staged so far: picks the staging buffer
     const int m_limit = (p.mode == GEMM_GROUPED_M) ? (m_tiles * BM) : p.M;
     for (int t = blockIdx.x; t < n_total; t += gridDim.x) {
       const Tile ti = decode_tile(p, t, m_tiles, n_tiles);
@@ -452,6 +463,113 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const bool ok = mbar_wait(&tfull_bar[acc], acc_phase, wc, ST_TIMEOUT_TMEM_FULL);
       tc_fence_after();
       const uint32_t t_acc = tmem_base + acc * BN + lane_base;
+      if (EPI == EPI_STORE && p.out_mode != OUT_DIRECT) {
+        // ---- staged epilogue.  Every piece of 128 rows x 128 bytes goes registers -> swizzled shared memory ->
+        // global memory.  One named barrier per piece: it carries the OR of "my wait failed / abort seen", so all
+        // 128 threads leave the loop together and no barrier is ever left waiting for a thread that gave up.
+        const int unit_cols = p.d_fp32 ? 32 : 64;
+        const int sw = row_in_tile & 7;
+        bool any_bad = false;
+        int2 dest[8];
+        if (p.out_mode == OUT_SCATTER) {
+          // copy-out assignment: thread t moves 16-byte chunk (t & 7) of rows (t >> 3) + 16 i
+          const int t = threadIdx.x - EPI_FIRST_THREAD;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const long long rr = ti.m0 + (t >> 3) + 16 * i;
+            dest[i] = make_int2(-1, 0);
+            if (rr < m_limit) dest[i] = *reinterpret_cast<const int2*>(p.row_dest + 2 * rr);
+          }
+        }
+#pragma unroll 1
+        for (int u = 0; u < BN / unit_cols; ++u) {
+          const int col0 = ti.n0 + u * unit_cols;
+          if (col0 >= p.N) break;  // uniform
+          uint8_t* buf = stg + (stage_ctr & 1) * STAGING_BUF_BYTES;
+          uint8_t* myrow = buf + row_in_tile * 128;
+          if (ok) {
+            if (p.d_fp32) {
+              uint32_t r[32];
+              tmem_ld_32x32b_x32(t_acc + u * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<uint4*>(myrow + ((j ^ sw) << 4)) =
+                    make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            } else {
+              uint32_t r0[32], r1[32];
+              tmem_ld_32x32b_x32(t_acc + u * 64, r0);
+              tmem_ld_32x32b_x32(t_acc + u * 64 + 32, r1);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(r0[8 * j]), __uint_as_float(r0[8 * j + 1]));
+                o.y = pack_bf16x2(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
+                o.z = pack_bf16x2(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
+                o.w = pack_bf16x2(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
+                *reinterpret_cast<uint4*>(myrow + ((j ^ sw) << 4)) = o;
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(r1[8 * j]), __uint_as_float(r1[8 * j + 1]));
+                o.y = pack_bf16x2(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
+                o.z = pack_bf16x2(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
+                o.w = pack_bf16x2(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
+                *reinterpret_cast<uint4*>(myrow + (((j + 4) ^ sw) << 4)) = o;
+              }
+            }
+          }
+          if (p.out_mode != OUT_SCATTER) {
+            fence_proxy_async_smem();
+            // the store issued one piece ago has read the other buffer before anybody writes it again
+            if (threadIdx.x == EPI_FIRST_THREAD) bulk_wait_group_read<0>();
+          }
+          {
+            const int bad = (!ok || *abort_flag) ? 1 : 0;
+            int any;
+            asm volatile(
+                "{\n\t.reg .pred q, r;\n\tsetp.ne.s32 q, %1, 0;\n\tbar.red.or.pred r, 1, 128, q;\n\t"
+                "selp.s32 %0, 1, 0, r;\n\t}"
+                : "=r"(any)
+                : "r"(bad)
+                : "memory");
+            any_bad = any != 0;
+          }
+          if (any_bad) break;  // uniform over the 128 epilogue threads
+          if (p.out_mode == OUT_SCATTER) {
+            const int t = threadIdx.x - EPI_FIRST_THREAD;
+            const int ch = t & 7;
+            if (col0 + ch * 8 < p.N) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                if (dest[i].x >= 0) {
+                  const int rr = (t >> 3) + 16 * i;
+                  const uint4 v = *reinterpret_cast<const uint4*>(buf + rr * 128 + ((ch ^ (rr & 7)) << 4));
+                  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.scatter_out.ptr[dest[i].x]) +
+                                     static_cast<long long>(dest[i].y) * p.scatter_ld + col0 + ch * 8;
+                  *reinterpret_cast<uint4*>(o) = v;
+                }
+              }
+            }
+          } else if (threadIdx.x == EPI_FIRST_THREAD) {
+            const int zgrp = (p.mode == GEMM_GROUPED_K) ? ti.group : 0;
+            if (p.out_mode == OUT_TMA_REDUCE)
+              tma_reduce_add_3d(&tmD, buf, col0, ti.m0, zgrp);  // rows and columns past the edge are clipped
+            else
+              tma_store_3d(&tmD, buf, col0, ti.m0, zgrp);
+            bulk_commit_group();
+          }
+          ++stage_ctr;
+        }
+        tc_fence_before();
+        mbar_arrive(&tempty_bar[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+        if (any_bad) break;
+        continue;
+      }
       if (ok) {
         if (EPI == EPI_STORE) {
           if (p.accumulate && p.d_fp32) {
@@ -485,28 +603,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               for (int j = 0; j < 8; ++j) cur[j] = nxt[j];
             }
           } else {
-            // where this thread's row goes: D, or (fused scatter) a row of some rank's buffer
-            void* dst_base = Dg;
-            long long dst_ld = p.ldd, dst_row = row;
-            bool write = row_ok;
-            if (p.row_dest != nullptr && row_ok) {
-              const int dr = p.row_dest[2 * row], dq = p.row_dest[2 * row + 1];
-              write = dr >= 0;
-              dst_base = write ? p.scatter_out.ptr[dr] : Dg;
-              dst_ld = p.scatter_ld;
-              dst_row = dq;
-            }
+            // direct bf16 / fp32 stores (and bf16 accumulate) from registers, one row per thread
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
               if (ti.n0 + c * 32 >= p.N) break;  // uniform across the warp
               uint32_t r[32];
               tmem_ld_32x32b_x32(t_acc + c * 32, r);
               tmem_ld_wait();
-              if (write) {
+              if (row_ok) {
                 float v[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                store_row_chunk(dst_base, dst_ld, p.d_fp32, p.accumulate, dst_row, ti.n0 + c * 32, p.N, v);
+                store_row_chunk(Dg, p.ldd, p.d_fp32, p.accumulate, row, ti.n0 + c * 32, p.N, v);
               }
             }
           }
@@ -588,6 +696,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if (acc == 0) acc_phase ^= 1u;
       if (*abort_flag) break;
     }
+    // shared memory and the kernel's results must outlive the TMA stores still in flight
+    if (threadIdx.x == EPI_FIRST_THREAD && (p.out_mode == OUT_TMA_STORE || p.out_mode == OUT_TMA_REDUCE))
+      bulk_wait_group<0>();
   }
 
   // ------------------------------------------------------------------ teardown
@@ -681,9 +792,73 @@ cudaError_t make_tmap(CUtensorMap* out, const void* ptr, long long rows, long lo
   return cudaSuccess;
 }
 
+// Output map: [groups, rows, cols] of fp32 or bf16 with row stride ld and group stride gstride (elements); the box
+// is one staging buffer, 128 rows x 128 bytes, 128-byte swizzle.
+cudaError_t make_tmap_out(CUtensorMap* out, const void* ptr, int fp32, long long groups, long long rows,
+                          long long cols, long long ld, long long gstride) {
+  struct Key {
+    const void* ptr;
+    long long groups, rows, cols, ld, gstride;
+    int fp32;
+    bool operator==(const Key& o) const {
+      return ptr == o.ptr && groups == o.groups && rows == o.rows && cols == o.cols && ld == o.ld &&
+             gstride == o.gstride && fp32 == o.fp32;
+    }
+  };
+  struct KeyHash {
+    size_t operator()(const Key& k) const {
+      size_t h = reinterpret_cast<size_t>(k.ptr);
+      for (long long v : {k.groups, k.rows, k.cols, k.ld, k.gstride, static_cast<long long>(k.fp32)})
+        h = h * 1000003u ^ static_cast<size_t>(v);
+      return h;
+    }
+  };
+  static std::mutex mu;
+  static std::unordered_map<Key, CUtensorMap, KeyHash> cache;
+  Key key{ptr, groups, rows, cols, ld, gstride, fp32};
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return cudaSuccess;
+    }
+  }
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return cudaErrorNotSupported;
+  const long long es = fp32 ? 4 : 2;
+  cuuint64_t gdim[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(groups)};
+  cuuint64_t gstr[2] = {static_cast<cuuint64_t>(ld * es), static_cast<cuuint64_t>(gstride * es)};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(128 / es), static_cast<cuuint32_t>(BM), 1u};
+  cuuint32_t estride[3] = {1u, 1u, 1u};
+  CUresult r = enc(out, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                   const_cast<void*>(ptr), gdim, gstr, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    std::fprintf(stderr, "cmoe: cuTensorMapEncodeTiled (output) failed (%d) groups=%lld rows=%lld cols=%lld ld=%lld\n",
+                 static_cast<int>(r), groups, rows, cols, ld);
+    return cudaErrorInvalidValue;
+  }
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    if (cache.size() > 8192) cache.clear();
+    cache.emplace(key, *out);
+  }
+  return cudaSuccess;
+}
+
+// CMOE_GEMM_DIRECT_EPILOGUE=1 keeps every epilogue on per-thread stores from registers (for A/B measurements)
+bool direct_epilogue_forced() {
+  static const bool forced = [] {
+    const char* v = std::getenv("CMOE_GEMM_DIRECT_EPILOGUE");
+    return v != nullptr && v[0] != '\0' && v[0] != '0';
+  }();
+  return forced;
+}
+
 template <int EPI>
-cudaError_t launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const KParams& kp, int grid,
-                           cudaStream_t stream) {
+cudaError_t launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const KParams& kp,
+                           int grid, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -691,7 +866,7 @@ cudaError_t launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const
     configured = true;
   }
   const int threads = kp.pull_row_slot != nullptr ? GEMM_THREADS_PULL : GEMM_THREADS;
-  gemm_kernel<EPI><<<grid, threads, SMEM_BYTES, stream>>>(tmA, tmB, kp);
+  gemm_kernel<EPI><<<grid, threads, SMEM_BYTES, stream>>>(tmA, tmB, tmD, kp);
   return cudaGetLastError();
 }
 
@@ -750,6 +925,23 @@ cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   kp.scatter_ld = a.scatter_ld;
   if (a.row_dest != nullptr && (a.epilogue != EPI_STORE || a.d_fp32 || a.accumulate || a.mode == GEMM_GROUPED_K))
     return cudaErrorInvalidValue;
+  // how the EPI_STORE epilogue leaves the SM
+  kp.out_mode = OUT_DIRECT;
+  CUtensorMap tmD = tmA;  // placeholder when no output map is needed
+  if (a.epilogue == EPI_STORE && !direct_epilogue_forced()) {
+    if (a.row_dest != nullptr) {
+      if (a.scatter_ld % 8 == 0) kp.out_mode = OUT_SCATTER;
+    } else if (!(a.accumulate && !a.d_fp32)) {
+      const long long es = a.d_fp32 ? 4 : 2;
+      const long long d_rows = a.mode == GEMM_GROUPED_M ? a.a_rows : a.M;
+      const long long groups = a.mode == GEMM_GROUPED_K ? a.groups : 1;
+      const long long gstride = a.mode == GEMM_GROUPED_K ? a.d_group_stride : d_rows * a.ldd;
+      const bool aligned = (reinterpret_cast<uintptr_t>(a.D) & 15u) == 0 && (a.ldd * es) % 16 == 0 &&
+                           (gstride * es) % 16 == 0 && a.ldd >= a.N && d_rows > 0;
+      if (aligned && make_tmap_out(&tmD, a.D, a.d_fp32, groups, d_rows, a.N, a.ldd, gstride) == cudaSuccess)
+        kp.out_mode = a.accumulate ? OUT_TMA_REDUCE : OUT_TMA_STORE;
+    }
+  }
   kp.ready_flags = a.ready_flags;
   kp.ready_stride = a.ready_stride;
   kp.ready_count = a.ready_count;
@@ -779,11 +971,11 @@ cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream) {
 
   switch (a.epilogue) {
     case EPI_STORE:
-      return launch_variant<EPI_STORE>(tmA, tmB, kp, grid, stream);
+      return launch_variant<EPI_STORE>(tmA, tmB, tmD, kp, grid, stream);
     case EPI_SWIGLU_FWD:
-      return launch_variant<EPI_SWIGLU_FWD>(tmA, tmB, kp, grid, stream);
+      return launch_variant<EPI_SWIGLU_FWD>(tmA, tmB, tmD, kp, grid, stream);
     case EPI_SWIGLU_BWD:
-      return launch_variant<EPI_SWIGLU_BWD>(tmA, tmB, kp, grid, stream);
+      return launch_variant<EPI_SWIGLU_BWD>(tmA, tmB, tmD, kp, grid, stream);
     default:
       return cudaErrorInvalidValue;
   }

@@ -92,7 +92,8 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
                                                                  const __nv_bfloat16* __restrict__ w,
                                                                  const float* __restrict__ rstd,
                                                                  __nv_bfloat16* __restrict__ dx, float* __restrict__ dw,
-                                                                 long long rows, int H) {
+                                                                 float* __restrict__ dw_partial, long long rows,
+                                                                 int H) {
   __shared__ float red[RN_THREADS / 32];
   float wv[VEC][8], dwacc[VEC][8];
 #pragma unroll
@@ -137,7 +138,19 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
       }
     }
   }
-  if (dw) {
+  if (dw_partial) {
+    // one row of partial column sums per CTA, summed by colsum_add_kernel: thousands of CTAs adding atomically to
+    // the same H addresses serialise in L2 and cost more than the whole row pass
+    float* out = dw_partial + static_cast<long long>(blockIdx.x) * H;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const int c = (i * RN_THREADS + threadIdx.x) * 8;
+      if (c < H) {
+        *reinterpret_cast<float4*>(out + c) = make_float4(dwacc[i][0], dwacc[i][1], dwacc[i][2], dwacc[i][3]);
+        *reinterpret_cast<float4*>(out + c + 4) = make_float4(dwacc[i][4], dwacc[i][5], dwacc[i][6], dwacc[i][7]);
+      }
+    }
+  } else if (dw) {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       const int c = (i * RN_THREADS + threadIdx.x) * 8;
@@ -147,6 +160,16 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
       }
     }
   }
+}
+
+// dw[c] += sum_b partial[b, c]; grid (ceil(H / 128), row slices)
+__global__ void __launch_bounds__(128) colsum_add_kernel(const float* __restrict__ partial, float* __restrict__ dw,
+                                                         int n_rows, int H) {
+  const int c = blockIdx.x * 128 + threadIdx.x;
+  if (c >= H) return;
+  float s = 0.f;
+  for (int b = blockIdx.y; b < n_rows; b += gridDim.y) s += partial[static_cast<long long>(b) * H + c];
+  atomicAdd(dw + c, s);
 }
 
 // ------------------------------------------------------------------------------------ RoPE
@@ -582,20 +605,28 @@ cudaError_t launch_rmsnorm_fwd(const void* x, const void* w, void* y, float* rst
   return cudaGetLastError();
 }
 
+long long rmsnorm_bwd_partial_rows(long long rows, int num_sms) {
+  return grid_for(rows, 1, (num_sms > 0 ? num_sms : 148) * 8);
+}
+
 cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw,
-                               long long rows, int H, int num_sms, cudaStream_t stream) {
+                               float* dw_partial, long long rows, int H, int num_sms, cudaStream_t stream) {
   if (H % 8 != 0 || H > RN_THREADS * 8 * 8 || rows <= 0) return cudaErrorInvalidValue;
-  // every CTA ends with H atomics into dw: enough CTAs to hide the row latency, few enough to keep those cheap
-  const unsigned grid = grid_for(rows, 1, (num_sms > 0 ? num_sms : 148) * 8);
+  const unsigned grid = static_cast<unsigned>(rmsnorm_bwd_partial_rows(rows, num_sms));
+  if (dw == nullptr) dw_partial = nullptr;
   auto dyb = reinterpret_cast<const __nv_bfloat16*>(dy);
   auto xb = reinterpret_cast<const __nv_bfloat16*>(x);
   auto wb = reinterpret_cast<const __nv_bfloat16*>(w);
   auto dxb = reinterpret_cast<__nv_bfloat16*>(dx);
   switch (rn_vec_for(H)) {
-    case 1: rmsnorm_bwd_kernel<1><<<grid, RN_THREADS, 0, stream>>>(dyb, xb, wb, rstd, dxb, dw, rows, H); break;
-    case 2: rmsnorm_bwd_kernel<2><<<grid, RN_THREADS, 0, stream>>>(dyb, xb, wb, rstd, dxb, dw, rows, H); break;
-    case 4: rmsnorm_bwd_kernel<4><<<grid, RN_THREADS, 0, stream>>>(dyb, xb, wb, rstd, dxb, dw, rows, H); break;
-    default: rmsnorm_bwd_kernel<8><<<grid, RN_THREADS, 0, stream>>>(dyb, xb, wb, rstd, dxb, dw, rows, H); break;
+    case 1: rmsnorm_bwd_kernel<1><<<grid, RN_THREADS, 0, stream>>>(dyb, xb, wb, rstd, dxb, dw, dw_partial, rows, H); break;
+    case 2: rmsnorm_bwd_kernel<2><<<grid, RN_THREADS, 0, stream>>>(dyb, xb, wb, rstd, dxb, dw, dw_partial, rows, H); break;
+    case 4: rmsnorm_bwd_kernel<4><<<grid, RN_THREADS, 0, stream>>>(dyb, xb, wb, rstd, dxb, dw, dw_partial, rows, H); break;
+    default: rmsnorm_bwd_kernel<8><<<grid, RN_THREADS, 0, stream>>>(dyb, xb, wb, rstd, dxb, dw, dw_partial, rows, H); break;
+  }
+  if (dw_partial != nullptr) {
+    const unsigned slices = grid < 16u ? grid : 16u;
+    colsum_add_kernel<<<dim3((H + 127) / 128, slices), 128, 0, stream>>>(dw_partial, dw, static_cast<int>(grid), H);
   }
   return cudaGetLastError();
 }

@@ -11,9 +11,12 @@ namespace cmoe {
 // y = x * rsqrt(mean(x^2) + eps) * w, fp32 math, bf16 in/out.  rstd [rows] is saved for the backward.
 cudaError_t launch_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int H, float eps,
                                cudaStream_t stream);
-// dx (bf16) and dw (fp32, accumulated with atomics: zero it first unless accumulation is wanted)
+// dx (bf16) and dw (fp32, added to: zero it first unless accumulation is wanted).  With dw_partial (fp32
+// [rmsnorm_bwd_partial_rows(rows, num_sms), H] scratch) every CTA writes its column sums there and a second small
+// kernel adds them to dw; without it the CTAs add to dw with atomics.
+long long rmsnorm_bwd_partial_rows(long long rows, int num_sms);
 cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw,
-                               long long rows, int H, int num_sms, cudaStream_t stream);
+                               float* dw_partial, long long rows, int H, int num_sms, cudaStream_t stream);
 
 // ---- RoPE (rotate-half pairing: element i pairs with i + head_dim/2), in place -----------------
 // t: [batch*seq, heads, head_dim] bf16; cos/sin: [seq, head_dim/2] fp32; position of row r is r % seq.

@@ -61,10 +61,7 @@ class CausalSelfAttention(nn.Module):
         B, S, _ = qkv.shape
         heads = self.nh + 2 * self.nkv
         cos, sin = self._rope_tables(S, qkv.device)
-        t = OF.rope(qkv.reshape(B * S, heads, self.hd), cos, sin, S, self.nh + self.nkv)
-        t = t.view(B, S, heads, self.hd)
-        q, k, v = t[:, :, : self.nh], t[:, :, self.nh: self.nh + self.nkv], t[:, :, self.nh + self.nkv:]
-        o = OF.causal_attention(q, k, v)
+        o = OF.rope_causal_attention(qkv.view(B, S, heads, self.hd), cos, sin, self.nh, self.nkv)
         return self.wo(o.reshape(B, S, self.nh * self.hd))
 
 

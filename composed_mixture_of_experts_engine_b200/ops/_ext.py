@@ -93,6 +93,42 @@ def build(verbose: bool = False, force: bool = False) -> Path:
 
     BUILD_DIR.mkdir(parents=True, exist_ok=True)
     os.environ.setdefault("MAX_JOBS", str(min(8, os.cpu_count() or 4)))
+    with _build_lock():
+        if not force and so.exists() and stamp.exists() and stamp.read_text().strip() == want:
+            return so  # another process built it while this one waited
+        _compile(cpp_extension, verbose)
+        if not so.exists():
+            raise RuntimeError(f"extension build did not produce {so}")
+        stamp.write_text(want)
+    return so
+
+
+class _build_lock:
+    """Inter-process lock on the build directory that dies with its holder (``flock``).
+
+    torch's own build lock is a plain file that outlives a killed build and travels with a copy of the tree; whoever
+    finds it waits forever.  Builds are serialised by this lock instead, and a file left behind by torch's lock is
+    removed while it is held (nobody else can be building then)."""
+
+    def __enter__(self):
+        import fcntl
+
+        self._fh = open(BUILD_DIR / ".flock", "w")
+        fcntl.flock(self._fh, fcntl.LOCK_EX)
+        stale = BUILD_DIR / "lock"
+        if stale.exists():
+            stale.unlink()
+        return self
+
+    def __exit__(self, *exc):
+        import fcntl
+
+        fcntl.flock(self._fh, fcntl.LOCK_UN)
+        self._fh.close()
+        return False
+
+
+def _compile(cpp_extension, verbose: bool) -> None:
     cpp_extension.load(
         name=EXT_NAME,
         sources=[str(s) for s in sources()],
@@ -103,10 +139,6 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         verbose=verbose,
         is_python_module=False,
     )
-    if not so.exists():
-        raise RuntimeError(f"extension build did not produce {so}")
-    stamp.write_text(want)
-    return so
 
 
 IO_LIB = BUILD_DIR / "libcmoe_io.so"

@@ -108,6 +108,59 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch
     return _attn.causal_attention(q, k, v)
 
 
+class _RopeAttentionFn(torch.autograd.Function):
+    """RoPE + causal attention on a packed projection ``qkv`` [B, S, nh + 2 nkv, hd].
+
+    The rotation runs in place on ``qkv`` (the caller hands over the projection's output and must not read it
+    afterwards), the attention kernel reads q / k / v as strided views of the packed buffer, and the backward
+    writes dq / dk / dv straight into one packed gradient and un-rotates it in place.  This replaces the
+    slice / zero-fill / accumulate chain autograd would build around three views of one tensor (three zero
+    fills and two adds of the full packed size per layer)."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, nh, nkv):
+        B, S, heads, hd = qkv.shape
+        _ext.ext().rope(qkv.view(B * S, heads, hd)[:, : nh + nkv], cos, sin, S, False)
+        t = qkv.detach()
+        with torch.enable_grad():
+            q = t[:, :, :nh].permute(0, 2, 1, 3).requires_grad_()
+            k = t[:, :, nh: nh + nkv].permute(0, 2, 1, 3).requires_grad_()
+            v = t[:, :, nh + nkv:].permute(0, 2, 1, 3).requires_grad_()
+            kk, vv = k, v
+            if nkv != nh:
+                kk = k.repeat_interleave(nh // nkv, dim=1)
+                vv = v.repeat_interleave(nh // nkv, dim=1)
+            out = F.scaled_dot_product_attention(q, kk, vv, is_causal=True)
+        ctx.inner = (q, k, v, out)
+        ctx.save_for_backward(cos, sin)
+        ctx.dims = (B, S, heads, hd, nh, nkv)
+        return out.detach().permute(0, 2, 1, 3).contiguous()
+
+    @staticmethod
+    def backward(ctx, go):
+        cos, sin = ctx.saved_tensors
+        B, S, heads, hd, nh, nkv = ctx.dims
+        q, k, v, out = ctx.inner
+        ctx.inner = None
+        dq, dk, dv = torch.autograd.grad(out, (q, k, v), go.permute(0, 2, 1, 3))
+        dqkv = torch.empty(B, S, heads, hd, device=go.device, dtype=go.dtype)
+        dqkv[:, :, :nh].copy_(dq.permute(0, 2, 1, 3))
+        dqkv[:, :, nh: nh + nkv].copy_(dk.permute(0, 2, 1, 3))
+        dqkv[:, :, nh + nkv:].copy_(dv.permute(0, 2, 1, 3))
+        _ext.ext().rope(dqkv.view(B * S, heads, hd)[:, : nh + nkv], cos, sin, S, True)
+        return dqkv, None, None, None, None
+
+
+def rope_causal_attention(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, nh: int, nkv: int) -> torch.Tensor:
+    """``qkv`` [B, S, nh + 2 nkv, hd] (q heads, then k heads, then v heads) -> attention output [B, S, nh, hd] with
+    rotary embedding on q and k.  On the device path ``qkv`` is consumed (rotated in place)."""
+    B, S, heads, hd = qkv.shape
+    if on_device_path(qkv) and hd % 16 == 0 and qkv.is_contiguous():
+        return _RopeAttentionFn.apply(qkv, cos, sin, nh, nkv)
+    t = rope(qkv.reshape(B * S, heads, hd), cos, sin, S, nh + nkv).view(B, S, heads, hd)
+    return causal_attention(t[:, :, :nh], t[:, :, nh: nh + nkv], t[:, :, nh + nkv:])
+
+
 # ------------------------------------------------------------------------------------------ cross-entropy
 class _CrossEntropyFn(torch.autograd.Function):
     @staticmethod
@@ -228,17 +281,49 @@ def grouped_swiglu_backward(dyp: torch.Tensor, xp: torch.Tensor, hact: torch.Ten
     return dxp, dw13, dw2
 
 
+def _local_fused() -> bool:
+    """Gather and combine transfers run inside the grouped GEMMs (default) or as kernels of their own
+    (``CMOE_LOCAL_FUSED=0``)."""
+    import os
+
+    return os.environ.get("CMOE_LOCAL_FUSED", "1") != "0"
+
+
 class _LocalMoEFn(torch.autograd.Function):
-    """Route-sorted expert FFN on one GPU: plan -> gather -> grouped SwiGLU GEMMs -> weighted combine."""
+    """Route-sorted expert FFN on one GPU: plan -> gather -> grouped SwiGLU GEMMs -> weighted combine.
+
+    Fused form (default): the first GEMM of each direction brings its own rows in (row-pull warps reading the token
+    buffer through a one-entry "peer" table, so the gather overlaps the MMAs), and the last GEMM of each direction
+    stores its result rows at their (token, k) slot, which turns the combine into a streaming weighted sum of K
+    consecutive rows instead of an indexed gather."""
 
     @staticmethod
     def forward(ctx, x, gate_w32, idx32, w13, w2, capacity: int, holder: Optional[dict]):
         E = w13.shape[0]
+        N, K = idx32.shape
+        H = x.shape[1]
         plan = kernels.moe_plan(idx32, E, capacity=capacity)
-        xp = kernels.gather_rows(x, plan)
-        hact, gu, yp = grouped_swiglu_forward(xp, w13, w2, plan)
-        y = kernels.combine_rows(yp, plan, gate_w32)
-        ctx.save_for_backward(xp, hact, gu, yp, gate_w32, w13, w2)
+        fused = _local_fused() and H % 8 == 0
+        ctx.fused = fused
+        if fused:
+            x = x.contiguous()
+            xp = torch.empty(plan.cap_rows, H, device=x.device, dtype=torch.bfloat16)
+            slot = plan.row_slot
+            row_dest = torch.stack([torch.where(slot >= 0, 0, -1), slot.clamp(min=0)], dim=1).to(torch.int32).contiguous()
+            ar = torch.arange(N * K, device=x.device, dtype=torch.int32)
+            ident = torch.where(plan.slot_row >= 0, ar, torch.full_like(ar, -1))  # slot -> its own row, -1 if dropped
+            ys = torch.empty(N * K, H, device=x.device, dtype=torch.bfloat16)
+            hact, gu, _ = grouped_swiglu_forward(
+                xp, w13, w2, plan, pull=dict(src_ptrs=[x.data_ptr()], slots_per_src=N * K, pull_K=K, ld_src=H),
+                scatter=dict(row_dest=row_dest, out_ptrs=[ys.data_ptr()], out_ld=H))
+            y = torch.empty(N, H, device=x.device, dtype=torch.bfloat16)
+            _ext.ext().combine_rows(ys, ident, gate_w32, y, K)
+            ctx.save_for_backward(xp, hact, gu, ys, gate_w32, w13, w2, row_dest, ident)
+        else:
+            xp = kernels.gather_rows(x, plan)
+            hact, gu, yp = grouped_swiglu_forward(xp, w13, w2, plan)
+            y = kernels.combine_rows(yp, plan, gate_w32)
+            ctx.save_for_backward(xp, hact, gu, yp, gate_w32, w13, w2)
         ctx.plan = plan
         if holder is not None:
             holder["plan"] = plan
@@ -246,9 +331,31 @@ class _LocalMoEFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        xp, hact, gu, yp, gate_w32, w13, w2 = ctx.saved_tensors
         plan = ctx.plan
         dy = dy.contiguous()
+        if ctx.fused:
+            xp, hact, gu, ys, gate_w32, w13, w2, row_dest, ident = ctx.saved_tensors
+            N, K = gate_w32.shape
+            H = xp.shape[1]
+            ext = _ext.ext()
+            d_gate = None
+            if ctx.needs_input_grad[1]:
+                d_gate = torch.empty(N, K, device=dy.device, dtype=torch.float32)
+                ext.combine_bwd_w(ys, ident, dy, d_gate, K)
+            dyp = torch.empty(plan.cap_rows, H, device=dy.device, dtype=torch.bfloat16)
+            need_dx = ctx.needs_input_grad[0]
+            dxs = torch.empty(N * K, H, device=dy.device, dtype=torch.bfloat16) if need_dx else None
+            _, dw13, dw2 = grouped_swiglu_backward(
+                dyp, xp, hact, gu, w13, w2, plan, need_dx=need_dx,
+                pull=dict(src_ptrs=[dy.data_ptr()], slots_per_src=N * K, pull_K=K, ld_src=H,
+                          slot_scale=gate_w32.reshape(-1)),
+                scatter=dict(row_dest=row_dest, out_ptrs=[dxs.data_ptr()], out_ld=H) if need_dx else None)
+            dx = None
+            if need_dx:
+                dx = torch.empty(N, H, device=dy.device, dtype=torch.bfloat16)
+                ext.combine_rows(dxs, ident, None, dx, K)
+            return dx, d_gate, None, dw13, dw2, None, None
+        xp, hact, gu, yp, gate_w32, w13, w2 = ctx.saved_tensors
         d_gate = kernels.combine_bwd_w(yp, plan, dy) if ctx.needs_input_grad[1] else None
         dyp = kernels.gather_rows(dy, plan, slot_scale=gate_w32.reshape(-1))
         dxp, dw13, dw2 = grouped_swiglu_backward(dyp, xp, hact, gu, w13, w2, plan, need_dx=ctx.needs_input_grad[0])

@@ -5,9 +5,10 @@ GEMM kernel itself pulls the rows of all shards (four extra warps per CTA, plain
 pipeline consumes the tiles that have landed, so the all-gather overlaps the GEMM tile by tile and the gathered
 activation is written exactly once (it is also what the weight gradient needs later).
 
-``linear_reduce_scatter``: the GEMM writes this rank's partial result into a symmetric buffer; after a barrier each
-rank pulls the partial rows of its own sequence shard from every peer and sums them in fp32 (one kernel, no bf16
-reduction tree, no intermediate all-reduce buffer).
+``linear_reduce_scatter``: the GEMM's epilogue stores every partial result row straight into a staging slab on the
+rank that owns that sequence position (plain P2P stores, so the scatter overlaps the MMAs of later tiles); after
+one barrier each rank sums the ``tp`` slabs it received in fp32 from its own memory.  ``CMOE_TP_PUSH=0`` keeps the
+partial result local and lets each rank pull and sum the rows of its shard instead.
 
 Both are differentiable; the backward of one is the forward pattern of the other.  Replaces call sites C4-C7
 (pkg/distributed/tensor_parallel.py:128,201-206; sequence_parallel.py:131,165).
@@ -15,6 +16,7 @@ Both are differentiable; the backward of one is the forward pattern of the other
 
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Tuple
 
 import torch
@@ -33,6 +35,7 @@ class _TPContext:
         self.flag_ptrs = [int(p) for p in self.sg.flags.handle.buffer_ptrs]
         self._bufs: Dict[str, symm.SymmBuffer] = {}
         self._plans: Dict[Tuple[int, int], Tuple[MoEPlan, torch.Tensor]] = {}
+        self._scatter: Dict[Tuple[int, int], Tuple[torch.Tensor, torch.Tensor]] = {}
 
     def barrier(self) -> None:
         self.sg.epoch += 1
@@ -67,6 +70,22 @@ class _TPContext:
         own = (b * (tp * s_local) + self.rank * s_local + s).expand(batch, 1, s_local).reshape(-1).to(torch.int32)
         self._plans[key] = (plan, own.contiguous())
         return self._plans[key]
+
+    def scatter_plan(self, batch: int, s_local: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """(row_dest [batch*tp*s_local, 2], identity row map [batch*s_local]): full row (b, r, s) of this rank's
+        partial result goes to rank r, row  rank * batch*s_local + b*s_local + s  of its staging buffer."""
+        key = (batch, s_local)
+        hit = self._scatter.get(key)
+        if hit is None:
+            dev, tp = self.topo.device, self.world
+            b = torch.arange(batch, device=dev).view(batch, 1, 1)
+            r = torch.arange(tp, device=dev).view(1, tp, 1)
+            s = torch.arange(s_local, device=dev).view(1, 1, s_local)
+            row = (self.rank * (batch * s_local) + b * s_local + s).expand(batch, tp, s_local)
+            dest = torch.stack([r.expand(batch, tp, s_local), row], dim=-1).reshape(-1, 2).to(torch.int32).contiguous()
+            hit = (dest, torch.arange(batch * s_local, device=dev, dtype=torch.int32))
+            self._scatter[key] = hit
+        return hit
 
 
 _CTX: Dict[tuple, _TPContext] = {}
@@ -122,6 +141,31 @@ def _partial_gemm(c: _TPContext, x2d: torch.Tensor, weight: torch.Tensor, b_mn: 
     return part
 
 
+def _push() -> bool:
+    return os.environ.get("CMOE_TP_PUSH", "1") != "0"
+
+
+def _gemm_reduce_scatter(c: _TPContext, x2d: torch.Tensor, weight: torch.Tensor, b_mn: bool, batch: int,
+                         s_local: int, name: str) -> torch.Tensor:
+    """Sequence shard of  sum over ranks of (x2d @ W)  with the scatter fused into the GEMM epilogue."""
+    if not _push():
+        return _reduce_scattered(c, _partial_gemm(c, x2d, weight, b_mn, name), batch, s_local, name)
+    rows = x2d.shape[0]
+    N = weight.shape[1] if b_mn else weight.shape[0]
+    shard_rows = batch * s_local
+    dest, ident = c.scatter_plan(batch, s_local)
+    stage = c.buf(name + ".stage", c.world * shard_rows * N * 2)
+    c.barrier()  # every rank has finished reading its slabs of the previous call
+    kernels.gemm_scatter(x2d, weight, N=N, K=x2d.shape[1], row_dest=dest, out_ptrs=_ptrs(stage), out_ld=N, b_mn=b_mn,
+                         M=rows)
+    c.barrier()
+    out = torch.empty(shard_rows, N, device=x2d.device, dtype=torch.bfloat16)
+    base = stage.local.data_ptr()
+    slabs = [base + j * shard_rows * N * 2 for j in range(c.world)]  # all local: the partial sums are already here
+    _ext.ext().reduce_rows_peer(slabs, ident, out, N)
+    return out
+
+
 class _AllGatherLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, c: _TPContext):
@@ -138,8 +182,8 @@ class _AllGatherLinear(torch.autograd.Function):
         dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
         dx = None
         if ctx.needs_input_grad[0]:
-            part = _partial_gemm(c, dy2, weight, True, "ag_dx")  # dy [rows, out_l] @ W [out_l, in]
-            dx = _reduce_scattered(c, part, B, S_l, "ag_dx").view(B, S_l, -1)
+            # dy [rows, out_l] @ W [out_l, in], summed over ranks, this rank's sequence shard
+            dx = _gemm_reduce_scatter(c, dy2, weight, True, B, S_l, "ag_dx").view(B, S_l, -1)
         dw = kernels.linear_tn(dy2, full).to(weight.dtype) if ctx.needs_input_grad[1] else None
         return dx, dw, None
 
@@ -150,8 +194,7 @@ class _LinearReduceScatter(torch.autograd.Function):
         B, S, Kdim = x.shape
         S_l = S // c.world
         x2 = x.reshape(B * S, Kdim).contiguous()
-        part = _partial_gemm(c, x2, weight, False, "rs_y")
-        y = _reduce_scattered(c, part, B, S_l, "rs_y")
+        y = _gemm_reduce_scatter(c, x2, weight, False, B, S_l, "rs_y")
         ctx.save_for_backward(x2, weight)
         ctx.c, ctx.dims = c, (B, S_l)
         return y.view(B, S_l, weight.shape[0])

@@ -200,12 +200,19 @@ def trainer_steps(rank, world, config_path, steps):
 
 
 # -------------------------------------------------------------------------------------------------- GPU workers
+def _set_transport(transport):
+    """"nccl", "auto" (peer memory, results pushed by the GEMM epilogues) or "auto-pull" (peer memory, pulled)."""
+    push = "0" if transport.endswith("-pull") else "1"
+    os.environ["CMOE_EP_PUSH"] = os.environ["CMOE_TP_PUSH"] = push
+    os.environ["CMOE_EP_TRANSPORT"] = transport.replace("-pull", "")
+
+
 def gpu_ep_layer(rank, world, transport):
     """bf16 expert-parallel layer on `world` GPUs vs the same layer with all experts on one GPU."""
     import torch
     import torch.distributed as dist
 
-    os.environ["CMOE_EP_TRANSPORT"] = transport
+    _set_transport(transport)
     from composed_mixture_of_experts_engine_b200.ops.kernels import check_status
     from composed_mixture_of_experts_engine_b200.parallel import DistributedMoELayer, build_topology
 
@@ -271,11 +278,12 @@ def gpu_trainer(rank, world, transport, steps):
             "n_local": len(tr.model.blocks[0].moe.local_expert_ids)}
 
 
-def gpu_tp_sp(rank, world):
+def gpu_tp_sp(rank, world, transport="auto"):
     """Sequence-parallel column -> SiLU -> row pair over tp=world GPUs on the peer-memory path vs unsharded."""
     import torch
     import torch.nn.functional as F
 
+    _set_transport(transport)
     from composed_mixture_of_experts_engine_b200.ops.kernels import check_status
     from composed_mixture_of_experts_engine_b200.parallel import (ColumnParallelLinear, RowParallelLinear,
                                                                   build_topology, gather_from_sequence_parallel,

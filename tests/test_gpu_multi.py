@@ -51,7 +51,7 @@ def _world():
     return 4 if n >= 4 else 2
 
 
-@pytest.mark.parametrize("transport", ["nccl", "auto"])
+@pytest.mark.parametrize("transport", ["nccl", "auto", "auto-pull"])
 def test_ep_layer_matches_single_gpu(transport):
     res = _spawn_gpu("gpu_ep_layer", _world(), transport)
     for r, out in res.items():
@@ -68,8 +68,9 @@ def test_trainer_multi_gpu(transport):
         assert out["sync"] == 0.0 and out["ep"] == _world()
 
 
-def test_sequence_parallel_linears_on_peer_memory():
-    res = _spawn_gpu("gpu_tp_sp", 2)
+@pytest.mark.parametrize("transport", ["auto", "auto-pull"])
+def test_sequence_parallel_linears_on_peer_memory(transport):
+    res = _spawn_gpu("gpu_tp_sp", 2, transport)
     for r, out in res.items():
         for k, v in out.items():
             assert v < 4e-2, (r, k, v, out)

@@ -29,11 +29,13 @@ def _write_cfg(tmp_path: Path, arch: str, max_steps: int) -> Path:
 
 
 @pytest.mark.parametrize("arch", ["toy_moe", "moe_decoder"])
-def test_train_main_writes_telemetry_and_both_tiers_then_resumes(tmp_path, arch):
+def test_train_main_writes_telemetry_and_both_tiers_then_resumes(tmp_path, arch, monkeypatch):
     import train
 
+    monkeypatch.setenv("MOE_PROFILE_DIR", str(tmp_path / "profile"))
     cfg = _write_cfg(tmp_path, arch, max_steps=4)
     assert train.main(["--config", str(cfg), "--no-wandb", "--cpu", "--profile"]) == 0
+    assert len(list((tmp_path / "profile").glob("run_*_rank0.json"))) == 1
     lines = [json.loads(l) for l in (tmp_path / "logs" / "step.jsonl").read_text().splitlines()]
     assert [l["step"] for l in lines] == [0, 1, 2, 3]
     rec = lines[-1]

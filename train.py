@@ -214,8 +214,8 @@ def main(argv=None) -> int:
         check_status(trainer.device)
     logger.close()
     if args.profile and rank == 0 and profile_rows:
-        out_dir = ROOT / "benchmarks"
-        out_dir.mkdir(exist_ok=True)
+        out_dir = Path(os.environ.get("MOE_PROFILE_DIR", str(ROOT / "benchmarks")))
+        out_dir.mkdir(parents=True, exist_ok=True)
         ms = sorted(r["step_ms"] for r in profile_rows)
         summary = {"steps": profile_rows, "mean_step_ms": sum(ms) / len(ms), "p50_step_ms": ms[len(ms) // 2],
                    "mfu_summary": mfu_acct.summary_str()}
