@@ -167,7 +167,9 @@ __device__ __forceinline__ Tile decode_tile(const KParams& p, int t, int m_tiles
   return ti;
 }
 
-__device__ __forceinline__ float sigmoidf_fast(float x) { return 1.0f / (1.0f + __expf(-x)); }
+// ex2.approx + rcp.approx: two special-function instructions instead of an IEEE division (the epilogue warps are
+// issue-bound: one warp per scheduler, so every instruction saved per element shortens the tile)
+__device__ __forceinline__ float sigmoidf_fast(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
 // 32 fp32 values of one output row -> bf16 (or fp32) in global memory, columns [col, col+32) masked by n_limit
 __device__ __forceinline__ void store_row_chunk(void* D, long long ldd, int d_fp32, int accumulate, long long row,
@@ -224,16 +226,33 @@ __device__ __forceinline__ void prefetch_f32_chunk(const float* row_ptr, int col
   }
 }
 
-// gate and up values (bf16) of one row for columns [col, col + 32): gate at row_ptr[col], up at row_ptr[N + col]
-__device__ __forceinline__ void prefetch_gu_chunk(const __nv_bfloat16* row_ptr, int col, int n, bool row_ok,
-                                                  uint4 (&g)[4], uint4 (&u)[4]) {
+// SwiGLU backward for 32 columns of one row: dH (fp32 bits in r) with the saved gate / up values (bf16 in cg / cu)
+// -> dGate at D[row, col..] and dUp at D[row, N + col..].  Eight columns at a time, straight from the packed
+// inputs to the packed outputs; columns past N hold garbage and are not stored.
+__device__ __forceinline__ void swiglu_bwd_chunk(const uint32_t (&r)[32], const uint4 (&cg)[4], const uint4 (&cu)[4],
+                                                 int col, int N, void* Dg, long long ldd, long long row) {
+  __nv_bfloat16* dgp = reinterpret_cast<__nv_bfloat16*>(Dg) + row * ldd + col;
+  __nv_bfloat16* dup = dgp + N;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    g[j] = make_uint4(0u, 0u, 0u, 0u);
-    u[j] = make_uint4(0u, 0u, 0u, 0u);
-    if (row_ok && col + j * 8 < n) {
-      g[j] = *reinterpret_cast<const uint4*>(row_ptr + col + j * 8);
-      u[j] = *reinterpret_cast<const uint4*>(row_ptr + n + col + j * 8);
+    const uint32_t gw[4] = {cg[j].x, cg[j].y, cg[j].z, cg[j].w};
+    const uint32_t uw[4] = {cu[j].x, cu[j].y, cu[j].z, cu[j].w};
+    uint32_t og[4], ou[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float2 g = unpack_bf16x2(gw[q]);
+      const float2 u = unpack_bf16x2(uw[q]);
+      const float dh0 = __uint_as_float(r[8 * j + 2 * q]), dh1 = __uint_as_float(r[8 * j + 2 * q + 1]);
+      const float s0 = sigmoidf_fast(g.x), s1 = sigmoidf_fast(g.y);
+      // d silu(g)/dg = s (1 + g (1 - s))
+      const float dg0 = dh0 * u.x * (s0 * fmaf(g.x, 1.f - s0, 1.f));
+      const float dg1 = dh1 * u.y * (s1 * fmaf(g.y, 1.f - s1, 1.f));
+      og[q] = pack_bf16x2(dg0, dg1);
+      ou[q] = pack_bf16x2(dh0 * (g.x * s0), dh1 * (g.y * s1));
+    }
+    if (col + j * 8 < N) {  // N is a multiple of 8
+      *reinterpret_cast<uint4*>(dgp + j * 8) = make_uint4(og[0], og[1], og[2], og[3]);
+      *reinterpret_cast<uint4*>(dup + j * 8) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
     }
   }
 }
@@ -252,7 +271,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint64_t* empty_bar = bars + STAGES;       // [STAGES]
   uint64_t* tfull_bar = bars + 2 * STAGES;   // [2]
   uint64_t* tempty_bar = bars + 2 * STAGES + 2;  // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  uint64_t* gfull_bar = bars + 2 * STAGES + 4;   // [2] saved gate/up pieces landed (SwiGLU backward)
+  uint64_t* gempty_bar = bars + 2 * STAGES + 6;  // [2] ... and were consumed by all epilogue threads
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -267,10 +288,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
       mbar_init(&tempty_bar[a], 128);
+      mbar_init(&gfull_bar[a], 1);
+      mbar_init(&gempty_bar[a], 128);
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmD);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -460,6 +484,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
         continue;
       }
+      // SwiGLU backward: pieces of 128 rows x 32 columns of the saved gate and up values are brought into the
+      // staging area by TMA, one piece ahead of the one being processed; the first piece of a tile is requested
+      // before the wait for its accumulator
+      auto gu_issue = [&](uint32_t ctr, int col) {
+        const uint32_t b = ctr & 1u;
+        if (!mbar_wait(&gempty_bar[b], ((ctr >> 1) & 1u) ^ 1u, wc, ST_TIMEOUT_SMEM_EMPTY)) return;
+        uint8_t* dst = stg + b * STAGING_BUF_BYTES;
+        mbar_arrive_expect_tx(&gfull_bar[b], STAGING_BUF_BYTES);
+        tma_load_2d(dst, &tmD, &gfull_bar[b], col, ti.m0);
+        tma_load_2d(dst + STAGING_BUF_BYTES / 2, &tmD, &gfull_bar[b], p.N + col, ti.m0);
+      };
+      if (EPI == EPI_SWIGLU_BWD && threadIdx.x == EPI_FIRST_THREAD) gu_issue(stage_ctr, ti.n0);
       const bool ok = mbar_wait(&tfull_bar[acc], acc_phase, wc, ST_TIMEOUT_TMEM_FULL);
       tc_fence_after();
       const uint32_t t_acc = tmem_base + acc * BN + lane_base;
@@ -643,51 +679,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               }
             }
           }
-        } else {  // EPI_SWIGLU_BWD: acc = dH; D = [dGate | dUp] with row stride ldd (>= 2N)
-          const __nv_bfloat16* gurow = p.aux_in + row * p.ld_aux_in;
-          uint4 cg[4], cu[4], ng[4], nu[4];
-          prefetch_gu_chunk(gurow, ti.n0, p.N, row_ok, cg, cu);
+        }
+      }
+      if (EPI == EPI_SWIGLU_BWD) {
+        // acc = dH; D = [dGate | dUp] with row stride ldd (>= 2N).  Runs whether or not the accumulator wait succeeded, so that every requested piece is also consumed
+        const int gsw = (row_in_tile >> 1) & 3;  // 64-byte swizzle: 16-byte chunk j of row r sits at j ^ ((r / 2) % 4)
 #pragma unroll 1
-          for (int c = 0; c < BN / 32; ++c) {
-            const int col = ti.n0 + c * 32;
-            if (col >= p.N) break;
-            uint32_t r[32];
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col = ti.n0 + c * 32;
+          if (col >= p.N) break;
+          if (threadIdx.x == EPI_FIRST_THREAD && c + 1 < BN / 32 && col + 32 < p.N) gu_issue(stage_ctr + 1, col + 32);
+          const uint32_t b = stage_ctr & 1u;
+          const bool got = mbar_wait(&gfull_bar[b], (stage_ctr >> 1) & 1u, wc, ST_TIMEOUT_SMEM_FULL);
+          uint32_t r[32];
+          if (ok) {
             tmem_ld_32x32b_x32(t_acc + c * 32, r);
-            prefetch_gu_chunk(gurow, col + 32, p.N, row_ok, ng, nu);  // next chunk's gate/up while this one computes
             tmem_ld_wait();
-            if (row_ok) {
-              float g[32], u[32], dg[32], du[32];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const bool in = (col + j * 8) < p.N;  // N is a multiple of 8
-                const float2 g0 = unpack_bf16x2(cg[j].x), g1 = unpack_bf16x2(cg[j].y), g2 = unpack_bf16x2(cg[j].z),
-                             g3 = unpack_bf16x2(cg[j].w);
-                const float2 u0 = unpack_bf16x2(cu[j].x), u1 = unpack_bf16x2(cu[j].y), u2 = unpack_bf16x2(cu[j].z),
-                             u3 = unpack_bf16x2(cu[j].w);
-                g[8 * j] = in ? g0.x : 0.f; g[8 * j + 1] = in ? g0.y : 0.f; g[8 * j + 2] = in ? g1.x : 0.f;
-                g[8 * j + 3] = in ? g1.y : 0.f; g[8 * j + 4] = in ? g2.x : 0.f; g[8 * j + 5] = in ? g2.y : 0.f;
-                g[8 * j + 6] = in ? g3.x : 0.f; g[8 * j + 7] = in ? g3.y : 0.f;
-                u[8 * j] = in ? u0.x : 0.f; u[8 * j + 1] = in ? u0.y : 0.f; u[8 * j + 2] = in ? u1.x : 0.f;
-                u[8 * j + 3] = in ? u1.y : 0.f; u[8 * j + 4] = in ? u2.x : 0.f; u[8 * j + 5] = in ? u2.y : 0.f;
-                u[8 * j + 6] = in ? u3.x : 0.f; u[8 * j + 7] = in ? u3.y : 0.f;
-              }
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const float dh = __uint_as_float(r[j]);
-                const float s = sigmoidf_fast(g[j]);
-                const float silu = g[j] * s;
-                dg[j] = dh * u[j] * (s * (1.f + g[j] * (1.f - s)));
-                du[j] = dh * silu;
-              }
-              store_row_chunk(Dg, p.ldd, 0, 0, row, col, p.N, dg);
-              store_row_chunk(reinterpret_cast<__nv_bfloat16*>(Dg) + p.N, p.ldd, 0, 0, row, col, p.N, du);
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              cg[j] = ng[j];
-              cu[j] = nu[j];
-            }
           }
+          uint4 cg[4], cu[4];
+          const uint8_t* grow = stg + b * STAGING_BUF_BYTES + row_in_tile * 64;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            cg[j] = *reinterpret_cast<const uint4*>(grow + ((j ^ gsw) << 4));
+            cu[j] = *reinterpret_cast<const uint4*>(grow + STAGING_BUF_BYTES / 2 + ((j ^ gsw) << 4));
+          }
+          mbar_arrive(&gempty_bar[b]);
+          if (ok && got && row_ok) swiglu_bwd_chunk(r, cg, cu, col, p.N, Dg, p.ldd, row);
+          ++stage_ctr;
         }
       }
       tc_fence_before();
@@ -739,9 +757,10 @@ EncodeTiledFn get_encode_fn() {
 struct TmapKey {
   const void* ptr;
   long long rows, cols, ld;
-  int box_rows;
+  int box_rows, box_cols;
   bool operator==(const TmapKey& o) const {
-    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows &&
+           box_cols == o.box_cols;
   }
 };
 struct TmapKeyHash {
@@ -751,15 +770,19 @@ struct TmapKeyHash {
     h = h * 1000003u ^ static_cast<size_t>(k.cols);
     h = h * 1000003u ^ static_cast<size_t>(k.ld);
     h = h * 1000003u ^ static_cast<size_t>(k.box_rows);
+    h = h * 1000003u ^ static_cast<size_t>(k.box_cols);
     return h;
   }
 };
 
-// bf16 row-major [rows, cols] (leading dimension ld), box = 64 columns x box_rows rows, 128-byte swizzle
-cudaError_t make_tmap(CUtensorMap* out, const void* ptr, long long rows, long long cols, long long ld, int box_rows) {
+// bf16 row-major [rows, cols] (leading dimension ld), box = box_cols columns x box_rows rows; 64 columns use the
+// 128-byte swizzle (operands), 32 columns the 64-byte swizzle (epilogue pieces)
+cudaError_t make_tmap(CUtensorMap* out, const void* ptr, long long rows, long long cols, long long ld, int box_rows,
+                      int box_cols = 64) {
   static std::mutex mu;
   static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
-  TmapKey key{ptr, rows, cols, ld, box_rows};
+  if (box_cols != 64 && box_cols != 32) return cudaErrorInvalidValue;
+  TmapKey key{ptr, rows, cols, ld, box_rows, box_cols};
   {
     std::lock_guard<std::mutex> lk(mu);
     auto it = cache.find(key);
@@ -774,11 +797,12 @@ cudaError_t make_tmap(CUtensorMap* out, const void* ptr, long long rows, long lo
     return cudaErrorInvalidValue;
   cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
   cuuint64_t gstride[1] = {static_cast<cuuint64_t>(ld) * 2};
-  cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estride[2] = {1u, 1u};
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estride,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     std::fprintf(stderr, "cmoe: cuTensorMapEncodeTiled failed (%d) rows=%lld cols=%lld ld=%lld box_rows=%d\n",
                  static_cast<int>(r), rows, cols, ld, box_rows);
@@ -941,6 +965,13 @@ cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream) {
       if (aligned && make_tmap_out(&tmD, a.D, a.d_fp32, groups, d_rows, a.N, a.ldd, gstride) == cudaSuccess)
         kp.out_mode = a.accumulate ? OUT_TMA_REDUCE : OUT_TMA_STORE;
     }
+  }
+  if (a.epilogue == EPI_SWIGLU_BWD) {
+    // the saved gate|up matrix [rows, 2N] comes into the epilogue through TMA (pieces of 128 rows x 32 columns)
+    if (a.aux_in == nullptr || a.ld_aux_in < 2LL * a.N) return cudaErrorInvalidValue;
+    const long long aux_rows = a.mode == GEMM_GROUPED_M ? a.a_rows : a.M;
+    e = make_tmap(&tmD, a.aux_in, aux_rows, 2LL * a.N, a.ld_aux_in, BM, 32);
+    if (e != cudaSuccess) return e;
   }
   kp.ready_flags = a.ready_flags;
   kp.ready_stride = a.ready_stride;

@@ -282,17 +282,18 @@ def grouped_swiglu_backward(dyp: torch.Tensor, xp: torch.Tensor, hact: torch.Ten
 
 
 def _local_fused() -> bool:
-    """Gather and combine transfers run inside the grouped GEMMs (default) or as kernels of their own
-    (``CMOE_LOCAL_FUSED=0``)."""
+    """Gather and combine transfers run as kernels of their own (default) or inside the grouped GEMMs
+    (``CMOE_LOCAL_FUSED=1``; measured slightly slower on one B200: the row-pull warps cost the GEMM about what the
+    separate gather kernel costs)."""
     import os
 
-    return os.environ.get("CMOE_LOCAL_FUSED", "1") != "0"
+    return os.environ.get("CMOE_LOCAL_FUSED", "0") != "0"
 
 
 class _LocalMoEFn(torch.autograd.Function):
     """Route-sorted expert FFN on one GPU: plan -> gather -> grouped SwiGLU GEMMs -> weighted combine.
 
-    Fused form (default): the first GEMM of each direction brings its own rows in (row-pull warps reading the token
+    Fused form (``CMOE_LOCAL_FUSED=1``): the first GEMM of each direction brings its own rows in (row-pull warps reading the token
     buffer through a one-entry "peer" table, so the gather overlaps the MMAs), and the last GEMM of each direction
     stores its result rows at their (token, k) slot, which turns the combine into a streaming weighted sum of K
     consecutive rows instead of an indexed gather."""

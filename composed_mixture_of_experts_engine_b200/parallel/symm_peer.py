@@ -7,16 +7,18 @@ Per layer call, on one stream, with no host round trip:
               pull every rank's idx and w (a few hundred KB)       peer_allgather
               row plan of the local experts over all ranks' slots  moe_plan  (slot -> row table lands in symmetric memory)
               pull the rows that route here, expert-sorted         gather_rows_peer   <- the dispatch, P2P loads over NVLink
-              grouped SwiGLU GEMMs (tcgen05), yp into a symmetric buffer
+              grouped SwiGLU GEMMs (tcgen05); the epilogue of the second one copies every finished row out of its
+              staging area straight into the buffer of the rank that owns the token (coalesced P2P stores that
+              overlap the MMAs of later tiles)                          <- the combine transfer
               barrier
-              y[t] = sum_k w * yp[owner][row]                      combine_rows_peer  <- the combine, P2P loads
-    backward  publish dy; barrier; d(gate) by dot products against the owners' yp rows; pull dy rows (scaled by
-              the gate weights) inside the dgrad GEMM; dxp into a symmetric buffer; barrier; dx[t] = sum_k dxp
+              y[t] = sum_k w * ycomb[t*K+k]                        combine_rows_peer on local rows
+    backward  publish dy; barrier; d(gate) by dot products against the local ycomb rows; pull dy rows (scaled by
+              the gate weights) inside the dgrad GEMM; the dX GEMM pushes its rows to the token owners; barrier;
+              dx[t] = sum_k dxcomb[t*K+k]
 
-``CMOE_EP_PUSH=1`` moves the combine transfer into the GEMM epilogues instead: the second forward GEMM and the dX
-GEMM copy every finished row out of their staging area straight into the buffer of the rank that owns the token
-(coalesced P2P stores, overlapping the MMAs of later tiles), and the combine kernels then read local memory only.
-``CMOE_EP_FUSED=0`` turns the dispatch into a separate pull kernel.
+``CMOE_EP_PUSH=0`` keeps the results on the expert's rank and lets the combine kernels pull them instead (measured
+slower: 178.6 K against 188.6 K tokens/s on the two-GPU training benchmark); ``CMOE_EP_FUSED=0`` turns the dispatch
+into a separate pull kernel.
 
 Nothing is gathered that is not needed, nothing is reduced in bf16, and no buffer is materialised twice (the
 library transport all-gathers x and reduce-scatters a [ep*T, H] partial result).  Barriers are flag words in
@@ -56,8 +58,8 @@ def available(topology: Optional[ParallelTopology], axis: str) -> bool:
 
 
 def _push() -> bool:
-    """Result rows are pushed to the token owners by the GEMM epilogue (``CMOE_EP_PUSH=1``) or pulled by the combine kernel (default)."""
-    return os.environ.get("CMOE_EP_PUSH", "0") != "0"
+    """Result rows are pushed to the token owners by the GEMM epilogue (default) or pulled by the combine kernel (``CMOE_EP_PUSH=0``)."""
+    return os.environ.get("CMOE_EP_PUSH", "1") != "0"
 
 
 def _row_dest(row_slot: torch.Tensor, slots_per_rank: int) -> torch.Tensor:
