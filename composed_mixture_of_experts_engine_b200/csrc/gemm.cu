@@ -411,37 +411,53 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int pw = warp - 6;  // 0..3: each warp brings in 32 of the 128 rows of a tile
       for (int mt = blockIdx.x; mt < m_tiles; mt += gridDim.x) {
         if (p.tile_group[mt] >= 0) {
-          for (int i = 0; i < 32; ++i) {
-            const long long r = static_cast<long long>(mt) * BM + pw * 32 + i;
-            const int slot = p.pull_row_slot[r];
-            __nv_bfloat16* o = p.pull_dst + r * p.pull_ld_dst;
-            if (slot < 0) {
-              for (int c = lane * 8; c < p.pull_cols; c += 256)
-                *reinterpret_cast<uint4*>(o + c) = make_uint4(0u, 0u, 0u, 0u);
-              continue;
+          // Two rows at a time and up to eight 16-byte loads per lane and row in flight (16 KiB per warp): remote
+          // loads over NVLink take microseconds, so the transfer rate is set by the bytes in flight
+          for (int i = 0; i < 32; i += 2) {
+            const long long r0 = static_cast<long long>(mt) * BM + pw * 32 + i;
+            int slot[2];
+            const __nv_bfloat16* src[2];
+            float sc[2];
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              slot[q] = p.pull_row_slot[r0 + q];
+              src[q] = nullptr;
+              sc[q] = 1.f;
+              if (slot[q] >= 0) {
+                const int src_rank = static_cast<int>(slot[q] / p.pull_slots_per_src);
+                const long long tok = (slot[q] - src_rank * p.pull_slots_per_src) / p.pull_K;
+                src[q] = reinterpret_cast<const __nv_bfloat16*>(p.pull_src.ptr[src_rank]) + tok * p.pull_ld_src;
+                if (p.pull_slot_scale) sc[q] = p.pull_slot_scale[slot[q]];
+              }
             }
-            const int src_rank = static_cast<int>(slot / p.pull_slots_per_src);
-            const long long tok = (slot - src_rank * p.pull_slots_per_src) / p.pull_K;
-            const __nv_bfloat16* s =
-                reinterpret_cast<const __nv_bfloat16*>(p.pull_src.ptr[src_rank]) + tok * p.pull_ld_src;
-            const float sc = p.pull_slot_scale ? p.pull_slot_scale[slot] : 1.f;
-            for (int c0 = lane * 8; c0 < p.pull_cols; c0 += 1024) {
-              uint4 v[4];
+            for (int c0 = lane * 8; c0 < p.pull_cols; c0 += 2048) {
+              uint4 v[2][8];
 #pragma unroll
-              for (int j = 0; j < 4; ++j)
-                if (c0 + j * 256 < p.pull_cols) v[j] = *reinterpret_cast<const uint4*>(s + c0 + j * 256);
+              for (int q = 0; q < 2; ++q) {
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                if (c0 + j * 256 < p.pull_cols) {
-                  if (p.pull_slot_scale) {
-                    const float2 a = unpack_bf16x2(v[j].x), b = unpack_bf16x2(v[j].y), c = unpack_bf16x2(v[j].z),
-                                 d = unpack_bf16x2(v[j].w);
-                    v[j].x = pack_bf16x2(a.x * sc, a.y * sc);
-                    v[j].y = pack_bf16x2(b.x * sc, b.y * sc);
-                    v[j].z = pack_bf16x2(c.x * sc, c.y * sc);
-                    v[j].w = pack_bf16x2(d.x * sc, d.y * sc);
+                for (int j = 0; j < 8; ++j) {
+                  v[q][j] = make_uint4(0u, 0u, 0u, 0u);  // padding rows are zero filled
+                  if (src[q] != nullptr && c0 + j * 256 < p.pull_cols)
+                    v[q][j] = *reinterpret_cast<const uint4*>(src[q] + c0 + j * 256);
+                }
+              }
+#pragma unroll
+              for (int q = 0; q < 2; ++q) {
+                __nv_bfloat16* o = p.pull_dst + (r0 + q) * p.pull_ld_dst;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  if (c0 + j * 256 < p.pull_cols) {
+                    uint4 w = v[q][j];
+                    if (p.pull_slot_scale) {
+                      const float2 a = unpack_bf16x2(w.x), b = unpack_bf16x2(w.y), c = unpack_bf16x2(w.z),
+                                   d = unpack_bf16x2(w.w);
+                      w.x = pack_bf16x2(a.x * sc[q], a.y * sc[q]);
+                      w.y = pack_bf16x2(b.x * sc[q], b.y * sc[q]);
+                      w.z = pack_bf16x2(c.x * sc[q], c.y * sc[q]);
+                      w.w = pack_bf16x2(d.x * sc[q], d.y * sc[q]);
+                    }
+                    *reinterpret_cast<uint4*>(o + c0 + j * 256) = w;
                   }
-                  *reinterpret_cast<uint4*>(o + c0 + j * 256) = v[j];
                 }
               }
             }

@@ -106,6 +106,20 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
     }
     if (c < H) load8(w + c, wv[i]);
   }
+  // the raw 16-byte pieces of the next row are requested before the block-wide reduction of the current one, so a
+  // CTA always has two rows in flight
+  uint4 nx[VEC], nd[VEC];
+  auto fetch = [&](long long row) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const int c = (i * RN_THREADS + threadIdx.x) * 8;
+      if (row < rows && c < H) {
+        nx[i] = __ldcs(reinterpret_cast<const uint4*>(x + row * H + c));
+        nd[i] = __ldcs(reinterpret_cast<const uint4*>(dy + row * H + c));
+      }
+    }
+  };
+  fetch(blockIdx.x);
   for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
     const float r = rstd[row];
     float xh[VEC][8], g[VEC][8];
@@ -114,18 +128,22 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
     for (int i = 0; i < VEC; ++i) {
       const int c = (i * RN_THREADS + threadIdx.x) * 8;
       if (c < H) {
-        float xv[8], dv[8];
-        load8(x + row * H + c, xv);
-        load8(dy + row * H + c, dv);
+        const uint32_t xw[4] = {nx[i].x, nx[i].y, nx[i].z, nx[i].w};
+        const uint32_t dw4[4] = {nd[i].x, nd[i].y, nd[i].z, nd[i].w};
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          xh[i][j] = xv[j] * r;
-          g[i][j] = dv[j] * wv[i][j];
-          dot += g[i][j] * xh[i][j];
-          dwacc[i][j] += dv[j] * xh[i][j];
+        for (int q = 0; q < 4; ++q) {
+          const float2 xv = unpack_bf16x2(xw[q]), dv = unpack_bf16x2(dw4[q]);
+          xh[i][2 * q] = xv.x * r;
+          xh[i][2 * q + 1] = xv.y * r;
+          g[i][2 * q] = dv.x * wv[i][2 * q];
+          g[i][2 * q + 1] = dv.y * wv[i][2 * q + 1];
+          dot += g[i][2 * q] * xh[i][2 * q] + g[i][2 * q + 1] * xh[i][2 * q + 1];
+          dwacc[i][2 * q] += dv.x * xh[i][2 * q];
+          dwacc[i][2 * q + 1] += dv.y * xh[i][2 * q + 1];
         }
       }
     }
+    fetch(row + gridDim.x);
     dot = block_sum<RN_THREADS>(dot, red) / H;
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
@@ -415,14 +433,48 @@ __global__ void __launch_bounds__(1024) moe_plan_scan_kernel(const MoePlanArgs a
   int* hist = a.scratch;
   int* bin_base = a.scratch + static_cast<long long>(n_units) * nbins;
   int* bin_total = bin_base + nbins;
-  for (int b = threadIdx.x; b < nbins; b += blockDim.x) {
-    int run = 0;
-    for (int u = 0; u < n_units; ++u) {
-      const int c = hist[static_cast<long long>(u) * nbins + b];
-      hist[static_cast<long long>(u) * nbins + b] = run;
-      run += c;
+  __shared__ int s_part[1024];
+  if (nbins <= 1024) {
+    // all 1024 threads: thread = (chunk of units, bin).  Chunk sums, a short serial prefix over the chunks of the
+    // bin in shared memory, then the exclusive prefix inside the chunk.  Loads of neighbouring threads are
+    // neighbouring bins (coalesced) and independent of the running sum.
+    int chunks = 1024 / nbins;
+    if (chunks > n_units) chunks = n_units;
+    const int per = (n_units + chunks - 1) / chunks;
+    const int b = threadIdx.x % nbins, c = threadIdx.x / nbins;
+    const bool live = c < chunks;
+    const int u0 = c * per, u1 = min(n_units, u0 + per);
+    int sum = 0;
+    if (live) {
+#pragma unroll 8
+      for (int u = u0; u < u1; ++u) sum += hist[static_cast<long long>(u) * nbins + b];
     }
-    bin_total[b] = (a.capacity > 0 && run > a.capacity) ? a.capacity : run;
+    s_part[threadIdx.x] = sum;
+    __syncthreads();
+    if (live) {
+      int run = 0;
+      for (int cc = 0; cc < c; ++cc) run += s_part[cc * nbins + b];
+#pragma unroll 8
+      for (int u = u0; u < u1; ++u) {
+        const int cnt = hist[static_cast<long long>(u) * nbins + b];
+        hist[static_cast<long long>(u) * nbins + b] = run;
+        run += cnt;
+      }
+      if (c == chunks - 1) {  // the last chunk's running sum is the bin total
+        for (int cc = c + 1; cc < chunks; ++cc) run += s_part[cc * nbins + b];
+        bin_total[b] = (a.capacity > 0 && run > a.capacity) ? a.capacity : run;
+      }
+    }
+  } else {
+    for (int b = threadIdx.x; b < nbins; b += blockDim.x) {
+      int run = 0;
+      for (int u = 0; u < n_units; ++u) {
+        const int c = hist[static_cast<long long>(u) * nbins + b];
+        hist[static_cast<long long>(u) * nbins + b] = run;
+        run += c;
+      }
+      bin_total[b] = (a.capacity > 0 && run > a.capacity) ? a.capacity : run;
+    }
   }
   __syncthreads();
   __shared__ int s_total_rows;

@@ -91,6 +91,12 @@ def _should_use_fused(tokens: torch.Tensor, gate_w: torch.Tensor, force_referenc
             and tokens.stride(1) == 1 and (tokens.stride(0) * 2) % 16 == 0)
 
 
+def _next_pow2(n: int) -> int:
+    """Smallest power of two >= n (the reference sizes its expert tile with it, moe_router.py:297-388; the fused
+    kernel pads the expert dimension to a multiple of 16 instead, this stays for callers of the helper)."""
+    return 1 if n <= 1 else 1 << (int(n) - 1).bit_length()
+
+
 def _should_use_triton(tokens: torch.Tensor, gate_w: torch.Tensor, force_reference: bool) -> bool:
     """Kept for callers of the reference API: true when a device kernel (here: the fused sm_100a one) runs."""
     return _should_use_fused(tokens, gate_w, force_reference)

@@ -357,7 +357,8 @@ def test_cross_entropy(ext, rows, V):
     assert _rel_err(work, lf.grad) < 1e-2
 
 
-@pytest.mark.parametrize("N,K,E,cap", [(1000, 2, 8, 0), (4096, 8, 64, 0), (777, 2, 16, 60), (3000, 6, 64, 0)])
+@pytest.mark.parametrize("N,K,E,cap", [(1000, 2, 8, 0), (4096, 8, 64, 0), (777, 2, 16, 60), (3000, 6, 64, 0),
+                                       (50000, 8, 8, 0), (20000, 4, 64, 900)])
 def test_moe_plan_gather_combine(ext, N, K, E, cap):
     torch.manual_seed(11)
     H = 128
