@@ -83,8 +83,12 @@ def bench_router_fwd_bwd(N, H, E, K, device, dtype):
     return {"bench": "router_fwd_bwd", "N": N, "H": H, "E": E, "K": K, "ms": ms, "tokens_per_sec": N / ms * 1e3}
 
 
+_layer_topology = None  # the reference's layer needs an explicit (degenerate, single-rank) topology
+
+
 def bench_moe_layer(B, S, H, Fd, E, K, device, dtype):
-    layer = DistributedMoELayer(H, Fd, E, K, dtype=dtype).to(device)
+    kw = {"topology": _layer_topology(device)} if _layer_topology is not None else {}
+    layer = DistributedMoELayer(H, Fd, E, K, dtype=dtype, **kw).to(device)
     x = torch.randn(B, S, H, device=device, dtype=dtype)
     with torch.no_grad():
         ms = _time_fn(lambda: layer(x), device)
@@ -134,14 +138,38 @@ def run_suite(device: str, dtype: torch.dtype):
     return rows
 
 
+def _use_reference() -> None:
+    """Rebind the benchmarked entry points to the unmodified reference package installed under baseline/_ref
+    (its Triton router on a GPU, its Python expert loop), so both implementations run the same workloads here."""
+    global moe_topk_route, DistributedMoELayer, _layer_topology
+    ref = ROOT / "baseline" / "_ref"
+    if not (ref / "pkg").exists():
+        raise SystemExit("baseline/_ref is not installed")
+    sys.path[:] = [p for p in sys.path if Path(p or ".").resolve() != ROOT]
+    sys.path.insert(0, str(ref))
+    for name in [m for m in sys.modules if m == "pkg" or m.startswith("pkg.")]:
+        del sys.modules[name]
+    from pkg.distributed.parallel_mesh import DistributedMoELayer as RefLayer
+    from pkg.kernels.moe_router import moe_topk_route as ref_route
+
+    from pkg.distributed.parallel_mesh import build_topology as ref_topology
+
+    moe_topk_route, DistributedMoELayer = ref_route, RefLayer
+    _layer_topology = lambda device: ref_topology(dp_size=1, ep_size=1, device_type=device)  # noqa: E731
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours",
+                    help="'reference' runs the same suite on the unmodified reference under baseline/_ref")
     ap.add_argument("--cuda", action="store_true", help="also run the GPU suite")
     ap.add_argument("--json", type=str, default=None)
     ap.add_argument("--csv", type=str, default=None)
     ap.add_argument("--dtype", choices=["bf16", "fp32"], default="bf16", help="input dtype of the GPU suite")
     ap.add_argument("--skip-cpu", action="store_true")
     args = ap.parse_args(argv)
+    if args.impl == "reference":
+        _use_reference()
     rows = []
     if not args.skip_cpu:
         rows += run_suite("cpu", torch.float32)
@@ -151,6 +179,7 @@ def main(argv=None) -> int:
             return 2
         rows += run_suite("cuda", torch.bfloat16 if args.dtype == "bf16" else torch.float32)
     for r in rows:
+        r["impl"] = args.impl
         print(json.dumps(r))
     if args.json:
         Path(args.json).write_text(json.dumps({"torch": torch.__version__, "results": rows}, indent=1))

@@ -234,6 +234,26 @@ void rope(Tensor& t, const Tensor& cos_tab, const Tensor& sin_tab, int64_t seq, 
                                t.stride(0), inverse ? 1 : 0, cur_stream()),
              "rope");
 }
+void qkv_grad_pack(const Tensor& dq, const Tensor& dk, const Tensor& dv, Tensor& out, const Tensor& cos_tab,
+                   const Tensor& sin_tab) {
+  // dq [B, nh, S, hd], dk / dv [B, nkv, S, hd] (any batch / head / sequence strides); out [B, S, nh + 2 nkv, hd]
+  const c10::cuda::CUDAGuard guard(out.device());
+  TORCH_CHECK(dq.dim() == 4 && dk.dim() == 4 && dv.dim() == 4 && out.dim() == 4 && out.is_contiguous());
+  for (const Tensor* t : {&dq, &dk, &dv})
+    TORCH_CHECK(t->scalar_type() == at::kBFloat16 && t->stride(3) == 1 && t->is_cuda(), "bf16 CUDA, unit inner stride");
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && cos_tab.scalar_type() == at::kFloat && cos_tab.is_contiguous() &&
+              sin_tab.is_contiguous());
+  const int64_t B = dq.size(0), nh = dq.size(1), S = dq.size(2), hd = dq.size(3), nkv = dk.size(1);
+  TORCH_CHECK(dv.size(1) == nkv && out.size(0) == B && out.size(1) == S && out.size(2) == nh + 2 * nkv &&
+              out.size(3) == hd && cos_tab.size(0) >= S && cos_tab.size(1) == hd / 2);
+  const long long sq[3] = {dq.stride(0), dq.stride(1), dq.stride(2)};
+  const long long sk[3] = {dk.stride(0), dk.stride(1), dk.stride(2)};
+  const long long sv[3] = {dv.stride(0), dv.stride(1), dv.stride(2)};
+  check_cuda(cmoe::launch_qkv_grad_pack(dq.data_ptr(), sq, dk.data_ptr(), sk, dv.data_ptr(), sv, out.data_ptr(),
+                                        cos_tab.data_ptr<float>(), sin_tab.data_ptr<float>(), B, static_cast<int>(S),
+                                        static_cast<int>(nh), static_cast<int>(nkv), static_cast<int>(hd), cur_stream()),
+             "qkv_grad_pack");
+}
 void adamw(Tensor& p32, const OptTensor& p16, Tensor& m, Tensor& v, Tensor& grad, double lr, double beta1, double beta2,
            double eps, double weight_decay, int64_t step, double grad_scale, double max_norm, const OptTensor& sumsq,
            bool zero_grad) {
@@ -363,6 +383,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("rope", &rope);
+  m.def("qkv_grad_pack", &qkv_grad_pack);
   m.def("adamw", &adamw);
   m.def("sumsq", &sumsq);
   m.def("cross_entropy", &cross_entropy);

@@ -222,6 +222,58 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ t, const float* __restri
   }
 }
 
+// Packs the three attention gradients into one [rows, heads, head_dim] buffer (q heads, k heads, v heads) and undoes
+// the rotary embedding on the q and k heads on the way: one read and one write of every element instead of three
+// strided copies plus an in-place rotation pass.  Sources are [B, h, S, head_dim] views with arbitrary batch / head /
+// sequence strides and unit stride on head_dim.
+struct QkvGradSrc {
+  const __nv_bfloat16* ptr;
+  long long sb, sh, ss;  // strides (elements) of batch, head, sequence position
+};
+
+__global__ void qkv_grad_pack_kernel(QkvGradSrc dq, QkvGradSrc dk, QkvGradSrc dv, __nv_bfloat16* __restrict__ out,
+                                     const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
+                                     long long rows, int seq, int nh, int nkv, int head_dim) {
+  const int heads = nh + 2 * nkv;
+  const int half = head_dim / 2;
+  const int vec_per_head = half / 8;
+  const long long total = rows * heads * vec_per_head;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int vi = static_cast<int>(i % vec_per_head);
+    const long long rh = i / vec_per_head;
+    const int h = static_cast<int>(rh % heads);
+    const long long r = rh / heads;
+    const int pos = static_cast<int>(r % seq);
+    const long long b = r / seq;
+    const QkvGradSrc& s = h < nh ? dq : (h < nh + nkv ? dk : dv);
+    const int hh = h < nh ? h : (h < nh + nkv ? h - nh : h - nh - nkv);
+    const __nv_bfloat16* src = s.ptr + b * s.sb + hh * s.sh + pos * s.ss + vi * 8;
+    __nv_bfloat16* dst = out + (r * heads + h) * head_dim + vi * 8;
+    const uint4 ra = __ldcs(reinterpret_cast<const uint4*>(src));
+    const uint4 rb = __ldcs(reinterpret_cast<const uint4*>(src + half));
+    if (h >= nh + nkv) {  // v heads: plain copy
+      *reinterpret_cast<uint4*>(dst) = ra;
+      *reinterpret_cast<uint4*>(dst + half) = rb;
+      continue;
+    }
+    const uint32_t aw[4] = {ra.x, ra.y, ra.z, ra.w}, bw[4] = {rb.x, rb.y, rb.z, rb.w};
+    uint32_t oa[4], ob[4];
+    const float* cp = cos_tab + static_cast<long long>(pos) * half + vi * 8;
+    const float* sp = sin_tab + static_cast<long long>(pos) * half + vi * 8;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float2 a = unpack_bf16x2(aw[q]), bb = unpack_bf16x2(bw[q]);
+      const float c0 = cp[2 * q], c1 = cp[2 * q + 1], s0 = sp[2 * q], s1 = sp[2 * q + 1];
+      // the transpose of the rotation: [a; b] -> [a c + b s; b c - a s]
+      oa[q] = pack_bf16x2(a.x * c0 + bb.x * s0, a.y * c1 + bb.y * s1);
+      ob[q] = pack_bf16x2(bb.x * c0 - a.x * s0, bb.y * c1 - a.y * s1);
+    }
+    *reinterpret_cast<uint4*>(dst) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+    *reinterpret_cast<uint4*>(dst + half) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+  }
+}
+
 // ------------------------------------------------------------------------------------ AdamW
 __global__ void adamw_kernel(const AdamWArgs a) {
   float gs = a.grad_scale;
@@ -689,6 +741,24 @@ cudaError_t launch_rope(void* t, const float* cos_tab, const float* sin_tab, lon
   const long long total = rows * heads * (head_dim / 16);
   rope_kernel<<<grid_for(total, 256, 148 * 16), 256, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(t), cos_tab, sin_tab,
                                                                   rows, seq, heads, head_dim, row_stride, inverse);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_qkv_grad_pack(const void* dq, const long long* dq_strides, const void* dk, const long long* dk_strides,
+                                 const void* dv, const long long* dv_strides, void* out, const float* cos_tab,
+                                 const float* sin_tab, long long batch, int seq, int nh, int nkv, int head_dim,
+                                 cudaStream_t stream) {
+  if (head_dim % 16 != 0 || batch <= 0 || seq <= 0 || nh <= 0 || nkv <= 0) return cudaErrorInvalidValue;
+  auto mk = [](const void* p, const long long* st) {
+    return QkvGradSrc{reinterpret_cast<const __nv_bfloat16*>(p), st[0], st[1], st[2]};
+  };
+  for (const long long* st : {dq_strides, dk_strides, dv_strides})
+    if (st[0] % 8 != 0 || st[1] % 8 != 0 || st[2] % 8 != 0) return cudaErrorInvalidValue;  // 16-byte vector loads
+  const long long rows = batch * seq;
+  const long long total = rows * (nh + 2 * nkv) * (head_dim / 16);
+  qkv_grad_pack_kernel<<<grid_for(total, 256, 148 * 16), 256, 0, stream>>>(
+      mk(dq, dq_strides), mk(dk, dk_strides), mk(dv, dv_strides), reinterpret_cast<__nv_bfloat16*>(out), cos_tab,
+      sin_tab, rows, seq, nh, nkv, head_dim);
   return cudaGetLastError();
 }
 

@@ -24,6 +24,13 @@ cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
 cudaError_t launch_rope(void* t, const float* cos_tab, const float* sin_tab, long long rows, int seq, int heads,
                         int head_dim, long long row_stride, int inverse, cudaStream_t stream);
 
+// dqkv[b*seq + s, h, :] = un-rotated dq / dk (first nh, next nkv heads) or dv (last nkv heads); each source is a
+// [batch, heads, seq, head_dim] view given by its (batch, head, seq) strides in elements, unit stride on head_dim.
+cudaError_t launch_qkv_grad_pack(const void* dq, const long long* dq_strides, const void* dk, const long long* dk_strides,
+                                 const void* dv, const long long* dv_strides, void* out, const float* cos_tab,
+                                 const float* sin_tab, long long batch, int seq, int nh, int nkv, int head_dim,
+                                 cudaStream_t stream);
+
 // ---- fused AdamW ---------------------------------------------------------------------------
 // Decoupled weight decay; p32 is the fp32 master copy, p16 (optional) the bf16 copy that the model
 // computes with.  grad is fp32 or bf16.  The gradient is first multiplied by

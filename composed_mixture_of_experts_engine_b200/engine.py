@@ -110,6 +110,7 @@ class Trainer:
                           + (topology.ep_rank if topology.ep_size > 1 else 0) * 100003)
         self.dtype = DTYPE_MAP.get(cfg.model.dtype, torch.float32)
         self.model = build_model(cfg, topology)
+        self._sync_tensor_parallel_replicas()
         self.model = apply_fsdp2(self.model, topology)
         self.is_decoder = isinstance(self.model, MoEDecoder)
         t = cfg.training
@@ -126,6 +127,22 @@ class Trainer:
             self.stage = PipelineStage(topology.pp_rank, topology.pp_size, self.model, topology)
         self.last_aux: Optional[torch.Tensor] = None
         self.last_z: Optional[torch.Tensor] = None
+
+    def _sync_tensor_parallel_replicas(self) -> None:
+        """Tensor-parallel ranks draw their weight slices from different random streams; everything that is NOT
+        sliced (norms, router gates, embeddings under sequence parallelism, biases of row-parallel layers) must
+        start identical on all of them: take the copy of the group's first rank."""
+        topo = self.topology
+        if topo.tp_size <= 1 or not dist.is_initialized():
+            return
+        from .parallel.mesh import tp_process_group
+
+        group = tp_process_group(topo)
+        src = topo.axis_ranks("tp")[0]
+        with torch.no_grad():
+            for p in self.model.parameters():
+                if not getattr(p, "tensor_parallel_shard", False):
+                    dist.broadcast(p.data, src=src, group=group)
 
     # ---- batch helpers --------------------------------------------------------------------------------
     @property
@@ -220,28 +237,32 @@ class Trainer:
 
     def _clip_grads_library(self, max_norm: float) -> None:
         """Global-norm clipping where every rank arrives at the same norm: replicated parameters count once,
-        expert shards are summed over the ranks that hold different experts (and pipeline stages)."""
+        tensor-parallel slices are summed over the tensor-parallel group, expert shards over the ranks that hold
+        different experts, and everything over the pipeline stages."""
         topo = self.topology
-        dense_sq = torch.zeros((), dtype=torch.float64, device=self.device)
-        expert_sq = torch.zeros((), dtype=torch.float64, device=self.device)
+        # [replicated over tp, sliced over tp] x [dense, expert]
+        sq = {(sh, ex): torch.zeros((), dtype=torch.float64, device=self.device) for sh in (0, 1) for ex in (0, 1)}
         for p in self.model.parameters():
             if p.grad is None:
                 continue
-            sq = p.grad.detach().double().pow(2).sum()
-            if getattr(p, "is_expert_param", False):
-                expert_sq += sq
-            else:
-                dense_sq += sq
+            key = (int(bool(getattr(p, "tensor_parallel_shard", False)) and topo.tp_size > 1),
+                   int(bool(getattr(p, "is_expert_param", False))))
+            sq[key] += p.grad.detach().double().pow(2).sum()
         if dist.is_initialized() and topo.world_size > 1:
-            from .parallel.mesh import ep_process_group, pp_process_group
+            from .parallel.mesh import ep_process_group, pp_process_group, tp_process_group
 
+            if topo.tp_size > 1:  # slices of one matrix live on different tensor-parallel ranks
+                sliced = torch.stack([sq[(1, 0)], sq[(1, 1)]])
+                dist.all_reduce(sliced, group=tp_process_group(topo))
+                sq[(1, 0)], sq[(1, 1)] = sliced[0], sliced[1]
+            expert_sq = sq[(0, 1)] + sq[(1, 1)]
             if topo.ep_size > 1:
                 dist.all_reduce(expert_sq, group=ep_process_group(topo))
-            total = dense_sq + expert_sq
+            total = sq[(0, 0)] + sq[(1, 0)] + expert_sq
             if topo.pp_size > 1:
                 dist.all_reduce(total, group=pp_process_group(topo))
         else:
-            total = dense_sq + expert_sq
+            total = sum(sq.values())
         coef = float(max_norm / (total.sqrt() + 1e-6))
         if coef < 1.0:
             for p in self.model.parameters():

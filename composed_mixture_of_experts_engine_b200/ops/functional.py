@@ -113,7 +113,7 @@ class _RopeAttentionFn(torch.autograd.Function):
 
     The rotation runs in place on ``qkv`` (the caller hands over the projection's output and must not read it
     afterwards), the attention kernel reads q / k / v as strided views of the packed buffer, and the backward
-    writes dq / dk / dv straight into one packed gradient and un-rotates it in place.  This replaces the
+    packs dq / dk / dv into one gradient buffer and un-rotates the q and k heads in the same pass.  This replaces the
     slice / zero-fill / accumulate chain autograd would build around three views of one tensor (three zero
     fills and two adds of the full packed size per layer)."""
 
@@ -144,10 +144,14 @@ class _RopeAttentionFn(torch.autograd.Function):
         ctx.inner = None
         dq, dk, dv = torch.autograd.grad(out, (q, k, v), go.permute(0, 2, 1, 3))
         dqkv = torch.empty(B, S, heads, hd, device=go.device, dtype=go.dtype)
-        dqkv[:, :, :nh].copy_(dq.permute(0, 2, 1, 3))
-        dqkv[:, :, nh: nh + nkv].copy_(dk.permute(0, 2, 1, 3))
-        dqkv[:, :, nh + nkv:].copy_(dv.permute(0, 2, 1, 3))
-        _ext.ext().rope(dqkv.view(B * S, heads, hd)[:, : nh + nkv], cos, sin, S, True)
+        if all(t.stride(3) == 1 and all(st % 8 == 0 for st in t.stride()[:3]) for t in (dq, dk, dv)):
+            # one pass: pack the three gradients and undo the rotation of the q and k heads on the way
+            _ext.ext().qkv_grad_pack(dq, dk, dv, dqkv, cos, sin)
+        else:
+            dqkv[:, :, :nh].copy_(dq.permute(0, 2, 1, 3))
+            dqkv[:, :, nh: nh + nkv].copy_(dk.permute(0, 2, 1, 3))
+            dqkv[:, :, nh + nkv:].copy_(dv.permute(0, 2, 1, 3))
+            _ext.ext().rope(dqkv.view(B * S, heads, hd)[:, : nh + nkv], cos, sin, S, True)
         return dqkv, None, None, None, None
 
 

@@ -180,6 +180,7 @@ class DistributedMoELayer(nn.Module):
         e_local, f_local = len(self.local_expert_ids), ffn_dim // tp
         self.w13 = nn.Parameter(torch.empty(max(e_local, 0), 2 * f_local, hidden_dim, dtype=dtype, device=device))
         self.w2 = nn.Parameter(torch.empty(max(e_local, 0), hidden_dim, f_local, dtype=dtype, device=device))
+        self.w13.tensor_parallel_shard = self.w2.tensor_parallel_shard = True  # sliced on the FFN width over tp
         nn.init.normal_(self.w13, std=init_std if init_std is not None else 1.0 / math.sqrt(hidden_dim))
         nn.init.normal_(self.w2, std=init_std if init_std is not None else 1.0 / math.sqrt(ffn_dim))
         # the module list holds views only (no parameters), so state dicts and optimisers see w13 / w2 once
@@ -262,11 +263,14 @@ class DistributedMoELayer(nn.Module):
             raise ValueError(f"hidden size {flat.shape[-1]} != layer hidden_dim {self.hidden_dim}")
         topo = self.topology
         N = flat.shape[0]
-        if topo.tp_size > 1:
-            flat = C.copy_to_group(flat, tp_process_group(topo))
-
         idx, w, _counts = self.router(flat)
         gate_w = self.router.last_w32  # fp32 gate weights, differentiable on every path
+        if topo.tp_size > 1:
+            # The router runs replicated on every tensor-parallel rank; the experts are sliced on the FFN width, so
+            # each rank produces partial sums.  Their gradients with respect to the tokens AND to the gate weights
+            # are partial too: both enter the sliced region through an identity whose backward is an all-reduce.
+            flat = C.copy_to_group(flat, tp_process_group(topo))
+            gate_w = C.copy_to_group(gate_w, tp_process_group(topo))
         cap = self.capacity(N) if self.capacity_dropping else 0
         self._last_n_slots = N * self.top_k
 

@@ -51,6 +51,7 @@ class ColumnParallelLinear(nn.Module):
         self.sequence_parallel = sequence_parallel
         self.seq_dim = seq_dim
         self.weight = nn.Parameter(torch.empty(self.out_per_rank, in_features, device=device, dtype=dtype))
+        self.weight.tensor_parallel_shard = True  # every tensor-parallel rank holds a different slice
         nn.init.normal_(self.weight, mean=0.0, std=1.0 / math.sqrt(in_features))
         # the bias is kept whole on every rank (as in the reference) and sliced when the output stays sharded
         self.bias = nn.Parameter(torch.zeros(out_features, device=device, dtype=dtype)) if bias else None
@@ -96,6 +97,7 @@ class RowParallelLinear(nn.Module):
         self.sequence_parallel = sequence_parallel
         self.seq_dim = seq_dim
         self.weight = nn.Parameter(torch.empty(out_features, self.in_per_rank, device=device, dtype=dtype))
+        self.weight.tensor_parallel_shard = True
         nn.init.normal_(self.weight, mean=0.0, std=1.0 / math.sqrt(in_features))
         self.bias = nn.Parameter(torch.zeros(out_features, device=device, dtype=dtype)) if bias else None
 

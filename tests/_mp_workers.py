@@ -199,6 +199,34 @@ def trainer_steps(rank, world, config_path, steps):
             "local_experts": tr.model.blocks[0].moe.local_expert_ids}
 
 
+def trainer_hybrid(rank, world, dp, ep, tp, pp, steps):
+    """The public Trainer with tensor (+ sequence) and pipeline parallelism on gloo ranks: tiny fp32 decoder, 1F1B over
+    4 microbatches.  Returns the per-step losses this rank saw (only the last pipeline stage sees them)."""
+    import torch
+
+    from composed_mixture_of_experts_engine_b200.engine import Trainer
+    from composed_mixture_of_experts_engine_b200.utils.config import MoEConfig
+
+    cfg = MoEConfig.from_dict({
+        "model": dict(arch="moe_decoder", hidden_dim=64, num_layers=4, num_heads=4, num_experts=4, top_k=2,
+                      ffn_dim=128, vocab_size=256, sequence_length=32, dtype="float32", aux_loss_coeff=0.01,
+                      init_std=0.02),
+        "training": dict(micro_batch_size=2, gradient_accumulation_steps=4, global_batch_size=8 * dp, max_steps=50,
+                         warmup_steps=0, learning_rate=2e-3, grad_clip=1.0, seed=0),
+        "parallelism": dict(data_parallel=dp, expert_parallel=ep, tensor_parallel=tp, pipeline_parallel=pp,
+                            ep_from_dp=True, sequence_parallel=tp > 1)})
+    tr = Trainer(cfg, device_type="cpu")
+    gen = torch.Generator().manual_seed(tr.topology.dp_rank)  # replicas of one model shard see the same data
+    ids, tgt = tr.synthetic_batch(gen, pinned=False)
+    losses = [float(tr.train_step(ids, tgt)) for _ in range(steps)]
+    blk = tr.model.blocks[0]
+    replicated = {"norm": blk.norm.weight, "attn_norm": blk.attn_norm.weight, "gate": blk.moe.router.gate_w}
+    return {"losses": losses, "pp_rank": tr.topology.pp_rank, "tp_rank": tr.topology.tp_rank,
+            "dp_rank": tr.topology.dp_rank, "last": tr.topology.is_last_pp_stage(),
+            "n_blocks": len(tr.model.blocks),
+            "replicated": {k: v.detach().double().flatten()[:64].tolist() for k, v in replicated.items()}}
+
+
 # -------------------------------------------------------------------------------------------------- GPU workers
 def _set_transport(transport):
     """"nccl", "auto" (peer memory, results pushed by the GEMM epilogues) or "auto-pull" (peer memory, pulled)."""

@@ -300,6 +300,28 @@ def test_rope_roundtrip_and_reference(ext):
     assert _rel_err(t, orig) < 1e-2
 
 
+@pytest.mark.parametrize("nh,nkv", [(4, 4), (8, 2)])
+def test_qkv_grad_pack_undoes_rope_and_packs(ext, nh, nkv):
+    """Packing dq / dk / dv (strided [B, h, S, hd] views) into one [B, S, heads, hd] gradient with the transpose of the
+    rotation applied to the q and k heads vs slicing + the fp32 restatement of the inverse rotation."""
+    from composed_mixture_of_experts_engine_b200.ops import functional as OF
+
+    torch.manual_seed(21)
+    B, S, hd = 2, 96, 64
+    heads = nh + 2 * nkv
+    cos, sin = OF.rope_tables(S, hd, 10000.0, torch.device("cuda"))
+    # sources laid out like attention gradients usually are: [B, S, h, hd] memory viewed as [B, h, S, hd]
+    dq = torch.randn(B, S, nh, hd, device="cuda", dtype=torch.bfloat16).permute(0, 2, 1, 3)
+    dk = torch.randn(B, nkv, S, hd, device="cuda", dtype=torch.bfloat16)  # and one dense [B, h, S, hd]
+    dv = torch.randn(B, S, nkv, hd, device="cuda", dtype=torch.bfloat16).permute(0, 2, 1, 3)
+    out = torch.full((B, S, heads, hd), 5.0, device="cuda", dtype=torch.bfloat16)
+    ext.qkv_grad_pack(dq, dk, dv, out, cos, sin)
+    packed = torch.cat([dq.permute(0, 2, 1, 3), dk.permute(0, 2, 1, 3), dv.permute(0, 2, 1, 3)], dim=2).float()
+    want = OF.rope_reference(packed.reshape(B * S, heads, hd), cos, -sin, S, nh + nkv).view(B, S, heads, hd)
+    assert _rel_err(out, want) < 5e-3
+    assert torch.equal(out[:, :, nh + nkv:], dv.permute(0, 2, 1, 3))
+
+
 @pytest.mark.parametrize("n,bf16_grad", [(1000, False), (4099, True), (1 << 20, True)])
 def test_adamw_matches_torch(ext, n, bf16_grad):
     torch.manual_seed(8)

@@ -90,3 +90,22 @@ def test_trainer_cpu_smoke_ep2():
         assert out["losses"][-1] < out["losses"][0]
         assert out["gate_sync"] < 1e-6
     assert res[0]["local_experts"] == [0, 1, 2, 3] and res[1]["local_experts"] == [4, 5, 6, 7]
+
+
+@pytest.mark.parametrize("dp,ep,tp,pp", [(1, 1, 2, 2), (2, 2, 1, 2), (2, 2, 2, 2)])
+def test_trainer_hybrid_tp_sp_pp(dp, ep, tp, pp):
+    """Trainer with tensor+sequence parallelism and a two-stage 1F1B pipeline (and with expert parallelism across a
+    pipeline): every stage holds half of the blocks, the loss is finite and falls, tensor-parallel peers agree."""
+    world = dp * tp * pp
+    res = _spawn("trainer_hybrid", world, dp, ep, tp, pp, 12, timeout=900)
+    last = [out for out in res.values() if out["last"]]
+    assert len(last) == world // pp and all(out["n_blocks"] == 2 for out in res.values())
+    for out in last:
+        assert all(math.isfinite(l) for l in out["losses"])
+        assert out["losses"][-1] < out["losses"][0]
+    if tp > 1:
+        a, b = sorted([o for o in last if o["dp_rank"] == 0], key=lambda o: o["tp_rank"])[:2]
+        assert max(abs(x - y) for x, y in zip(a["losses"], b["losses"])) < 1e-3
+        for name in a["replicated"]:  # parameters replicated over the tensor-parallel group stay identical
+            diff = max(abs(x - y) for x, y in zip(a["replicated"][name], b["replicated"][name]))
+            assert diff < 1e-6, (name, diff)
