@@ -100,19 +100,21 @@ void gemm(const Tensor& A, const Tensor& B, Tensor& D, int64_t mode, int64_t epi
   check_cuda(cmoe::launch_gemm(g, cur_stream()), "launch_gemm");
 }
 
-// GEMM (dense or grouped-M) whose output rows are scattered to per-row (rank, row) destinations by the epilogue
+// GEMM (dense or grouped-M) whose output rows are scattered by the epilogue: row r goes to rank
+// row_slot[r] / slots_per_rank, row row_slot[r] % slots_per_rank of that rank's buffer (negative slot: skipped)
 void gemm_scatter(const Tensor& A, const Tensor& B, Tensor& D, int64_t mode, int64_t M, int64_t N, int64_t K, bool b_mn,
                   int64_t groups, int64_t b_group_rows, const OptTensor& tile_group, const OptTensor& num_m_tiles,
-                  int64_t max_m_tiles, const Tensor& row_dest, const std::vector<int64_t>& out_ptrs, int64_t out_ld,
-                  const OptTensor& status, int64_t timeout_ns) {
+                  int64_t max_m_tiles, const Tensor& row_slot, int64_t slots_per_rank,
+                  const std::vector<int64_t>& out_ptrs, int64_t out_ld, const OptTensor& status, int64_t timeout_ns) {
   const c10::cuda::CUDAGuard guard(A.device());
   cmoe::GemmArgs g = gemm_args(A, B, D, mode, cmoe::EPI_STORE, M, N, K, false, b_mn, groups, b_group_rows, 0, tile_group,
                                num_m_tiles, max_m_tiles, std::nullopt, 0, false, std::nullopt, std::nullopt,
                                std::nullopt, 0, 0, 0, status, timeout_ns);
   TORCH_CHECK(!out_ptrs.empty() && out_ptrs.size() <= static_cast<size_t>(cmoe::kMaxPeers), "peer table size");
   for (size_t i = 0; i < out_ptrs.size(); ++i) g.scatter_out.ptr[i] = reinterpret_cast<void*>(out_ptrs[i]);
-  TORCH_CHECK(row_dest.scalar_type() == at::kInt && row_dest.is_contiguous() && row_dest.numel() >= 2 * A.size(0));
-  g.row_dest = row_dest.data_ptr<int>();
+  TORCH_CHECK(row_slot.scalar_type() == at::kInt && row_slot.is_contiguous() && row_slot.numel() >= A.size(0));
+  g.scatter_row_slot = row_slot.data_ptr<int>();
+  g.scatter_slots_per_rank = slots_per_rank;
   g.scatter_ld = out_ld;
   check_cuda(cmoe::launch_gemm(g, cur_stream()), "launch_gemm(scatter)");
 }

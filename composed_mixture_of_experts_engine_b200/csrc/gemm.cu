@@ -87,8 +87,9 @@ struct KParams {
   int pull_cols;
   uint32_t* tile_ready;
   uint32_t pull_epoch;
-  // fused scatter: per-row destination (rank, row) of the output
-  const int* row_dest;
+  // fused scatter: the slot of every output row gives its destination (rank, row)
+  const int* scatter_row_slot;
+  long long scatter_slots_per_rank;
   PeerTable scatter_out;
   long long scatter_ld;
   int out_mode;  // OutMode (EPI_STORE only)
@@ -530,7 +531,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           for (int i = 0; i < 8; ++i) {
             const long long rr = ti.m0 + (t >> 3) + 16 * i;
             dest[i] = make_int2(-1, 0);
-            if (rr < m_limit) dest[i] = *reinterpret_cast<const int2*>(p.row_dest + 2 * rr);
+            if (rr < m_limit) {
+              const int slot = p.scatter_row_slot[rr];
+              if (slot >= 0) {
+                const int dr = static_cast<int>(slot / p.scatter_slots_per_rank);
+                dest[i] = make_int2(dr, static_cast<int>(slot - dr * p.scatter_slots_per_rank));
+              }
+            }
           }
         }
 #pragma unroll 1
@@ -960,17 +967,20 @@ cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   if (a.pull_row_slot != nullptr &&
       (a.mode != GEMM_GROUPED_M || a.a_mn || a.tile_ready == nullptr || a.a_cols % 8 != 0))
     return cudaErrorInvalidValue;
-  kp.row_dest = a.row_dest;
+  kp.scatter_row_slot = a.scatter_row_slot;
+  kp.scatter_slots_per_rank = a.scatter_slots_per_rank;
   kp.scatter_out = a.scatter_out;
   kp.scatter_ld = a.scatter_ld;
-  if (a.row_dest != nullptr && (a.epilogue != EPI_STORE || a.d_fp32 || a.accumulate || a.mode == GEMM_GROUPED_K))
+  if (a.scatter_row_slot != nullptr &&
+      (a.epilogue != EPI_STORE || a.d_fp32 || a.accumulate || a.mode == GEMM_GROUPED_K ||
+       a.scatter_slots_per_rank <= 0 || a.scatter_ld % 8 != 0))
     return cudaErrorInvalidValue;
   // how the EPI_STORE epilogue leaves the SM
   kp.out_mode = OUT_DIRECT;
   CUtensorMap tmD = tmA;  // placeholder when no output map is needed
   if (a.epilogue == EPI_STORE && !direct_epilogue_forced()) {
-    if (a.row_dest != nullptr) {
-      if (a.scatter_ld % 8 == 0) kp.out_mode = OUT_SCATTER;
+    if (a.scatter_row_slot != nullptr) {
+      kp.out_mode = OUT_SCATTER;
     } else if (!(a.accumulate && !a.d_fp32)) {
       const long long es = a.d_fp32 ? 4 : 2;
       const long long d_rows = a.mode == GEMM_GROUPED_M ? a.a_rows : a.M;

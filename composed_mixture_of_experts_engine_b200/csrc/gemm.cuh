@@ -85,11 +85,13 @@ struct GemmArgs {
   uint32_t* tile_ready = nullptr;
   uint32_t pull_epoch = 0;
 
-  // Fused scatter (EPI_STORE, bf16, no accumulate).  When row_dest is set, output row r is not written to D but
-  // to rank row_dest[2r]'s buffer in scatter_out at row row_dest[2r+1] (leading dimension scatter_ld), with
-  // plain stores from the epilogue (peer memory over NVLink, or local); rows with rank < 0 are skipped.  This is
-  // the combine push of expert parallelism and the scatter half of a reduce-scatter.
-  const int* row_dest = nullptr;
+  // Fused scatter (EPI_STORE, bf16, no accumulate).  When scatter_row_slot is set, output row r is not written to D
+  // but to the buffer of rank  slot / scatter_slots_per_rank  in scatter_out, at row  slot % scatter_slots_per_rank
+  // (slot = scatter_row_slot[r], leading dimension scatter_ld), with stores from the epilogue's staging area (peer
+  // memory over NVLink, or local); rows with a negative slot are skipped.  This is the combine push of expert
+  // parallelism (the slot of a row is the (token, k) pair it came from) and the scatter half of a reduce-scatter.
+  const int* scatter_row_slot = nullptr;
+  long long scatter_slots_per_rank = 0;
   PeerTable scatter_out = {};
   long long scatter_ld = 0;
 

@@ -313,17 +313,15 @@ class _LocalMoEFn(torch.autograd.Function):
         if fused:
             x = x.contiguous()
             xp = torch.empty(plan.cap_rows, H, device=x.device, dtype=torch.bfloat16)
-            slot = plan.row_slot
-            row_dest = torch.stack([torch.where(slot >= 0, 0, -1), slot.clamp(min=0)], dim=1).to(torch.int32).contiguous()
             ar = torch.arange(N * K, device=x.device, dtype=torch.int32)
             ident = torch.where(plan.slot_row >= 0, ar, torch.full_like(ar, -1))  # slot -> its own row, -1 if dropped
             ys = torch.empty(N * K, H, device=x.device, dtype=torch.bfloat16)
             hact, gu, _ = grouped_swiglu_forward(
                 xp, w13, w2, plan, pull=dict(src_ptrs=[x.data_ptr()], slots_per_src=N * K, pull_K=K, ld_src=H),
-                scatter=dict(row_dest=row_dest, out_ptrs=[ys.data_ptr()], out_ld=H))
+                scatter=dict(row_slot=plan.row_slot, slots_per_rank=N * K, out_ptrs=[ys.data_ptr()], out_ld=H))
             y = torch.empty(N, H, device=x.device, dtype=torch.bfloat16)
             _ext.ext().combine_rows(ys, ident, gate_w32, y, K)
-            ctx.save_for_backward(xp, hact, gu, ys, gate_w32, w13, w2, row_dest, ident)
+            ctx.save_for_backward(xp, hact, gu, ys, gate_w32, w13, w2, ident)
         else:
             xp = kernels.gather_rows(x, plan)
             hact, gu, yp = grouped_swiglu_forward(xp, w13, w2, plan)
@@ -339,7 +337,7 @@ class _LocalMoEFn(torch.autograd.Function):
         plan = ctx.plan
         dy = dy.contiguous()
         if ctx.fused:
-            xp, hact, gu, ys, gate_w32, w13, w2, row_dest, ident = ctx.saved_tensors
+            xp, hact, gu, ys, gate_w32, w13, w2, ident = ctx.saved_tensors
             N, K = gate_w32.shape
             H = xp.shape[1]
             ext = _ext.ext()
@@ -354,7 +352,8 @@ class _LocalMoEFn(torch.autograd.Function):
                 dyp, xp, hact, gu, w13, w2, plan, need_dx=need_dx,
                 pull=dict(src_ptrs=[dy.data_ptr()], slots_per_src=N * K, pull_K=K, ld_src=H,
                           slot_scale=gate_w32.reshape(-1)),
-                scatter=dict(row_dest=row_dest, out_ptrs=[dxs.data_ptr()], out_ld=H) if need_dx else None)
+                scatter=dict(row_slot=plan.row_slot, slots_per_rank=N * K, out_ptrs=[dxs.data_ptr()], out_ld=H)
+                if need_dx else None)
             dx = None
             if need_dx:
                 dx = torch.empty(N, H, device=dy.device, dtype=torch.bfloat16)

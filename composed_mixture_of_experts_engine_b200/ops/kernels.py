@@ -266,16 +266,17 @@ def gemm_pull(A: torch.Tensor, B: torch.Tensor, D: torch.Tensor, plan: MoEPlan, 
     return D
 
 
-def gemm_scatter(A: torch.Tensor, B: torch.Tensor, *, N: int, K: int, row_dest: torch.Tensor, out_ptrs, out_ld: int,
-                 plan: Optional[MoEPlan] = None, groups: int = 1, b_group_rows: int = 0, b_mn: bool = False,
-                 M: int = 0) -> None:
-    """GEMM (grouped by ``plan`` or dense with ``M`` rows) whose epilogue stores output row r at row
-    ``row_dest[r, 1]`` of rank ``row_dest[r, 0]``'s buffer in ``out_ptrs`` (skipped when the rank is negative)."""
+def gemm_scatter(A: torch.Tensor, B: torch.Tensor, *, N: int, K: int, row_slot: torch.Tensor, slots_per_rank: int,
+                 out_ptrs, out_ld: int, plan: Optional[MoEPlan] = None, groups: int = 1, b_group_rows: int = 0,
+                 b_mn: bool = False, M: int = 0) -> None:
+    """GEMM (grouped by ``plan`` or dense with ``M`` rows) whose epilogue stores output row r in the buffer of rank
+    ``row_slot[r] // slots_per_rank`` (one of ``out_ptrs``) at row ``row_slot[r] % slots_per_rank``; rows with a
+    negative slot are skipped."""
     dummy = A  # D is not written in scatter mode; any bf16 2-D tensor satisfies the binding's checks
     if plan is not None:
         _ext.ext().gemm_scatter(A, B, dummy, GEMM_GROUPED_M, 0, N, K, b_mn, groups, b_group_rows, plan.tile_group,
-                                plan.num_m_tiles, plan.max_m_tiles, row_dest, list(out_ptrs), out_ld,
+                                plan.num_m_tiles, plan.max_m_tiles, row_slot, slots_per_rank, list(out_ptrs), out_ld,
                                 status_word(A.device), 0)
     else:
-        _ext.ext().gemm_scatter(A, B, dummy, GEMM_DENSE, M, N, K, b_mn, 1, 0, None, None, 0, row_dest, list(out_ptrs),
-                                out_ld, status_word(A.device), 0)
+        _ext.ext().gemm_scatter(A, B, dummy, GEMM_DENSE, M, N, K, b_mn, 1, 0, None, None, 0, row_slot, slots_per_rank,
+                                list(out_ptrs), out_ld, status_word(A.device), 0)

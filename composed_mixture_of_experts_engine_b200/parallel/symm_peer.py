@@ -62,15 +62,6 @@ def _push() -> bool:
     return os.environ.get("CMOE_EP_PUSH", "1") != "0"
 
 
-def _row_dest(row_slot: torch.Tensor, slots_per_rank: int) -> torch.Tensor:
-    """[rows, 2] int32 (rank, row) of every expert-sorted row's home: slot s belongs to rank s // slots_per_rank and
-    lands in row s % slots_per_rank of its buffer; padding rows (slot < 0) get rank -1."""
-    slot = row_slot.to(torch.int64)
-    rank = torch.where(slot >= 0, slot // slots_per_rank, torch.full_like(slot, -1))
-    row = torch.where(slot >= 0, slot % slots_per_rank, torch.zeros_like(slot))
-    return torch.stack([rank, row], dim=1).to(torch.int32).contiguous()
-
-
 def _fused() -> bool:
     """Dispatch inside the grouped GEMM (default) or as a separate pull kernel (``CMOE_EP_FUSED=0``)."""
     return os.environ.get("CMOE_EP_FUSED", "1") != "0"
@@ -178,11 +169,9 @@ class _EPMoEPeer(torch.autograd.Function):
         y = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
         if push:
             ycs = pc.per_layer(lkey, "ycomb", T * K * H * 2)
-            row_dest = _row_dest(plan.row_slot, T * K)
-            kw = dict(scatter=dict(row_dest=row_dest, out_ptrs=_ptrs(ycs), out_ld=H))
+            kw = dict(scatter=dict(row_slot=plan.row_slot, slots_per_rank=T * K, out_ptrs=_ptrs(ycs), out_ld=H))
         else:
             yps = pc.per_layer(lkey, "yp", cap_rows * H * 2)
-            row_dest = None
             kw = dict(yp_out=yps.view(torch.bfloat16, cap_rows * H).view(cap_rows, H))
         if _fused():
             # the dispatch runs inside the first grouped GEMM: rows stream in over NVLink tile by tile
@@ -196,7 +185,7 @@ class _EPMoEPeer(torch.autograd.Function):
                                   ycs.view(torch.bfloat16, T * K * H).view(T * K, H))
         else:
             ext.combine_rows_peer(_ptrs(yps), _ptrs(srow), idx32, erank, gate_w32, y, K, pc.rank * T * K, H, None)
-        ctx.push, ctx.row_dest = push, row_dest
+        ctx.push = push
 
         ctx.save_for_backward(xp, hact, gu, w_all, w13, w2, idx32, gate_w32)
         ctx.plan, ctx.pc, ctx.lkey, ctx.cap_rows = plan, pc, lkey, cap_rows
@@ -236,7 +225,7 @@ class _EPMoEPeer(torch.autograd.Function):
         kw = {}
         if push:
             dxs = pc.shared("dxcomb", T * K * H * 2)
-            kw["scatter"] = dict(row_dest=ctx.row_dest, out_ptrs=_ptrs(dxs), out_ld=H)
+            kw["scatter"] = dict(row_slot=plan.row_slot, slots_per_rank=T * K, out_ptrs=_ptrs(dxs), out_ld=H)
         else:
             dxs = pc.shared("dxp", cap_rows * H * 2)
             kw["dxp_out"] = dxs.view(torch.bfloat16, cap_rows * H).view(cap_rows, H)

@@ -35,7 +35,7 @@ class _TPContext:
         self.flag_ptrs = [int(p) for p in self.sg.flags.handle.buffer_ptrs]
         self._bufs: Dict[str, symm.SymmBuffer] = {}
         self._plans: Dict[Tuple[int, int], Tuple[MoEPlan, torch.Tensor]] = {}
-        self._scatter: Dict[Tuple[int, int], Tuple[torch.Tensor, torch.Tensor]] = {}
+        self._scatter: Dict[Tuple[int, int], Tuple[torch.Tensor, int, torch.Tensor]] = {}
 
     def barrier(self) -> None:
         self.sg.epoch += 1
@@ -71,19 +71,21 @@ class _TPContext:
         self._plans[key] = (plan, own.contiguous())
         return self._plans[key]
 
-    def scatter_plan(self, batch: int, s_local: int) -> Tuple[torch.Tensor, torch.Tensor]:
-        """(row_dest [batch*tp*s_local, 2], identity row map [batch*s_local]): full row (b, r, s) of this rank's
-        partial result goes to rank r, row  rank * batch*s_local + b*s_local + s  of its staging buffer."""
+    def scatter_plan(self, batch: int, s_local: int) -> Tuple[torch.Tensor, int, torch.Tensor]:
+        """(row slots [batch*tp*s_local], slots per rank, identity row map [batch*s_local]): full row (b, r, s) of this
+        rank's partial result goes to rank r, row  rank * batch*s_local + b*s_local + s  of its staging buffer; as a
+        slot number that is  r * slots_per_rank + row."""
         key = (batch, s_local)
         hit = self._scatter.get(key)
         if hit is None:
             dev, tp = self.topo.device, self.world
+            per_rank = tp * batch * s_local
             b = torch.arange(batch, device=dev).view(batch, 1, 1)
             r = torch.arange(tp, device=dev).view(1, tp, 1)
             s = torch.arange(s_local, device=dev).view(1, 1, s_local)
-            row = (self.rank * (batch * s_local) + b * s_local + s).expand(batch, tp, s_local)
-            dest = torch.stack([r.expand(batch, tp, s_local), row], dim=-1).reshape(-1, 2).to(torch.int32).contiguous()
-            hit = (dest, torch.arange(batch * s_local, device=dev, dtype=torch.int32))
+            slot = r * per_rank + self.rank * (batch * s_local) + b * s_local + s
+            hit = (slot.reshape(-1).to(torch.int32).contiguous(), per_rank,
+                   torch.arange(batch * s_local, device=dev, dtype=torch.int32))
             self._scatter[key] = hit
         return hit
 
@@ -153,11 +155,11 @@ def _gemm_reduce_scatter(c: _TPContext, x2d: torch.Tensor, weight: torch.Tensor,
     rows = x2d.shape[0]
     N = weight.shape[1] if b_mn else weight.shape[0]
     shard_rows = batch * s_local
-    dest, ident = c.scatter_plan(batch, s_local)
+    slots, per_rank, ident = c.scatter_plan(batch, s_local)
     stage = c.buf(name + ".stage", c.world * shard_rows * N * 2)
     c.barrier()  # every rank has finished reading its slabs of the previous call
-    kernels.gemm_scatter(x2d, weight, N=N, K=x2d.shape[1], row_dest=dest, out_ptrs=_ptrs(stage), out_ld=N, b_mn=b_mn,
-                         M=rows)
+    kernels.gemm_scatter(x2d, weight, N=N, K=x2d.shape[1], row_slot=slots, slots_per_rank=per_rank,
+                         out_ptrs=_ptrs(stage), out_ld=N, b_mn=b_mn, M=rows)
     c.barrier()
     out = torch.empty(shard_rows, N, device=x2d.device, dtype=torch.bfloat16)
     base = stage.local.data_ptr()

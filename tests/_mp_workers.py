@@ -199,6 +199,38 @@ def trainer_steps(rank, world, config_path, steps):
             "local_experts": tr.model.blocks[0].moe.local_expert_ids}
 
 
+def moe_layer_tp(rank, world):
+    """MoE layer with the experts sliced on the FFN width over tp=world ranks vs the unsliced layer: output, token
+    gradient, router gate gradient (needs the all-reduce of the partial gate-weight gradients) and weight slices."""
+    import torch
+
+    from composed_mixture_of_experts_engine_b200.parallel import DistributedMoELayer, build_topology
+
+    H, F, E, K, N = 16, 32, 4, 2, 20
+    topo = build_topology(1, 1, tp_size=world, device_type="cpu")
+    torch.manual_seed(0)
+    full = DistributedMoELayer(H, F, E, K)
+    layer = DistributedMoELayer(H, F, E, K, topology=topo)
+    fl = F // world
+    lo, hi = rank * fl, (rank + 1) * fl
+    with torch.no_grad():
+        layer.router.gate_w.copy_(full.router.gate_w)
+        layer.w13.copy_(torch.cat([full.w13[:, lo:hi], full.w13[:, F + lo:F + hi]], dim=1))
+        layer.w2.copy_(full.w2[:, :, lo:hi])
+    torch.manual_seed(7)  # the same tokens on every tensor-parallel rank
+    x = torch.randn(N, H, requires_grad=True)
+    y = layer(x)
+    y.pow(2).sum().backward()
+    x2 = x.detach().clone().requires_grad_(True)
+    y2 = full(x2)
+    y2.pow(2).sum().backward()
+    g13 = torch.cat([full.w13.grad[:, lo:hi], full.w13.grad[:, F + lo:F + hi]], dim=1)
+    return {"y": float((y - y2).abs().max()), "dx": float((x.grad - x2.grad).abs().max()),
+            "dgate": float((layer.router.gate_w.grad - full.router.gate_w.grad).abs().max()),
+            "dw13": float((layer.w13.grad - g13).abs().max()),
+            "dw2": float((layer.w2.grad - full.w2.grad[:, :, lo:hi]).abs().max())}
+
+
 def trainer_hybrid(rank, world, dp, ep, tp, pp, steps):
     """The public Trainer with tensor (+ sequence) and pipeline parallelism on gloo ranks: tiny fp32 decoder, 1F1B over
     4 microbatches.  Returns the per-step losses this rank saw (only the last pipeline stage sees them)."""

@@ -493,10 +493,9 @@ def test_gemm_with_fused_row_pull_matches_gather_then_gemm(ext, status):
 
 
 def test_gemm_with_fused_scatter_matches_gemm_then_scatter(ext, status):
-    """The grouped GEMM whose epilogue stores each result row at its home (rank, row) (fused combine push) vs the
+    """The grouped GEMM whose epilogue stores each result row at the home of its slot (fused combine push) vs the
     plain grouped GEMM followed by an index copy.  Two local buffers stand in for the two ranks."""
     from composed_mixture_of_experts_engine_b200.ops import kernels
-    from composed_mixture_of_experts_engine_b200.parallel.symm_peer import _row_dest
 
     torch.manual_seed(13)
     T, K, E, H, F = 1100, 2, 4, 256, 512
@@ -507,10 +506,9 @@ def test_gemm_with_fused_scatter_matches_gemm_then_scatter(ext, status):
     yp = torch.empty(plan.cap_rows, H, device="cuda", dtype=torch.bfloat16)
     kernels.gemm(hact, W2.view(-1, F), yp, mode=GROUPED_M, N=H, K=F, groups=E, b_group_rows=H,
                  tile_group=plan.tile_group, num_m_tiles=plan.num_m_tiles, max_m_tiles=plan.max_m_tiles)
-    dest = _row_dest(plan.row_slot, T * K)
     outs = [torch.full((T * K, H), 7.0, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
-    kernels.gemm_scatter(hact, W2.view(-1, F), N=H, K=F, row_dest=dest, out_ptrs=[o.data_ptr() for o in outs],
-                         out_ld=H, plan=plan, groups=E, b_group_rows=H)
+    kernels.gemm_scatter(hact, W2.view(-1, F), N=H, K=F, row_slot=plan.row_slot, slots_per_rank=T * K,
+                         out_ptrs=[o.data_ptr() for o in outs], out_ld=H, plan=plan, groups=E, b_group_rows=H)
     torch.cuda.synchronize()
     kernels.check_status(torch.device("cuda", 0))
     n = int(plan.num_m_tiles) * 128

@@ -109,3 +109,10 @@ def test_trainer_hybrid_tp_sp_pp(dp, ep, tp, pp):
         for name in a["replicated"]:  # parameters replicated over the tensor-parallel group stay identical
             diff = max(abs(x - y) for x, y in zip(a["replicated"][name], b["replicated"][name]))
             assert diff < 1e-6, (name, diff)
+
+
+def test_moe_layer_tensor_parallel_matches_unsliced():
+    res = _spawn("moe_layer_tp", 2)
+    for r, out in res.items():
+        for k, v in out.items():
+            assert v < 1e-4, (r, k, v, out)
