@@ -71,7 +71,9 @@ def main() -> int:
     if world > 1:
         dist.init_process_group("nccl", rank=rank, world_size=world)
 
-    from composed_mixture_of_experts_engine_b200.ops.kernels import check_status
+    if args.zipf > 0:  # skewed routing: size the row buffers for the worst case so that nothing is dropped
+        os.environ["CMOE_EP_BUFFER_FACTOR"] = str(world)
+    from composed_mixture_of_experts_engine_b200.ops.kernels import check_status, overflow_counter
     from composed_mixture_of_experts_engine_b200.parallel import DistributedMoELayer, build_topology
 
     H, F, E, K, T = args.hidden, args.ffn, args.experts, args.top_k, args.tokens
@@ -141,6 +143,8 @@ def main() -> int:
     for name, v in out["transports"].items():
         v["exposed_dispatch_combine_fwd_us"] = (v["fwd_ms"] - lf) * 1e3
         v["exposed_dispatch_combine_fwd_bwd_us"] = (v["fwd_bwd_ms"] - lfb) * 1e3
+    out["rows_dropped_for_buffer_space"] = int(overflow_counter(dev).item()) if world > 1 else 0
+    out["rows_this_rank"] = rows
     if rank == 0:
         print(json.dumps(out))
     if dist.is_initialized():

@@ -214,6 +214,11 @@ def moe_plan(topk_idx: torch.Tensor, num_experts: int, expert_lo: int = 0, n_loc
     ext.moe_plan(topk_idx, K, num_experts, expert_lo, n_local, per_k, capacity, plan.slot_row, plan.row_slot,
                  plan.group_offsets, plan.tile_group, plan.num_m_tiles, plan.counts_kept,
                  _scratch_i32(topk_idx.device, words), overflow_counter(topk_idx.device))
+    from . import debug
+
+    if debug.enabled():  # validate every index before a gather / GEMM / combine kernel consumes the plan
+        debug.check_plan(plan.slot_row, plan.row_slot, plan.tile_group, plan.num_m_tiles, plan.group_offsets, n_local,
+                         cap_rows, N * K)
     return plan
 
 

@@ -4,7 +4,7 @@ One :class:`SymmGroup` per process group: buffers are allocated with ``torch.dis
 (CUDA virtual memory mapped into every peer of the group over NVLink), and what the kernels receive is a
 small device table of the peers' base addresses.  Nothing here launches a kernel that waits without a bound.
 
-The reference has no counterpart: it only calls NCCL / gloo collectives (SURVEY of call sites:
+The reference has no counterpart: it only calls NCCL / gloo collectives (call sites:
 pkg/distributed/expert_parallel.py:104-218, tensor_parallel.py:128,201).
 """
 

@@ -76,6 +76,11 @@ class StepRecord:
             self.routing.setdefault(name, getattr(self, name))
 
 
+def _nvtx_enabled() -> bool:
+    """``CMOE_NVTX=1`` wraps every timed phase (and the trainer's microbatches / optimizer step) in an NVTX range."""
+    return os.environ.get("CMOE_NVTX", "0") not in ("", "0") and torch.cuda.is_available()
+
+
 class PhaseTimer:
     """Named CUDA-event pairs, resolved lazily.
 
@@ -94,6 +99,9 @@ class PhaseTimer:
             self.t, self.name = timer, name
 
         def __enter__(self):
+            self.nvtx = _nvtx_enabled()
+            if self.nvtx:  # a named range in Nsight Systems / CUPTI timelines, independent of the event timing
+                torch.cuda.nvtx.range_push(self.name)
             if not self.t.enabled:
                 return self
             if torch.cuda.is_available():
@@ -105,6 +113,8 @@ class PhaseTimer:
             return self
 
         def __exit__(self, *exc):
+            if self.nvtx:
+                torch.cuda.nvtx.range_pop()
             if not self.t.enabled:
                 return False
             if torch.cuda.is_available():

@@ -338,6 +338,29 @@ def gpu_trainer(rank, world, transport, steps):
             "n_local": len(tr.model.blocks[0].moe.local_expert_ids)}
 
 
+def gpu_trainer_hybrid(rank, world, dp, ep, tp, pp, steps):
+    """bf16 Trainer on GPUs with pipeline (and optionally tensor / expert) parallelism: NCCL 1F1B, fused optimizer."""
+    import torch
+
+    from composed_mixture_of_experts_engine_b200.engine import Trainer
+    from composed_mixture_of_experts_engine_b200.ops.kernels import check_status
+    from composed_mixture_of_experts_engine_b200.utils.config import MoEConfig
+
+    cfg = MoEConfig.from_dict({
+        "model": dict(arch="moe_decoder", hidden_dim=256, num_layers=4, num_heads=4, num_experts=8, top_k=2,
+                      ffn_dim=256, vocab_size=2048, sequence_length=256, dtype="bfloat16", aux_loss_coeff=0.01,
+                      init_std=0.02),
+        "training": dict(micro_batch_size=2, gradient_accumulation_steps=4, global_batch_size=8 * dp, max_steps=100,
+                         warmup_steps=0, learning_rate=1e-3, grad_clip=1.0),
+        "parallelism": dict(data_parallel=dp, expert_parallel=ep, tensor_parallel=tp, pipeline_parallel=pp,
+                            ep_from_dp=True, sequence_parallel=tp > 1)})
+    tr = Trainer(cfg)
+    ids, tgt = tr.synthetic_batch(torch.Generator().manual_seed(tr.topology.dp_rank))
+    losses = [float(tr.train_step(ids, tgt)) for _ in range(steps)]
+    check_status(tr.device)
+    return {"losses": losses, "last": tr.topology.is_last_pp_stage(), "n_blocks": len(tr.model.blocks)}
+
+
 def gpu_tp_sp(rank, world, transport="auto"):
     """Sequence-parallel column -> SiLU -> row pair over tp=world GPUs on the peer-memory path vs unsharded."""
     import torch

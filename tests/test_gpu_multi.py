@@ -74,3 +74,15 @@ def test_sequence_parallel_linears_on_peer_memory(transport):
     for r, out in res.items():
         for k, v in out.items():
             assert v < 4e-2, (r, k, v, out)
+
+
+def test_trainer_pipeline_parallel_on_gpus():
+    """Two pipeline stages over NCCL (1F1B, 4 microbatches), bf16 kernels and the fused optimizer on every stage; with
+    four GPUs also tensor + sequence parallelism inside each stage."""
+    world = _world()
+    tp = 2 if world == 4 else 1
+    res = _spawn_gpu("gpu_trainer_hybrid", world, 1, 1, tp, 2, 8)
+    last = [out for out in res.values() if out["last"]]
+    assert len(last) == world // 2 and all(out["n_blocks"] == 2 for out in res.values())
+    for out in last:
+        assert all(math.isfinite(l) for l in out["losses"]) and out["losses"][-1] < out["losses"][0]
