@@ -92,7 +92,8 @@ struct KParams {
   long long scatter_slots_per_rank;
   PeerTable scatter_out;
   long long scatter_ld;
-  int out_mode;  // OutMode (EPI_STORE only)
+  int out_mode;    // OutMode (EPI_STORE only)
+  int fwd_staged;  // SwiGLU forward: h (tmD) and gate|up (tmE) leave through the staging area and TMA stores
 };
 
 struct Tile {
@@ -261,7 +262,7 @@ __device__ __forceinline__ void swiglu_bwd_chunk(const uint32_t (&r)[32], const 
 template <int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS_PULL, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const __grid_constant__ CUtensorMap tmD, const KParams p) {
+            const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmE, const KParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -296,6 +297,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
     tma_prefetch_desc(&tmD);
+    tma_prefetch_desc(&tmE);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -629,6 +631,74 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (any_bad) break;
         continue;
       }
+      if (EPI == EPI_SWIGLU_FWD && p.fwd_staged) {
+        // ---- staged SwiGLU forward: 32 output columns at a time, h / gate / up as three pieces of 128 rows x 64
+        // bytes (64-byte swizzle) in one staging buffer; two named barriers per piece (buffer free, buffer filled)
+        const int gsw = (row_in_tile >> 1) & 3;
+        uint8_t* hrow = stg + row_in_tile * 64;
+        bool any_bad = false;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          const int col = ti.n0 + c * 32;
+          if (col >= p.N) break;  // uniform
+          uint32_t ph[16], pg[16], pu[16];
+          if (ok) {
+            uint32_t rg[32], ru[32];
+            tmem_ld_32x32b_x32(t_acc + c * 32, rg);
+            tmem_ld_32x32b_x32(t_acc + 128 + c * 32, ru);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float g0 = __uint_as_float(rg[2 * j]), g1 = __uint_as_float(rg[2 * j + 1]);
+              const float u0 = __uint_as_float(ru[2 * j]), u1 = __uint_as_float(ru[2 * j + 1]);
+              ph[j] = pack_bf16x2(g0 * sigmoidf_fast(g0) * u0, g1 * sigmoidf_fast(g1) * u1);
+              pg[j] = pack_bf16x2(g0, g1);
+              pu[j] = pack_bf16x2(u0, u1);
+            }
+          }
+          // the stores issued for the previous piece have read the buffer
+          if (threadIdx.x == EPI_FIRST_THREAD) bulk_wait_group_read<0>();
+          {
+            const int bad = (!ok || *abort_flag) ? 1 : 0;
+            int any;
+            asm volatile(
+                "{\n\t.reg .pred q, r;\n\tsetp.ne.s32 q, %1, 0;\n\tbar.red.or.pred r, 1, 128, q;\n\t"
+                "selp.s32 %0, 1, 0, r;\n\t}"
+                : "=r"(any)
+                : "r"(bad)
+                : "memory");
+            any_bad = any != 0;
+          }
+          if (any_bad) break;  // uniform over the 128 epilogue threads
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int o = (j ^ gsw) << 4;
+            *reinterpret_cast<uint4*>(hrow + o) = make_uint4(ph[4 * j], ph[4 * j + 1], ph[4 * j + 2], ph[4 * j + 3]);
+            if (p.aux_out != nullptr) {
+              *reinterpret_cast<uint4*>(hrow + STAGING_BUF_BYTES / 2 + o) =
+                  make_uint4(pg[4 * j], pg[4 * j + 1], pg[4 * j + 2], pg[4 * j + 3]);
+              *reinterpret_cast<uint4*>(hrow + STAGING_BUF_BYTES + o) =
+                  make_uint4(pu[4 * j], pu[4 * j + 1], pu[4 * j + 2], pu[4 * j + 3]);
+            }
+          }
+          fence_proxy_async_smem();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (threadIdx.x == EPI_FIRST_THREAD) {
+            tma_store_3d(&tmD, stg, col, ti.m0, 0);
+            if (p.aux_out != nullptr) {
+              tma_store_3d(&tmE, stg + STAGING_BUF_BYTES / 2, col, 0, ti.m0);  // gate half
+              tma_store_3d(&tmE, stg + STAGING_BUF_BYTES, col, 1, ti.m0);      // up half
+            }
+            bulk_commit_group();
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(&tempty_bar[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+        if (any_bad) break;
+        continue;
+      }
       if (ok) {
         if (EPI == EPI_STORE) {
           if (p.accumulate && p.d_fp32) {
@@ -738,7 +808,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if (*abort_flag) break;
     }
     // shared memory and the kernel's results must outlive the TMA stores still in flight
-    if (threadIdx.x == EPI_FIRST_THREAD && (p.out_mode == OUT_TMA_STORE || p.out_mode == OUT_TMA_REDUCE))
+    if (threadIdx.x == EPI_FIRST_THREAD &&
+        (p.out_mode == OUT_TMA_STORE || p.out_mode == OUT_TMA_REDUCE || (EPI == EPI_SWIGLU_FWD && p.fwd_staged)))
       bulk_wait_group<0>();
   }
 
@@ -842,27 +913,29 @@ cudaError_t make_tmap(CUtensorMap* out, const void* ptr, long long rows, long lo
 // Output map: [groups, rows, cols] of fp32 or bf16 with row stride ld and group stride gstride (elements); the box
 // is one staging buffer, 128 rows x 128 bytes, 128-byte swizzle.
 cudaError_t make_tmap_out(CUtensorMap* out, const void* ptr, int fp32, long long groups, long long rows,
-                          long long cols, long long ld, long long gstride) {
+                          long long cols, long long ld, long long gstride, int box_bytes = 128) {
   struct Key {
     const void* ptr;
     long long groups, rows, cols, ld, gstride;
-    int fp32;
+    int fp32, box_bytes;
     bool operator==(const Key& o) const {
       return ptr == o.ptr && groups == o.groups && rows == o.rows && cols == o.cols && ld == o.ld &&
-             gstride == o.gstride && fp32 == o.fp32;
+             gstride == o.gstride && fp32 == o.fp32 && box_bytes == o.box_bytes;
     }
   };
   struct KeyHash {
     size_t operator()(const Key& k) const {
       size_t h = reinterpret_cast<size_t>(k.ptr);
-      for (long long v : {k.groups, k.rows, k.cols, k.ld, k.gstride, static_cast<long long>(k.fp32)})
+      for (long long v : {k.groups, k.rows, k.cols, k.ld, k.gstride, static_cast<long long>(k.fp32),
+                          static_cast<long long>(k.box_bytes)})
         h = h * 1000003u ^ static_cast<size_t>(v);
       return h;
     }
   };
   static std::mutex mu;
   static std::unordered_map<Key, CUtensorMap, KeyHash> cache;
-  Key key{ptr, groups, rows, cols, ld, gstride, fp32};
+  if (box_bytes != 128 && box_bytes != 64) return cudaErrorInvalidValue;
+  Key key{ptr, groups, rows, cols, ld, gstride, fp32, box_bytes};
   {
     std::lock_guard<std::mutex> lk(mu);
     auto it = cache.find(key);
@@ -876,16 +949,61 @@ cudaError_t make_tmap_out(CUtensorMap* out, const void* ptr, int fp32, long long
   const long long es = fp32 ? 4 : 2;
   cuuint64_t gdim[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(groups)};
   cuuint64_t gstr[2] = {static_cast<cuuint64_t>(ld * es), static_cast<cuuint64_t>(gstride * es)};
-  cuuint32_t box[3] = {static_cast<cuuint32_t>(128 / es), static_cast<cuuint32_t>(BM), 1u};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(box_bytes / es), static_cast<cuuint32_t>(BM), 1u};
   cuuint32_t estride[3] = {1u, 1u, 1u};
   CUresult r = enc(out, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
                    const_cast<void*>(ptr), gdim, gstr, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     std::fprintf(stderr, "cmoe: cuTensorMapEncodeTiled (output) failed (%d) groups=%lld rows=%lld cols=%lld ld=%lld\n",
                  static_cast<int>(r), groups, rows, cols, ld);
     return cudaErrorInvalidValue;
   }
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    if (cache.size() > 8192) cache.clear();
+    cache.emplace(key, *out);
+  }
+  return cudaSuccess;
+}
+
+// bf16 [rows, 2N] viewed as [rows, 2 halves, N] (gate | up): dims (N, 2, rows), box 32 columns x 1 half x 128 rows,
+// 64-byte swizzle; a store of columns [c, c+32) of one half is clipped at N and never reaches into the other half
+cudaError_t make_tmap_halves(CUtensorMap* out, const void* ptr, long long rows, long long n, long long ld) {
+  struct Key {
+    const void* ptr;
+    long long rows, n, ld;
+    bool operator==(const Key& o) const { return ptr == o.ptr && rows == o.rows && n == o.n && ld == o.ld; }
+  };
+  struct KeyHash {
+    size_t operator()(const Key& k) const {
+      size_t h = reinterpret_cast<size_t>(k.ptr);
+      for (long long v : {k.rows, k.n, k.ld}) h = h * 1000003u ^ static_cast<size_t>(v);
+      return h;
+    }
+  };
+  static std::mutex mu;
+  static std::unordered_map<Key, CUtensorMap, KeyHash> cache;
+  Key key{ptr, rows, n, ld};
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return cudaSuccess;
+    }
+  }
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return cudaErrorNotSupported;
+  cuuint64_t gdim[3] = {static_cast<cuuint64_t>(n), 2u, static_cast<cuuint64_t>(rows)};
+  cuuint64_t gstr[2] = {static_cast<cuuint64_t>(n * 2), static_cast<cuuint64_t>(ld * 2)};
+  cuuint32_t box[3] = {32u, 1u, static_cast<cuuint32_t>(BM)};
+  cuuint32_t estride[3] = {1u, 1u, 1u};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), gdim, gstr, box, estride,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
   {
     std::lock_guard<std::mutex> lk(mu);
     if (cache.size() > 8192) cache.clear();
@@ -904,8 +1022,8 @@ bool direct_epilogue_forced() {
 }
 
 template <int EPI>
-cudaError_t launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const KParams& kp,
-                           int grid, cudaStream_t stream) {
+cudaError_t launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD,
+                           const CUtensorMap& tmE, const KParams& kp, int grid, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -913,7 +1031,7 @@ cudaError_t launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const
     configured = true;
   }
   const int threads = kp.pull_row_slot != nullptr ? GEMM_THREADS_PULL : GEMM_THREADS;
-  gemm_kernel<EPI><<<grid, threads, SMEM_BYTES, stream>>>(tmA, tmB, tmD, kp);
+  gemm_kernel<EPI><<<grid, threads, SMEM_BYTES, stream>>>(tmA, tmB, tmD, tmE, kp);
   return cudaGetLastError();
 }
 
@@ -992,6 +1110,20 @@ cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream) {
         kp.out_mode = a.accumulate ? OUT_TMA_REDUCE : OUT_TMA_STORE;
     }
   }
+  CUtensorMap tmE = tmA;  // placeholder unless the SwiGLU forward stages its gate|up output
+  kp.fwd_staged = 0;
+  if (a.epilogue == EPI_SWIGLU_FWD && !direct_epilogue_forced() && a.mode != GEMM_GROUPED_K) {
+    // h [rows, N] and the optional gate|up copy [rows, 2N] (as [2 halves, rows, N]) leave through TMA stores
+    const long long d_rows = a.mode == GEMM_GROUPED_M ? a.a_rows : a.M;
+    bool okmaps = !a.d_fp32 && (reinterpret_cast<uintptr_t>(a.D) & 15u) == 0 && (a.ldd * 2) % 16 == 0 && d_rows > 0 &&
+                  make_tmap_out(&tmD, a.D, 0, 1, d_rows, a.N, a.ldd, d_rows * a.ldd, 64) == cudaSuccess;
+    if (okmaps && a.aux_out != nullptr) {
+      okmaps = (reinterpret_cast<uintptr_t>(a.aux_out) & 15u) == 0 && (a.ld_aux_out * 2) % 16 == 0 &&
+               a.ld_aux_out >= 2LL * a.N &&
+               make_tmap_halves(&tmE, a.aux_out, d_rows, a.N, a.ld_aux_out) == cudaSuccess;
+    }
+    kp.fwd_staged = okmaps ? 1 : 0;
+  }
   if (a.epilogue == EPI_SWIGLU_BWD) {
     // the saved gate|up matrix [rows, 2N] comes into the epilogue through TMA (pieces of 128 rows x 32 columns)
     if (a.aux_in == nullptr || a.ld_aux_in < 2LL * a.N) return cudaErrorInvalidValue;
@@ -1028,11 +1160,11 @@ cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream) {
 
   switch (a.epilogue) {
     case EPI_STORE:
-      return launch_variant<EPI_STORE>(tmA, tmB, tmD, kp, grid, stream);
+      return launch_variant<EPI_STORE>(tmA, tmB, tmD, tmE, kp, grid, stream);
     case EPI_SWIGLU_FWD:
-      return launch_variant<EPI_SWIGLU_FWD>(tmA, tmB, tmD, kp, grid, stream);
+      return launch_variant<EPI_SWIGLU_FWD>(tmA, tmB, tmD, tmE, kp, grid, stream);
     case EPI_SWIGLU_BWD:
-      return launch_variant<EPI_SWIGLU_BWD>(tmA, tmB, tmD, kp, grid, stream);
+      return launch_variant<EPI_SWIGLU_BWD>(tmA, tmB, tmD, tmE, kp, grid, stream);
     default:
       return cudaErrorInvalidValue;
   }
