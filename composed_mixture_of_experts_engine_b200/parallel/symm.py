@@ -16,6 +16,8 @@ from typing import Dict, Optional, Tuple
 import torch
 import torch.distributed as dist
 
+from ..ops import debug
+
 from .mesh import ParallelTopology, dp_process_group, ep_process_group, tp_process_group
 
 _GROUPS: Dict[Tuple[str, Tuple[int, ...]], "SymmGroup"] = {}
@@ -45,13 +47,22 @@ def enabled_for(topo: Optional[ParallelTopology], axis: str) -> bool:
 
 
 class SymmBuffer:
-    """A buffer that exists at the same size on every rank of a group, with all peers' addresses."""
+    """A buffer that exists at the same size on every rank of a group, with all peers' addresses.
 
-    def __init__(self, local: torch.Tensor, handle, world: int):
-        self.local = local
+    ``local`` is this rank's usable part; ``ptrs()`` are the addresses of the same part on every rank.  With
+    ``CMOE_DEBUG_BOUNDS=1`` the allocation carries a guard band on either side (``guard``), which
+    ``SymmGroup.verify_guards`` checks: a peer kernel that wrote outside its buffer shows up there."""
+
+    def __init__(self, full: torch.Tensor, handle, world: int, nbytes: int, guard=None):
+        self.full = full
         self.handle = handle
-        self.peer_ptrs = torch.tensor([int(p) for p in handle.buffer_ptrs], dtype=torch.int64, device=local.device)
+        self.guard = guard
+        self.offset = debug.GUARD_BYTES if guard is not None else 0
+        self.local = full[self.offset:self.offset + nbytes]
         self.world = world
+
+    def ptrs(self):
+        return [int(p) + self.offset for p in self.handle.buffer_ptrs]
 
     def view(self, dtype: torch.dtype, numel: int, offset_bytes: int = 0) -> torch.Tensor:
         raw = self.local.view(torch.uint8)[offset_bytes:offset_bytes + numel * torch.empty((), dtype=dtype).element_size()]
@@ -79,6 +90,8 @@ class SymmGroup:
         if buf is not None and buf.local.numel() >= nbytes:
             return buf
         nbytes = (nbytes + 4095) // 4096 * 4096
+        guarded = debug.enabled()
+        total = nbytes + (2 * debug.GUARD_BYTES if guarded else 0)
         try:  # older torch versions want the group registered first; newer ones ignore / deprecate the call
             import warnings
 
@@ -87,11 +100,18 @@ class SymmGroup:
                 symm_mem.enable_symm_mem_for_group(self.group.group_name)
         except Exception:
             pass
-        t = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+        t = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
         handle = symm_mem.rendezvous(t, self.group)
-        buf = SymmBuffer(t, handle, self.world)
+        buf = SymmBuffer(t, handle, self.world, nbytes, debug.Canary(t, nbytes) if guarded else None)
         self._buffers[name] = buf
         return buf
+
+    def verify_guards(self) -> None:
+        """Debug mode: raise if anything (this rank or a peer) wrote outside one of this group's buffers."""
+        torch.cuda.synchronize(self.device)
+        for name, buf in self._buffers.items():
+            if buf.guard is not None:
+                buf.guard.verify(name)
 
     def get(self, name: str) -> Optional[SymmBuffer]:
         return self._buffers.get(name)

@@ -66,9 +66,9 @@ class DPPeer:
         self.flat_g = self.gbuf.view(grad_dtype, numel)
         self.flat_p.zero_()
         self.flat_g.zero_()
-        self.p_ptrs = [int(p) for p in self.pbuf.handle.buffer_ptrs]
-        self.g_ptrs = [int(p) for p in self.gbuf.handle.buffer_ptrs]
-        self.flag_ptrs = [int(p) for p in self.sg.flags.handle.buffer_ptrs]
+        self.p_ptrs = self.pbuf.ptrs()
+        self.g_ptrs = self.gbuf.ptrs()
+        self.flag_ptrs = self.sg.flags.ptrs()
         self.device = topo.device
         self._ext, self._kernels = _ext, kernels
 

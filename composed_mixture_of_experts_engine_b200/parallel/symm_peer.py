@@ -75,7 +75,7 @@ class _EPContext:
         self.group = symm.group_for(topo, "ep")
         self.rank, self.world = self.group.rank, self.group.world
         self.flags = self.group.flags
-        self.flag_ptrs = [int(p) for p in self.flags.handle.buffer_ptrs]
+        self.flag_ptrs = self.flags.ptrs()
         self.epoch = 0
         self._shared: Dict[str, symm.SymmBuffer] = {}
         self._layer: Dict[tuple, symm.SymmBuffer] = {}
@@ -134,7 +134,7 @@ def _layer_key(layer) -> int:
 
 
 def _ptrs(buf: symm.SymmBuffer) -> List[int]:
-    return [int(p) for p in buf.handle.buffer_ptrs]
+    return buf.ptrs()
 
 
 class _EPMoEPeer(torch.autograd.Function):

@@ -32,7 +32,7 @@ class _TPContext:
         self.topo = topo
         self.sg = symm.group_for(topo, "tp")
         self.rank, self.world = self.sg.rank, self.sg.world
-        self.flag_ptrs = [int(p) for p in self.sg.flags.handle.buffer_ptrs]
+        self.flag_ptrs = self.sg.flags.ptrs()
         self._bufs: Dict[str, symm.SymmBuffer] = {}
         self._plans: Dict[Tuple[int, int], Tuple[MoEPlan, torch.Tensor]] = {}
         self._scatter: Dict[Tuple[int, int], Tuple[torch.Tensor, int, torch.Tensor]] = {}
@@ -101,7 +101,7 @@ def _ctx(topo: ParallelTopology) -> _TPContext:
 
 
 def _ptrs(buf: symm.SymmBuffer) -> List[int]:
-    return [int(p) for p in buf.handle.buffer_ptrs]
+    return buf.ptrs()
 
 
 def _gathered_gemm(c: _TPContext, shard2d: torch.Tensor, weight: torch.Tensor, batch: int, s_local: int,

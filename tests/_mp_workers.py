@@ -261,10 +261,13 @@ def trainer_hybrid(rank, world, dp, ep, tp, pp, steps):
 
 # -------------------------------------------------------------------------------------------------- GPU workers
 def _set_transport(transport):
-    """"nccl", "auto" (peer memory, results pushed by the GEMM epilogues) or "auto-pull" (peer memory, pulled)."""
+    """"nccl", "auto" (peer memory, results pushed by the GEMM epilogues), "auto-pull" (peer memory, pulled) or
+    "auto-debug" (as "auto" with the debug-mode checks switched on)."""
     push = "0" if transport.endswith("-pull") else "1"
     os.environ["CMOE_EP_PUSH"] = os.environ["CMOE_TP_PUSH"] = push
-    os.environ["CMOE_EP_TRANSPORT"] = transport.replace("-pull", "")
+    if transport.endswith("-debug"):  # row-plan index checks + guard bands around the symmetric buffers
+        os.environ["CMOE_DEBUG_BOUNDS"] = "1"
+    os.environ["CMOE_EP_TRANSPORT"] = transport.replace("-pull", "").replace("-debug", "")
 
 
 def gpu_ep_layer(rank, world, transport):
@@ -307,6 +310,10 @@ def gpu_ep_layer(rank, world, transport):
         out[f"dw13_{it}"] = rel(layer.w13.grad, g13[mine[0]:mine[-1] + 1])
         out[f"dgate{it}"] = rel(layer.router.gate_w.grad, full.router.gate_w.grad)
     check_status(dev)
+    if transport.endswith("-debug"):  # nothing (this rank or a peer) wrote outside a symmetric buffer
+        from composed_mixture_of_experts_engine_b200.parallel import symm
+
+        symm.group_for(topo, "ep").verify_guards()
     return out
 
 

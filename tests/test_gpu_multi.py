@@ -51,7 +51,7 @@ def _world():
     return 4 if n >= 4 else 2
 
 
-@pytest.mark.parametrize("transport", ["nccl", "auto", "auto-pull"])
+@pytest.mark.parametrize("transport", ["nccl", "auto", "auto-pull", "auto-debug"])
 def test_ep_layer_matches_single_gpu(transport):
     res = _spawn_gpu("gpu_ep_layer", _world(), transport)
     for r, out in res.items():
