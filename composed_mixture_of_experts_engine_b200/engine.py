@@ -31,7 +31,7 @@ from .parallel.mesh import ParallelTopology, build_topology
 from .parallel.pipeline_parallel import PipelineStage
 from .utils.config import MoEConfig
 
-__all__ = ["Trainer", "init_distributed", "lr_at"]
+__all__ = ["Trainer", "init_distributed", "elastic_generation_store", "lr_at"]
 
 
 def init_distributed(device_type: Optional[str] = None) -> Tuple[int, int]:
@@ -47,8 +47,30 @@ def init_distributed(device_type: Optional[str] = None) -> Tuple[int, int]:
         kwargs = {}
         if use_cuda:
             kwargs["device_id"] = torch.device("cuda", torch.cuda.current_device())
+        store = elastic_generation_store(rank, world)
+        if store is not None:
+            kwargs["store"] = store
         dist.init_process_group(backend="nccl" if use_cuda else "gloo", rank=rank, world_size=world, **kwargs)
     return rank, world
+
+
+def elastic_generation_store(rank: int, world: int):
+    """Under a TorchElastic launcher that restarts workers (``TORCHELASTIC_RESTART_COUNT`` set), a rendezvous store
+    whose keys are private to this restart generation; ``None`` otherwise.
+
+    The launcher's store outlives a worker generation.  A restarted worker that rendezvouses under the same keys
+    can read the address its dead predecessor's peer published and then fails to connect ("connectFullMesh ...
+    Connection refused"); prefixing the keys with the generation makes every restart start from an empty namespace."""
+    gen = os.environ.get("TORCHELASTIC_RESTART_COUNT")
+    addr, port = os.environ.get("MASTER_ADDR"), os.environ.get("MASTER_PORT")
+    if gen is None or not addr or not port:
+        return None
+    from datetime import timedelta
+
+    agent_hosts_store = os.environ.get("TORCHELASTIC_USE_AGENT_STORE", "False").lower() in ("1", "true")
+    base = dist.TCPStore(addr, int(port), world, is_master=(rank == 0 and not agent_hosts_store),
+                         timeout=timedelta(seconds=300), multi_tenant=True)
+    return dist.PrefixStore(f"generation{gen}", base)
 
 
 def lr_at(step: int, base_lr: float, warmup_steps: int, max_steps: int) -> float:

@@ -26,6 +26,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from composed_mixture_of_experts_engine_b200.elastic import AsyncCheckpointer, LocalNVMeAdapter
+from composed_mixture_of_experts_engine_b200.engine import elastic_generation_store
 
 
 def sha(model: nn.Module) -> str:
@@ -43,8 +44,9 @@ def main() -> int:
     kill_step = int(os.environ.get("CHAOS_KILL_STEP", "-1"))
     stall = float(os.environ.get("CHAOS_STALL_S", "0"))
     generation = int(os.environ.get("TORCHELASTIC_RESTART_COUNT", "0"))
-    dist.init_process_group("gloo")
-    rank, world = dist.get_rank(), dist.get_world_size()
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    # rendezvous keys private to this restart generation (a restarted worker must not read its predecessor's)
+    dist.init_process_group("gloo", store=elastic_generation_store(rank, world), rank=rank, world_size=world)
     torch.manual_seed(0)
     model = nn.Sequential(nn.Linear(16, 32), nn.Tanh(), nn.Linear(32, 4))
     opt = torch.optim.SGD(model.parameters(), lr=0.05)
