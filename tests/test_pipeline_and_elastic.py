@@ -249,3 +249,29 @@ def test_resharded_load_re_owns_experts(tmp_path):
     h.shutdown()
     assert torch.equal(fresh.w13, full.w13) and torch.equal(fresh.w2, full.w2)
     assert torch.equal(fresh.router.gate_w, full.router.gate_w)
+
+
+def test_generation_store_is_private_to_the_restart(monkeypatch):
+    """Without a TorchElastic launcher there is nothing to prefix; with one, the keys of two restart generations do
+    not see each other (a restarted worker must not read addresses its dead predecessor's peers published)."""
+    import torch.distributed as dist
+
+    from composed_mixture_of_experts_engine_b200.engine import elastic_generation_store
+    from tests.conftest import find_free_port
+
+    for var in ("TORCHELASTIC_RESTART_COUNT", "MASTER_ADDR", "MASTER_PORT", "TORCHELASTIC_USE_AGENT_STORE"):
+        monkeypatch.delenv(var, raising=False)
+    assert elastic_generation_store(0, 1) is None
+    port = find_free_port()
+    monkeypatch.setenv("MASTER_ADDR", "127.0.0.1")
+    monkeypatch.setenv("MASTER_PORT", str(port))
+    monkeypatch.setenv("TORCHELASTIC_RESTART_COUNT", "0")
+    gen0 = elastic_generation_store(0, 1)  # rank 0 hosts the store when the launcher does not
+    assert isinstance(gen0, dist.PrefixStore)
+    gen0.set("addr", "old")
+    monkeypatch.setenv("TORCHELASTIC_RESTART_COUNT", "1")
+    monkeypatch.setenv("TORCHELASTIC_USE_AGENT_STORE", "True")  # second generation: connect as a client
+    gen1 = elastic_generation_store(0, 1)
+    assert gen1.num_keys() >= 1 and not gen1.check(["addr"])
+    gen1.set("addr", "new")
+    assert gen0.get("addr") == b"old" and gen1.get("addr") == b"new"
