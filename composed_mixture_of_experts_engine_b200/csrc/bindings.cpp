@@ -4,6 +4,8 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <cstdlib>
+
 #include <optional>
 #include <string>
 #include <vector>
@@ -97,6 +99,15 @@ void gemm(const Tensor& A, const Tensor& B, Tensor& D, int64_t mode, int64_t epi
   cmoe::GemmArgs g = gemm_args(A, B, D, mode, epilogue, M, N, K, a_mn, b_mn, groups, b_group_rows, split_n, tile_group,
                                num_m_tiles, max_m_tiles, group_offsets, d_group_stride, accumulate, aux_in, aux_out,
                                ready_flags, ready_stride, ready_count, ready_target, status, timeout_ns);
+  // dense and grouped-K launches with plain results run on the two-SM kernel (CMOE_GEMM_2CTA=0: one-CTA kernel)
+  static const bool two_cta = [] {
+    const char* v = std::getenv("CMOE_GEMM_2CTA");
+    return v == nullptr || (v[0] != '\0' && v[0] != '0');
+  }();
+  if (two_cta && cmoe::gemm_2cta_supported(g)) {
+    check_cuda(cmoe::launch_gemm_2cta(g, cur_stream()), "launch_gemm_2cta");
+    return;
+  }
   check_cuda(cmoe::launch_gemm(g, cur_stream()), "launch_gemm");
 }
 

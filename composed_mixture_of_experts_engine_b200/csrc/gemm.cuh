@@ -104,4 +104,9 @@ struct GemmArgs {
 // encoding tensor maps or launching.
 cudaError_t launch_gemm(const GemmArgs& args, cudaStream_t stream);
 
+// Two-SM variant (clusters of two CTAs, `tcgen05.mma.cta_group::2`, 256 x 256 tiles) for dense GEMMs and grouped-K
+// weight-gradient GEMMs with plain results; `gemm_2cta_supported` says whether a launch description qualifies.
+bool gemm_2cta_supported(const GemmArgs& args);
+cudaError_t launch_gemm_2cta(const GemmArgs& args, cudaStream_t stream);
+
 }  // namespace cmoe

@@ -30,6 +30,7 @@ _SOURCES = [
     "bindings_attention.cpp",
     "bindings_ep.cpp",
     "gemm.cu",
+    "gemm2.cu",
     "router.cu",
     "ops.cu",
     "attention.cu",
