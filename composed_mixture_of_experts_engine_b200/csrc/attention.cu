@@ -1,0 +1,700 @@
+// Causal self-attention (grouped-query) on the 5th-generation tensor cores: forward and backward.
+//
+// Both kernels read q / k / v as tiles of the packed projection [B * S, (nh + 2 nkv) * hd] through one tensor map
+// (box = 64 columns x 128 rows, 128-byte swizzle), multiply with tcgen05.mma into TMEM and run the softmax
+// arithmetic with one thread per row straight out of TMEM (tcgen05.ld).  Probabilities (and their gradients) go
+// back to shared memory as bf16 in the same swizzled layout a TMA load would have produced, so the same bytes
+// serve as a K-major operand (P V, dS K) and as an MN-major operand (P^T dO, dS^T Q).
+//
+// Forward: one CTA per (128 query rows, head, batch).  Warp 0 loads Q once and K / V tiles into a two-stage ring,
+// warp 1 issues S = Q K^T for tile i+1 before P V for tile i (two S accumulators), warps 2-5 keep the running
+// maximum, the running sum and the output row in registers (O = O * alpha + P V, read back tile by tile).
+//
+// Backward: one CTA per (128 key rows, kv head, batch) loops over the query heads of its group and the query
+// tiles at or below the diagonal: S = Q K^T and dP = dO V^T, then P and dS = P (dP - delta) scale in shared
+// memory, then dV += P^T dO, dK += dS^T Q (accumulators stay in TMEM for the whole loop) and dQ = dS K, which the
+// row threads add to the fp32 query gradient with vector reductions.
+//
+// Every wait is bounded; a wait that runs out sets the status word and the kernel runs to its normal end.
+// The reference has no attention operator (pkg/models/moe.py:148-186).
+#include "attention.cuh"
+
+#include <cstdio>
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace cmoe {
+
+namespace {
+
+constexpr int BLK = 128;               // query rows per tile = key rows per tile
+constexpr int BLOCK_BYTES = BLK * 128;  // one [128 rows x 64 bf16] swizzled block
+constexpr int ATTN_THREADS = 192;      // warp 0: TMA, warp 1: MMA, warps 2-5: one thread per row
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// K-major operand block: rows of 64 bf16, eight-row groups 1024 bytes apart; `k16` selects 16 of the 64 columns
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t block_addr, int k16) {
+  return make_smem_desc_sw128(block_addr + static_cast<uint32_t>(k16) * 32u, 16, 1024);
+}
+// MN-major operand: 64-element MN chunks BLOCK_BYTES apart, k-rows of 128 bytes; `k16` selects 16 of the 128 k-rows
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile_addr, int k16) {
+  return make_smem_desc_sw128(tile_addr + static_cast<uint32_t>(k16) * 2048u, BLOCK_BYTES, 1024);
+}
+
+// Writes 32 bf16 (16 packed words) of row `r` at columns [col0, col0 + 32) of a [128 x 128] bf16 matrix held as two
+// swizzled [128 x 64] blocks: 16-byte piece j of a row sits at piece j ^ (r % 8).
+__device__ __forceinline__ void store_swizzled_32(uint8_t* mat, int r, int col0, const uint32_t (&w)[16]) {
+  uint8_t* row = mat + (col0 >> 6) * BLOCK_BYTES + r * 128;
+  const int piece0 = (col0 & 63) >> 3;
+  const int sw = r & 7;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    *reinterpret_cast<uint4*>(row + (((piece0 + j) ^ sw) << 4)) =
+        make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+  }
+}
+
+struct FwdParams {
+  __nv_bfloat16* out;
+  float* lse;
+  int S, nh, nkv;
+  float scale_log2;
+  int* status;
+  unsigned long long timeout_ns;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(ATTN_THREADS, 1)
+attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdParams p) {
+  constexpr int KB = HD / 64;                  // 64-column blocks of the head dimension
+  constexpr int TILE_BYTES = KB * BLOCK_BYTES;  // one Q, K or V tile
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + TILE_BYTES;      // [2]
+  uint8_t* sV = sK + 2 * TILE_BYTES;  // [2]
+  uint8_t* sP = sV + 2 * TILE_BYTES;  // 128 x 128 bf16
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * BLOCK_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;   // [2]
+  uint64_t* kv_empty = bars + 3;  // [2]
+  uint64_t* s_full = bars + 5;    // [2]
+  uint64_t* s_empty = bars + 7;   // [2]
+  uint64_t* p_full = bars + 9;
+  uint64_t* o_full = bars + 10;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;  // long rows first
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int hk = h / (p.nh / p.nkv);
+  const int n_kv = qt + 1;
+  const int row0 = b * p.S;
+  const int q_col = h * HD;
+  const int k_col = (p.nh + hk) * HD;
+  const int v_col = (p.nh + p.nkv + hk) * HD;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_empty[s], 128);
+    }
+    mbar_init(p_full, 128);
+    mbar_init(o_full, 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&tmQKV);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);  // S0 [0,128)  S1 [128,256)  PV [256, 256 + HD)
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  WaitCtx wc;
+  wc.abort_flag = abort_flag;
+  wc.status = p.status;
+  wc.timeout_ns = p.timeout_ns;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, TILE_BYTES);
+#pragma unroll
+      for (int kb = 0; kb < KB; ++kb) tma_load_2d(sQ + kb * BLOCK_BYTES, &tmQKV, q_full, q_col + 64 * kb, row0 + qt * BLK);
+      for (int i = 0; i < n_kv; ++i) {
+        const int st = i & 1;
+        if (!mbar_wait(&kv_empty[st], ((i >> 1) & 1) ^ 1u, wc, ST_TIMEOUT_SMEM_EMPTY)) break;
+        mbar_arrive_expect_tx(&kv_full[st], 2 * TILE_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+          tma_load_2d(sK + st * TILE_BYTES + kb * BLOCK_BYTES, &tmQKV, &kv_full[st], k_col + 64 * kb, row0 + i * BLK);
+          tma_load_2d(sV + st * TILE_BYTES + kb * BLOCK_BYTES, &tmQKV, &kv_full[st], v_col + 64 * kb, row0 + i * BLK);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(BLK, BLK, 0, 0);
+      const uint32_t idesc_pv = make_idesc_bf16(BLK, HD, 0, 1);
+      const uint32_t q_addr = smem_u32(sQ);
+      const uint32_t p_addr = smem_u32(sP);
+      bool ok = mbar_wait(q_full, 0, wc, ST_TIMEOUT_SMEM_FULL);
+      auto issue_s = [&](int i) -> bool {
+        const int st = i & 1;
+        if (!mbar_wait(&kv_full[st], (i >> 1) & 1, wc, ST_TIMEOUT_SMEM_FULL)) return false;
+        if (!mbar_wait(&s_empty[st], ((i >> 1) & 1) ^ 1u, wc, ST_TIMEOUT_TMEM_EMPTY)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sK + st * TILE_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            umma_bf16_ss(tmem_base + st * BLK, desc_kmajor(q_addr + kb * BLOCK_BYTES, k),
+                         desc_kmajor(k_addr + kb * BLOCK_BYTES, k), idesc_s, (kb | k) != 0 ? 1u : 0u);
+          }
+        }
+        umma_commit(&s_full[st]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int i = 0; ok && i < n_kv; ++i) {
+        if (i + 1 < n_kv && !issue_s(i + 1)) break;
+        if (!mbar_wait(p_full, i & 1, wc, ST_TIMEOUT_SMEM_FULL)) break;
+        tc_fence_after();
+        const int st = i & 1;
+        const uint32_t v_addr = smem_u32(sV + st * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          umma_bf16_ss(tmem_base + 2 * BLK, desc_kmajor(p_addr + (k >> 2) * BLOCK_BYTES, k & 3),
+                       desc_mnmajor(v_addr, k), idesc_pv, k != 0 ? 1u : 0u);
+        }
+        umma_commit(&kv_empty[st]);
+        umma_commit(o_full);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;  // row of the tile = TMEM lane
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    float O[HD];
+#pragma unroll
+    for (int j = 0; j < HD; ++j) O[j] = 0.f;
+    float m = -INFINITY, l = 0.f, alpha_saved = 0.f;
+    bool ok = true;
+    auto add_pv = [&]() {
+      uint32_t v[32];
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        tmem_ld_32x32b_x32(tmem_base + lane_base + 2 * BLK + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) O[c * 32 + j] = fmaf(O[c * 32 + j], alpha_saved, __uint_as_float(v[j]));
+      }
+    };
+    for (int i = 0; i < n_kv; ++i) {
+      if (i > 0) {
+        if (!mbar_wait(o_full, (i - 1) & 1, wc, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+        add_pv();
+      }
+      const int st = i & 1;
+      if (!mbar_wait(&s_full[st], (i >> 1) & 1, wc, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t s_tmem = tmem_base + lane_base + st * BLK;
+      const int limit = (i == qt) ? r : BLK;  // columns above `limit` lie in the future of this row
+      uint32_t v[32];
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld_32x32b_x32(s_tmem + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float s = __uint_as_float(v[j]);
+          mx = fmaxf(mx, (c * 32 + j <= limit) ? s : -INFINITY);
+        }
+      }
+      const float m_new = fmaxf(m, mx * p.scale_log2);
+      const float alpha = ex2_approx(m - m_new);
+      float lsum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld_32x32b_x32(s_tmem + c * 32, v);
+        tmem_ld_wait();
+        uint32_t w[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float p0 = ex2_approx(fmaf(__uint_as_float(v[j]), p.scale_log2, -m_new));
+          float p1 = ex2_approx(fmaf(__uint_as_float(v[j + 1]), p.scale_log2, -m_new));
+          if (c * 32 + j > limit) p0 = 0.f;
+          if (c * 32 + j + 1 > limit) p1 = 0.f;
+          lsum += p0 + p1;
+          w[j >> 1] = pack_bf16x2(p0, p1);
+        }
+        store_swizzled_32(sP, r, c * 32, w);
+      }
+      l = fmaf(l, alpha, lsum);
+      alpha_saved = alpha;
+      m = m_new;
+      tc_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(&s_empty[st]);
+      mbar_arrive(p_full);
+    }
+    if (ok && mbar_wait(o_full, (n_kv - 1) & 1, wc, ST_TIMEOUT_TMEM_FULL)) {
+      tc_fence_after();
+      add_pv();
+      const float inv = 1.f / l;
+      const long long grow = static_cast<long long>(row0) + qt * BLK + r;
+      __nv_bfloat16* dst = p.out + (grow * p.nh + h) * HD;
+#pragma unroll
+      for (int j = 0; j < HD; j += 8) {
+        uint4 o;
+        o.x = pack_bf16x2(O[j] * inv, O[j + 1] * inv);
+        o.y = pack_bf16x2(O[j + 2] * inv, O[j + 3] * inv);
+        o.z = pack_bf16x2(O[j + 4] * inv, O[j + 5] * inv);
+        o.w = pack_bf16x2(O[j + 6] * inv, O[j + 7] * inv);
+        *reinterpret_cast<uint4*>(dst + j) = o;
+      }
+      p.lse[(static_cast<long long>(b) * p.nh + h) * p.S + qt * BLK + r] = (m + log2f(l)) * kLn2;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
+// backward
+// ----------------------------------------------------------------------------------------------
+// delta[b, h, s] = sum_d dout[b, s, h, d] * out[b, s, h, d]: one warp per (row, head)
+__global__ void attention_delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
+                                       float* __restrict__ delta, long long rows, int S, int nh, int hd) {
+  const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= rows * nh) return;
+  const long long row = wid / nh;  // b * S + s
+  const int h = static_cast<int>(wid - row * nh);
+  const __nv_bfloat16* o = out + wid * hd;
+  const __nv_bfloat16* g = dout + wid * hd;
+  float acc = 0.f;
+  for (int c = lane * 2; c < hd; c += 64) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + c));
+    const float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(g + c));
+    acc += a.x * d.x + a.y * d.y;
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) {
+    const long long b = row / S;
+    const long long s = row - b * S;
+    delta[(b * nh + h) * S + s] = acc;
+  }
+}
+
+struct BwdParams {
+  const float* lse;
+  const float* delta;
+  float* dq;
+  __nv_bfloat16* dk;
+  __nv_bfloat16* dv;
+  int S, nh, nkv;
+  float scale, scale_log2;
+  int* status;
+  unsigned long long timeout_ns;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(ATTN_THREADS, 1)
+attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
+                     const BwdParams p) {
+  constexpr int KB = HD / 64;
+  constexpr int TILE_BYTES = KB * BLOCK_BYTES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + TILE_BYTES;
+  uint8_t* sQ = sV + TILE_BYTES;
+  uint8_t* sDO = sQ + TILE_BYTES;
+  uint8_t* sP = sDO + TILE_BYTES;       // 128 x 128 bf16, rows = queries, columns = keys
+  uint8_t* sDS = sP + 2 * BLOCK_BYTES;  // same shape
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + 2 * BLOCK_BYTES);
+  uint64_t* kv_full = bars;
+  uint64_t* qdo_full = bars + 1;
+  uint64_t* qdo_empty = bars + 2;
+  uint64_t* sdp_full = bars + 3;
+  uint64_t* sdp_empty = bars + 4;
+  uint64_t* pds_full = bars + 5;
+  uint64_t* dq_full = bars + 6;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int kt = blockIdx.x;  // key tile; tile 0 has the most query tiles below it and starts first
+  const int hk = blockIdx.y;
+  const int b = blockIdx.z;
+  const int T = p.S / BLK;
+  const int G = p.nh / p.nkv;
+  const int q_tiles = T - kt;
+  const int n_steps = G * q_tiles;
+  const int row0 = b * p.S;
+  const int k_col = (p.nh + hk) * HD;
+  const int v_col = (p.nh + p.nkv + hk) * HD;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(kv_full, 1);
+    mbar_init(qdo_full, 1);
+    mbar_init(qdo_empty, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(sdp_empty, 128);
+    mbar_init(pds_full, 128);
+    mbar_init(dq_full, 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&tmQKV);
+    tma_prefetch_desc(&tmDO);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);  // S, then dQ [0,128)   dP [128,256)   dV [256,384)   dK [384,512)
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  WaitCtx wc;
+  wc.abort_flag = abort_flag;
+  wc.status = p.status;
+  wc.timeout_ns = p.timeout_ns;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
+#pragma unroll
+      for (int kb = 0; kb < KB; ++kb) {
+        tma_load_2d(sK + kb * BLOCK_BYTES, &tmQKV, kv_full, k_col + 64 * kb, row0 + kt * BLK);
+        tma_load_2d(sV + kb * BLOCK_BYTES, &tmQKV, kv_full, v_col + 64 * kb, row0 + kt * BLK);
+      }
+      for (int s = 0; s < n_steps; ++s) {
+        const int hq = hk * G + s / q_tiles;
+        const int qt = kt + s % q_tiles;
+        if (!mbar_wait(qdo_empty, (s & 1) ^ 1u, wc, ST_TIMEOUT_SMEM_EMPTY)) break;
+        mbar_arrive_expect_tx(qdo_full, 2 * TILE_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+          tma_load_2d(sQ + kb * BLOCK_BYTES, &tmQKV, qdo_full, hq * HD + 64 * kb, row0 + qt * BLK);
+          tma_load_2d(sDO + kb * BLOCK_BYTES, &tmDO, qdo_full, hq * HD + 64 * kb, row0 + qt * BLK);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(BLK, BLK, 0, 0);   // S, dP: both operands K-major
+      const uint32_t idesc_t = make_idesc_bf16(BLK, HD, 1, 1);    // dV, dK: both operands MN-major
+      const uint32_t idesc_q = make_idesc_bf16(BLK, HD, 0, 1);    // dQ: dS K-major, K tile MN-major
+      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), do_addr = smem_u32(sDO);
+      const uint32_t p_addr = smem_u32(sP), ds_addr = smem_u32(sDS);
+      bool ok = mbar_wait(kv_full, 0, wc, ST_TIMEOUT_SMEM_FULL);
+      for (int s = 0; ok && s < n_steps; ++s) {
+        if (!mbar_wait(qdo_full, s & 1, wc, ST_TIMEOUT_SMEM_FULL)) break;
+        if (!mbar_wait(sdp_empty, (s & 1) ^ 1u, wc, ST_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            umma_bf16_ss(tmem_base, desc_kmajor(q_addr + kb * BLOCK_BYTES, k), desc_kmajor(k_addr + kb * BLOCK_BYTES, k),
+                         idesc_s, (kb | k) != 0 ? 1u : 0u);
+          }
+        }
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            umma_bf16_ss(tmem_base + BLK, desc_kmajor(do_addr + kb * BLOCK_BYTES, k),
+                         desc_kmajor(v_addr + kb * BLOCK_BYTES, k), idesc_s, (kb | k) != 0 ? 1u : 0u);
+          }
+        }
+        umma_commit(sdp_full);
+        if (!mbar_wait(pds_full, s & 1, wc, ST_TIMEOUT_SMEM_FULL)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // dV[key, d] += sum over queries P[query, key] dO[query, d]
+          umma_bf16_ss(tmem_base + 2 * BLK, desc_mnmajor(p_addr, k), desc_mnmajor(do_addr, k), idesc_t,
+                       (s | k) != 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // dK[key, d] += sum over queries dS[query, key] Q[query, d]
+          umma_bf16_ss(tmem_base + 3 * BLK, desc_mnmajor(ds_addr, k), desc_mnmajor(q_addr, k), idesc_t,
+                       (s | k) != 0 ? 1u : 0u);
+        umma_commit(qdo_empty);  // Q and dO may be replaced while dQ is computed
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // dQ[query, d] = sum over keys dS[query, key] K[key, d]
+          umma_bf16_ss(tmem_base, desc_kmajor(ds_addr + (k >> 2) * BLOCK_BYTES, k & 3), desc_mnmajor(k_addr, k),
+                       idesc_q, k != 0 ? 1u : 0u);
+        umma_commit(dq_full);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    bool ok = true;
+    for (int s = 0; s < n_steps; ++s) {
+      const int hq = hk * G + s / q_tiles;
+      const int qt = kt + s % q_tiles;
+      const long long stat = (static_cast<long long>(b) * p.nh + hq) * p.S + qt * BLK + r;
+      const float lse2 = p.lse[stat] * kLog2e;
+      const float dlt = p.delta[stat];
+      if (!mbar_wait(sdp_full, s & 1, wc, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int limit = (qt == kt) ? r : BLK;  // keys above `limit` lie in the future of this query
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32], dp[32];
+        tmem_ld_32x32b_x32(tmem_base + lane_base + c * 32, sv);
+        tmem_ld_32x32b_x32(tmem_base + lane_base + BLK + c * 32, dp);
+        tmem_ld_wait();
+        uint32_t pw[16], dw[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float p0 = ex2_approx(fmaf(__uint_as_float(sv[j]), p.scale_log2, -lse2));
+          float p1 = ex2_approx(fmaf(__uint_as_float(sv[j + 1]), p.scale_log2, -lse2));
+          if (c * 32 + j > limit) p0 = 0.f;
+          if (c * 32 + j + 1 > limit) p1 = 0.f;
+          const float d0 = p0 * (__uint_as_float(dp[j]) - dlt) * p.scale;
+          const float d1 = p1 * (__uint_as_float(dp[j + 1]) - dlt) * p.scale;
+          pw[j >> 1] = pack_bf16x2(p0, p1);
+          dw[j >> 1] = pack_bf16x2(d0, d1);
+        }
+        store_swizzled_32(sP, r, c * 32, pw);
+        store_swizzled_32(sDS, r, c * 32, dw);
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(pds_full);
+      if (!mbar_wait(dq_full, s & 1, wc, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      float* dq_row = p.dq + ((static_cast<long long>(row0) + qt * BLK + r) * p.nh + hq) * HD;
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_base + lane_base + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + c * 32 + j),
+                       "f"(__uint_as_float(v[j])), "f"(__uint_as_float(v[j + 1])), "f"(__uint_as_float(v[j + 2])),
+                       "f"(__uint_as_float(v[j + 3]))
+                       : "memory");
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(sdp_empty);
+    }
+    if (ok && n_steps > 0) {
+      // the last dq_full covered every MMA of the loop: dV and dK are complete
+      const long long grow = static_cast<long long>(row0) + kt * BLK + r;
+      __nv_bfloat16* dv_row = p.dv + (grow * p.nkv + hk) * HD;
+      __nv_bfloat16* dk_row = p.dk + (grow * p.nkv + hk) * HD;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        __nv_bfloat16* dst = which == 0 ? dv_row : dk_row;
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tmem_base + lane_base + (2 + which) * BLK + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+            o.y = pack_bf16x2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+            o.z = pack_bf16x2(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+            o.w = pack_bf16x2(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+            *reinterpret_cast<uint4*>(dst + c * 32 + j) = o;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
+// host side
+// ----------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn attn_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  });
+  return fn;
+}
+
+// bf16 row-major [rows, cols], box = 64 columns x 128 rows, 128-byte swizzle
+cudaError_t make_tile_map(CUtensorMap* out, const void* ptr, long long rows, long long cols) {
+  EncodeTiledFn enc = attn_encode_fn();
+  if (enc == nullptr) return cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0 || (cols * 2) % 16 != 0 || rows <= 0 || cols <= 0)
+    return cudaErrorInvalidValue;
+  cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t gstride[1] = {static_cast<cuuint64_t>(cols) * 2};
+  cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(BLK)};
+  cuuint32_t estride[2] = {1u, 1u};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estride,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    std::fprintf(stderr, "cmoe: cuTensorMapEncodeTiled (attention) failed (%d) rows=%lld cols=%lld\n",
+                 static_cast<int>(r), rows, cols);
+    return cudaErrorInvalidValue;
+  }
+  return cudaSuccess;
+}
+
+// One CTA per SM in every configuration: each CTA allocates all 512 TMEM columns, so a second resident CTA would
+// only wait for the first one's columns.
+constexpr int kMinSmem = 120 * 1024;
+
+template <int HD>
+constexpr int fwd_smem_bytes() {
+  return (5 * (HD / 64) + 2) * BLOCK_BYTES + 1024 + 256;
+}
+template <int HD>
+constexpr int bwd_smem_bytes() {
+  return (4 * (HD / 64) + 4) * BLOCK_BYTES + 1024 + 256;
+}
+
+template <int HD>
+cudaError_t launch_fwd_t(const AttnFwdArgs& a, const CUtensorMap& tm, const FwdParams& p, cudaStream_t stream) {
+  constexpr int smem = fwd_smem_bytes<HD>() > kMinSmem ? fwd_smem_bytes<HD>() : kMinSmem;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(attention_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+  dim3 grid(a.S / BLK, a.nh, a.B);
+  attention_fwd_kernel<HD><<<grid, ATTN_THREADS, smem, stream>>>(tm, p);
+  return cudaGetLastError();
+}
+
+template <int HD>
+cudaError_t launch_bwd_t(const AttnBwdArgs& a, const CUtensorMap& tq, const CUtensorMap& td, const BwdParams& p,
+                         cudaStream_t stream) {
+  constexpr int smem = bwd_smem_bytes<HD>() > kMinSmem ? bwd_smem_bytes<HD>() : kMinSmem;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(attention_bwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+  dim3 grid(a.S / BLK, a.nkv, a.B);
+  attention_bwd_kernel<HD><<<grid, ATTN_THREADS, smem, stream>>>(tq, td, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool attention_shape_supported(int S, int nh, int nkv, int hd) {
+  return S > 0 && S % BLK == 0 && (hd == 64 || hd == 128) && nkv > 0 && nh % nkv == 0;
+}
+
+cudaError_t launch_attention_fwd(const AttnFwdArgs& a, cudaStream_t stream) {
+  if (!attention_shape_supported(a.S, a.nh, a.nkv, a.hd) || a.B <= 0 || a.B > 65535 || a.nh > 65535 ||
+      a.qkv == nullptr || a.out == nullptr || a.lse == nullptr)
+    return cudaErrorInvalidValue;
+  if (static_cast<long long>(a.B) * a.S > 0x7fffffffLL) return cudaErrorInvalidValue;
+  CUtensorMap tm;
+  cudaError_t e = make_tile_map(&tm, a.qkv, static_cast<long long>(a.B) * a.S,
+                                static_cast<long long>(a.nh + 2 * a.nkv) * a.hd);
+  if (e != cudaSuccess) return e;
+  FwdParams p;
+  p.out = reinterpret_cast<__nv_bfloat16*>(a.out);
+  p.lse = a.lse;
+  p.S = a.S;
+  p.nh = a.nh;
+  p.nkv = a.nkv;
+  const float scale = a.scale > 0.f ? a.scale : 1.f / sqrtf(static_cast<float>(a.hd));
+  p.scale_log2 = scale * kLog2e;
+  p.status = a.status;
+  p.timeout_ns = a.timeout_ns ? a.timeout_ns : kDefaultTimeoutNs;
+  return a.hd == 128 ? launch_fwd_t<128>(a, tm, p, stream) : launch_fwd_t<64>(a, tm, p, stream);
+}
+
+cudaError_t launch_attention_bwd(const AttnBwdArgs& a, cudaStream_t stream) {
+  if (!attention_shape_supported(a.S, a.nh, a.nkv, a.hd) || a.B <= 0 || a.B > 65535 || a.nkv > 65535 ||
+      a.qkv == nullptr || a.out == nullptr || a.dout == nullptr || a.lse == nullptr || a.delta == nullptr ||
+      a.dq == nullptr || a.dk == nullptr || a.dv == nullptr)
+    return cudaErrorInvalidValue;
+  if (static_cast<long long>(a.B) * a.S > 0x7fffffffLL) return cudaErrorInvalidValue;
+  const long long rows = static_cast<long long>(a.B) * a.S;
+  CUtensorMap tq, td;
+  cudaError_t e = make_tile_map(&tq, a.qkv, rows, static_cast<long long>(a.nh + 2 * a.nkv) * a.hd);
+  if (e != cudaSuccess) return e;
+  e = make_tile_map(&td, a.dout, rows, static_cast<long long>(a.nh) * a.hd);
+  if (e != cudaSuccess) return e;
+  {
+    const long long warps = rows * a.nh;
+    const int threads = 256;
+    const long long blocks = (warps * 32 + threads - 1) / threads;
+    attention_delta_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(a.out), reinterpret_cast<const __nv_bfloat16*>(a.dout), a.delta, rows,
+        a.S, a.nh, a.hd);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  BwdParams p;
+  p.lse = a.lse;
+  p.delta = a.delta;
+  p.dq = a.dq;
+  p.dk = reinterpret_cast<__nv_bfloat16*>(a.dk);
+  p.dv = reinterpret_cast<__nv_bfloat16*>(a.dv);
+  p.S = a.S;
+  p.nh = a.nh;
+  p.nkv = a.nkv;
+  p.scale = a.scale > 0.f ? a.scale : 1.f / sqrtf(static_cast<float>(a.hd));
+  p.scale_log2 = p.scale * kLog2e;
+  p.status = a.status;
+  p.timeout_ns = a.timeout_ns ? a.timeout_ns : kDefaultTimeoutNs;
+  return a.hd == 128 ? launch_bwd_t<128>(a, tq, td, p, stream) : launch_bwd_t<64>(a, tq, td, p, stream);
+}
+
+}  // namespace cmoe

@@ -16,6 +16,7 @@ import torch
 import torch.nn.functional as F
 
 from . import _ext, kernels
+from . import attention_sm100 as _attn_sm100
 from .kernels import EPI_STORE, EPI_SWIGLU_BWD, EPI_SWIGLU_FWD, GEMM_GROUPED_K, GEMM_GROUPED_M, MoEPlan
 
 
@@ -122,6 +123,16 @@ class _RopeAttentionFn(torch.autograd.Function):
         B, S, heads, hd = qkv.shape
         _ext.ext().rope(qkv.view(B * S, heads, hd)[:, : nh + nkv], cos, sin, S, False)
         t = qkv.detach()
+        ctx.dims = (B, S, heads, hd, nh, nkv)
+        if _attn_sm100.enabled() and _attn_sm100.packed_supported(t, nh, nkv):
+            # hand-written tcgen05 kernels on the packed buffer; the backward needs the rotated projection,
+            # the output and the row log-sum-exps
+            out, lse = _attn_sm100.forward_packed(t, nh, nkv)
+            ctx.inner = (t, out, lse)
+            ctx.sm100 = True
+            ctx.save_for_backward(cos, sin)
+            return out
+        ctx.sm100 = False
         with torch.enable_grad():
             q = t[:, :, :nh].permute(0, 2, 1, 3).requires_grad_()
             k = t[:, :, nh: nh + nkv].permute(0, 2, 1, 3).requires_grad_()
@@ -140,10 +151,17 @@ class _RopeAttentionFn(torch.autograd.Function):
     def backward(ctx, go):
         cos, sin = ctx.saved_tensors
         B, S, heads, hd, nh, nkv = ctx.dims
+        dqkv = torch.empty(B, S, heads, hd, device=go.device, dtype=go.dtype)
+        if ctx.sm100:
+            t, out, lse = ctx.inner
+            ctx.inner = None
+            dq32, dk, dv = _attn_sm100.backward_packed(t, nh, nkv, out, go, lse)
+            _ext.ext().qkv_grad_pack(dq32.to(torch.bfloat16).permute(0, 2, 1, 3), dk.permute(0, 2, 1, 3),
+                                     dv.permute(0, 2, 1, 3), dqkv, cos, sin)
+            return dqkv, None, None, None, None
         q, k, v, out = ctx.inner
         ctx.inner = None
         dq, dk, dv = torch.autograd.grad(out, (q, k, v), go.permute(0, 2, 1, 3))
-        dqkv = torch.empty(B, S, heads, hd, device=go.device, dtype=go.dtype)
         if all(t.stride(3) == 1 and all(st % 8 == 0 for st in t.stride()[:3]) for t in (dq, dk, dv)):
             # one pass: pack the three gradients and undo the rotation of the q and k heads on the way
             _ext.ext().qkv_grad_pack(dq, dk, dv, dqkv, cos, sin)
