@@ -6,14 +6,17 @@
 // back to shared memory as bf16 in the same swizzled layout a TMA load would have produced, so the same bytes
 // serve as a K-major operand (P V, dS K) and as an MN-major operand (P^T dO, dS^T Q).
 //
-// Forward: one CTA per (128 query rows, head, batch).  Warp 0 loads Q once and K / V tiles into a two-stage ring,
-// warp 1 issues S = Q K^T for tile i+1 before P V for tile i (two S accumulators), warps 2-5 keep the running
-// maximum, the running sum and the output row in registers (O = O * alpha + P V, read back tile by tile).
+// Forward: one CTA per (128 query rows, head, batch).  Warp 0 loads Q once and K / V tiles into two-stage rings
+// (a K buffer is released as soon as its S has been computed, a V buffer after its P V), warp 1 issues S = Q K^T
+// for tile i+1 before P V for tile i (two S accumulators, two P buffers, two partial-product accumulators), warps
+// 2-9 run the softmax with two threads per query row: each keeps the running maximum (exchanged once per tile),
+// its part of the running sum and half of the output row in registers (O = O * alpha + P V, read back tile by tile).
 //
 // Backward: one CTA per (128 key rows, kv head, batch) loops over the query heads of its group and the query
 // tiles at or below the diagonal: S = Q K^T and dP = dO V^T, then P and dS = P (dP - delta) scale in shared
-// memory, then dV += P^T dO, dK += dS^T Q (accumulators stay in TMEM for the whole loop) and dQ = dS K, which the
-// row threads add to the fp32 query gradient with vector reductions.
+// memory, then dK += dS^T Q, dV += P^T dO (accumulators stay in TMEM for the whole loop) and dQ = dS K, which the
+// row threads move into the P / dS area, from where TMA reduce-add copies add it to the fp32 query gradient.
+// dO is double-buffered and S of the next step is issued while dQ of this one is on its way out.
 //
 // Every wait is bounded; a wait that runs out sets the status word and the kernel runs to its normal end.
 // The reference has no attention operator (pkg/models/moe.py:148-186).
@@ -31,7 +34,8 @@ namespace {
 
 constexpr int BLK = 128;               // query rows per tile = key rows per tile
 constexpr int BLOCK_BYTES = BLK * 128;  // one [128 rows x 64 bf16] swizzled block
-constexpr int ATTN_THREADS = 192;      // warp 0: TMA, warp 1: MMA, warps 2-5: one thread per row
+constexpr int ROW_THREADS = 256;       // warps 2-9: two threads per row of a tile
+constexpr int ATTN_THREADS = 64 + ROW_THREADS;  // warp 0: TMA, warp 1: MMA
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -72,26 +76,51 @@ struct FwdParams {
   unsigned long long timeout_ns;
 };
 
+// Shared-memory plan of the forward kernel (bytes, after the 1024-byte alignment of the base):
+//   Q tile | K tiles [2] | V tiles [2] | P [2] (128 x 128 bf16 each) | row-maximum exchange [2][2][128] fp32 | barriers
+template <int HD>
+struct FwdSmem {
+  static constexpr int TILE_BYTES = (HD / 64) * BLOCK_BYTES;
+  static constexpr int Q = 0;
+  static constexpr int K = Q + TILE_BYTES;
+  static constexpr int V = K + 2 * TILE_BYTES;
+  static constexpr int P = V + 2 * TILE_BYTES;
+  static constexpr int XCHG = P + 4 * BLOCK_BYTES;
+  static constexpr int BARS = XCHG + 2 * 2 * BLK * 4;
+  static constexpr int END = BARS + 192;
+};
+
 template <int HD>
 __global__ void __launch_bounds__(ATTN_THREADS, 1)
-attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdParams p) {
+attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdParams p, const int smem_bytes) {
+  using L = FwdSmem<HD>;
   constexpr int KB = HD / 64;                  // 64-column blocks of the head dimension
-  constexpr int TILE_BYTES = KB * BLOCK_BYTES;  // one Q, K or V tile
+  constexpr int TILE_BYTES = L::TILE_BYTES;    // one Q, K or V tile
+  constexpr int OC = HD / 2;                   // output columns kept by one row thread
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;
-  uint8_t* sK = sQ + TILE_BYTES;      // [2]
-  uint8_t* sV = sK + 2 * TILE_BYTES;  // [2]
-  uint8_t* sP = sV + 2 * TILE_BYTES;  // 128 x 128 bf16
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * BLOCK_BYTES);
+  if (smem + L::END > smem_raw + smem_bytes) {
+    // the launch did not provide room for the aligned plan: report and leave before anything is set up
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, ST_BAD_ARGUMENT);
+    return;
+  }
+  uint8_t* sQ = smem + L::Q;
+  uint8_t* sK = smem + L::K;  // [2]
+  uint8_t* sV = smem + L::V;  // [2]
+  uint8_t* sP = smem + L::P;  // [2]
+  float* xchg = reinterpret_cast<float*>(smem + L::XCHG);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BARS);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;   // [2]
-  uint64_t* kv_empty = bars + 3;  // [2]
-  uint64_t* s_full = bars + 5;    // [2]
-  uint64_t* s_empty = bars + 7;   // [2]
-  uint64_t* p_full = bars + 9;
-  uint64_t* o_full = bars + 10;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* k_full = bars + 1;    // [2]
+  uint64_t* k_empty = bars + 3;   // [2] released as soon as S of the tile has been computed
+  uint64_t* v_full = bars + 5;    // [2]
+  uint64_t* v_empty = bars + 7;   // [2] released after P V of the tile
+  uint64_t* s_full = bars + 9;    // [2]
+  uint64_t* s_empty = bars + 11;  // [2]
+  uint64_t* p_full = bars + 13;   // [2]
+  uint64_t* o_full = bars + 15;   // [2]
+  uint64_t* x_full = bars + 17;   // [2] both halves of a row have published their maximum (or, last, their sum)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -110,18 +139,21 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdParams 
     *abort_flag = 0;
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 128);
+      mbar_init(&s_empty[s], ROW_THREADS);
+      mbar_init(&p_full[s], ROW_THREADS);
+      mbar_init(&o_full[s], 1);
+      mbar_init(&x_full[s], ROW_THREADS);
     }
-    mbar_init(p_full, 128);
-    mbar_init(o_full, 1);
     fence_mbar_init();
     tma_prefetch_desc(&tmQKV);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);  // S0 [0,128)  S1 [128,256)  PV [256, 256 + HD)
+    tmem_alloc(tmem_slot, 512);  // S [2] at columns 0 and 128, P V [2] at columns 256 and 384
     tmem_relinquish();
   }
   tc_fence_before();
@@ -139,14 +171,26 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdParams 
       mbar_arrive_expect_tx(q_full, TILE_BYTES);
 #pragma unroll
       for (int kb = 0; kb < KB; ++kb) tma_load_2d(sQ + kb * BLOCK_BYTES, &tmQKV, q_full, q_col + 64 * kb, row0 + qt * BLK);
-      for (int i = 0; i < n_kv; ++i) {
-        const int st = i & 1;
-        if (!mbar_wait(&kv_empty[st], ((i >> 1) & 1) ^ 1u, wc, ST_TIMEOUT_SMEM_EMPTY)) break;
-        mbar_arrive_expect_tx(&kv_full[st], 2 * TILE_BYTES);
+      // K tiles run one tile ahead of V tiles: a K buffer is free as soon as its S has been computed (S is
+      // issued a whole tile early), a V buffer only after its P V, and the wait for the latter must not hold
+      // back the next K
+      for (int i = 0; i <= n_kv; ++i) {
+        if (i < n_kv) {
+          const int st = i & 1;
+          if (!mbar_wait(&k_empty[st], ((i >> 1) & 1) ^ 1u, wc, ST_TIMEOUT_SMEM_EMPTY)) break;
+          mbar_arrive_expect_tx(&k_full[st], TILE_BYTES);
 #pragma unroll
-        for (int kb = 0; kb < KB; ++kb) {
-          tma_load_2d(sK + st * TILE_BYTES + kb * BLOCK_BYTES, &tmQKV, &kv_full[st], k_col + 64 * kb, row0 + i * BLK);
-          tma_load_2d(sV + st * TILE_BYTES + kb * BLOCK_BYTES, &tmQKV, &kv_full[st], v_col + 64 * kb, row0 + i * BLK);
+          for (int kb = 0; kb < KB; ++kb)
+            tma_load_2d(sK + st * TILE_BYTES + kb * BLOCK_BYTES, &tmQKV, &k_full[st], k_col + 64 * kb, row0 + i * BLK);
+        }
+        if (i >= 1) {
+          const int j = i - 1;
+          const int st = j & 1;
+          if (!mbar_wait(&v_empty[st], ((j >> 1) & 1) ^ 1u, wc, ST_TIMEOUT_SMEM_EMPTY)) break;
+          mbar_arrive_expect_tx(&v_full[st], TILE_BYTES);
+#pragma unroll
+          for (int kb = 0; kb < KB; ++kb)
+            tma_load_2d(sV + st * TILE_BYTES + kb * BLOCK_BYTES, &tmQKV, &v_full[st], v_col + 64 * kb, row0 + j * BLK);
         }
       }
     }
@@ -155,11 +199,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdParams 
       const uint32_t idesc_s = make_idesc_bf16(BLK, BLK, 0, 0);
       const uint32_t idesc_pv = make_idesc_bf16(BLK, HD, 0, 1);
       const uint32_t q_addr = smem_u32(sQ);
-      const uint32_t p_addr = smem_u32(sP);
       bool ok = mbar_wait(q_full, 0, wc, ST_TIMEOUT_SMEM_FULL);
       auto issue_s = [&](int i) -> bool {
         const int st = i & 1;
-        if (!mbar_wait(&kv_full[st], (i >> 1) & 1, wc, ST_TIMEOUT_SMEM_FULL)) return false;
+        if (!mbar_wait(&k_full[st], (i >> 1) & 1, wc, ST_TIMEOUT_SMEM_FULL)) return false;
         if (!mbar_wait(&s_empty[st], ((i >> 1) & 1) ^ 1u, wc, ST_TIMEOUT_TMEM_EMPTY)) return false;
         tc_fence_after();
         const uint32_t k_addr = smem_u32(sK + st * TILE_BYTES);
@@ -171,110 +214,134 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdParams 
                          desc_kmajor(k_addr + kb * BLOCK_BYTES, k), idesc_s, (kb | k) != 0 ? 1u : 0u);
           }
         }
+        umma_commit(&k_empty[st]);
         umma_commit(&s_full[st]);
         return true;
       };
       if (ok) ok = issue_s(0);
       for (int i = 0; ok && i < n_kv; ++i) {
+        // S of the next tile goes to the tensor pipe before P V of this one, so that it runs while the row
+        // threads are still busy with this tile's softmax
         if (i + 1 < n_kv && !issue_s(i + 1)) break;
-        if (!mbar_wait(p_full, i & 1, wc, ST_TIMEOUT_SMEM_FULL)) break;
-        tc_fence_after();
         const int st = i & 1;
+        if (!mbar_wait(&v_full[st], (i >> 1) & 1, wc, ST_TIMEOUT_SMEM_FULL)) break;
+        if (!mbar_wait(&p_full[st], (i >> 1) & 1, wc, ST_TIMEOUT_SMEM_FULL)) break;
+        tc_fence_after();
         const uint32_t v_addr = smem_u32(sV + st * TILE_BYTES);
+        const uint32_t p_addr = smem_u32(sP + st * 2 * BLOCK_BYTES);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          umma_bf16_ss(tmem_base + 2 * BLK, desc_kmajor(p_addr + (k >> 2) * BLOCK_BYTES, k & 3),
+          umma_bf16_ss(tmem_base + (2 + st) * BLK, desc_kmajor(p_addr + (k >> 2) * BLOCK_BYTES, k & 3),
                        desc_mnmajor(v_addr, k), idesc_pv, k != 0 ? 1u : 0u);
         }
-        umma_commit(&kv_empty[st]);
-        umma_commit(o_full);
+        umma_commit(&v_empty[st]);
+        umma_commit(&o_full[st]);
       }
     }
   } else {
+    // Two threads per query row: `half` 0 owns key columns 0-63 of every tile and output columns [0, HD/2),
+    // `half` 1 the rest.  Both see the same running maximum (exchanged through shared memory once per tile) and
+    // keep partial sums that meet at the end.
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quad * 32 + lane;  // row of the tile = TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
-    float O[HD];
+    float O[OC];
 #pragma unroll
-    for (int j = 0; j < HD; ++j) O[j] = 0.f;
+    for (int j = 0; j < OC; ++j) O[j] = 0.f;
     float m = -INFINITY, l = 0.f, alpha_saved = 0.f;
     bool ok = true;
-    auto add_pv = [&]() {
+    auto add_pv = [&](int st) {
       uint32_t v[32];
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
-        tmem_ld_32x32b_x32(tmem_base + lane_base + 2 * BLK + c * 32, v);
+      for (int c = 0; c < OC / 32; ++c) {
+        tmem_ld_32x32b_x32(tmem_base + lane_base + (2 + st) * BLK + half * OC + c * 32, v);
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j) O[c * 32 + j] = fmaf(O[c * 32 + j], alpha_saved, __uint_as_float(v[j]));
       }
     };
     for (int i = 0; i < n_kv; ++i) {
-      if (i > 0) {
-        if (!mbar_wait(o_full, (i - 1) & 1, wc, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-        tc_fence_after();
-        add_pv();
-      }
       const int st = i & 1;
-      if (!mbar_wait(&s_full[st], (i >> 1) & 1, wc, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      const uint32_t par = (i >> 1) & 1;
+      if (!mbar_wait(&s_full[st], par, wc, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t s_tmem = tmem_base + lane_base + st * BLK;
+      const uint32_t s_tmem = tmem_base + lane_base + st * BLK + half * 64;
       const int limit = (i == qt) ? r : BLK;  // columns above `limit` lie in the future of this row
-      uint32_t v[32];
+      uint32_t sv[2][32];
+      tmem_ld_32x32b_x32(s_tmem, sv[0]);
+      tmem_ld_32x32b_x32(s_tmem + 32, sv[1]);
+      tmem_ld_wait();
       float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld_32x32b_x32(s_tmem + c * 32, v);
-        tmem_ld_wait();
+      for (int c = 0; c < 2; ++c) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          const float s = __uint_as_float(v[j]);
-          mx = fmaxf(mx, (c * 32 + j <= limit) ? s : -INFINITY);
+          const float s = __uint_as_float(sv[c][j]);
+          mx = fmaxf(mx, (half * 64 + c * 32 + j <= limit) ? s : -INFINITY);
         }
       }
+      xchg[(st * 2 + half) * BLK + r] = mx;
+      mbar_arrive(&x_full[st]);
+      if (!mbar_wait(&x_full[st], par, wc, ST_TIMEOUT_PEER_FLAG)) { ok = false; break; }
+      mx = fmaxf(mx, xchg[(st * 2 + (half ^ 1)) * BLK + r]);
       const float m_new = fmaxf(m, mx * p.scale_log2);
       const float alpha = ex2_approx(m - m_new);
       float lsum = 0.f;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld_32x32b_x32(s_tmem + c * 32, v);
-        tmem_ld_wait();
+      for (int c = 0; c < 2; ++c) {
         uint32_t w[16];
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
-          float p0 = ex2_approx(fmaf(__uint_as_float(v[j]), p.scale_log2, -m_new));
-          float p1 = ex2_approx(fmaf(__uint_as_float(v[j + 1]), p.scale_log2, -m_new));
-          if (c * 32 + j > limit) p0 = 0.f;
-          if (c * 32 + j + 1 > limit) p1 = 0.f;
+          float p0 = ex2_approx(fmaf(__uint_as_float(sv[c][j]), p.scale_log2, -m_new));
+          float p1 = ex2_approx(fmaf(__uint_as_float(sv[c][j + 1]), p.scale_log2, -m_new));
+          if (half * 64 + c * 32 + j > limit) p0 = 0.f;
+          if (half * 64 + c * 32 + j + 1 > limit) p1 = 0.f;
           lsum += p0 + p1;
           w[j >> 1] = pack_bf16x2(p0, p1);
         }
-        store_swizzled_32(sP, r, c * 32, w);
+        store_swizzled_32(sP + st * 2 * BLOCK_BYTES, r, half * 64 + c * 32, w);
       }
       l = fmaf(l, alpha, lsum);
-      alpha_saved = alpha;
       m = m_new;
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(&s_empty[st]);
-      mbar_arrive(p_full);
-    }
-    if (ok && mbar_wait(o_full, (n_kv - 1) & 1, wc, ST_TIMEOUT_TMEM_FULL)) {
-      tc_fence_after();
-      add_pv();
-      const float inv = 1.f / l;
-      const long long grow = static_cast<long long>(row0) + qt * BLK + r;
-      __nv_bfloat16* dst = p.out + (grow * p.nh + h) * HD;
-#pragma unroll
-      for (int j = 0; j < HD; j += 8) {
-        uint4 o;
-        o.x = pack_bf16x2(O[j] * inv, O[j + 1] * inv);
-        o.y = pack_bf16x2(O[j + 2] * inv, O[j + 3] * inv);
-        o.z = pack_bf16x2(O[j + 4] * inv, O[j + 5] * inv);
-        o.w = pack_bf16x2(O[j + 6] * inv, O[j + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + j) = o;
+      mbar_arrive(&p_full[st]);
+      if (i > 0) {
+        // the partial product of the previous tile was formed against the previous maximum
+        if (!mbar_wait(&o_full[st ^ 1], ((i - 1) >> 1) & 1, wc, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+        add_pv(st ^ 1);
       }
-      p.lse[(static_cast<long long>(b) * p.nh + h) * p.S + qt * BLK + r] = (m + log2f(l)) * kLn2;
+      alpha_saved = alpha;
+    }
+    const int last = (n_kv - 1) & 1;
+    if (ok && mbar_wait(&o_full[last], ((n_kv - 1) >> 1) & 1, wc, ST_TIMEOUT_TMEM_FULL)) {
+      tc_fence_after();
+      add_pv(last);
+      // the two halves of a row add their sums through the exchange buffer the last tile did not use
+      const int xb = last ^ 1;
+      xchg[(xb * 2 + half) * BLK + r] = l;
+      mbar_arrive(&x_full[xb]);
+      // completions of x_full[xb] so far: one per tile that used it
+      const int used = (xb == 0) ? (n_kv + 1) / 2 : n_kv / 2;
+      if (mbar_wait(&x_full[xb], used & 1, wc, ST_TIMEOUT_PEER_FLAG)) {
+        l += xchg[(xb * 2 + (half ^ 1)) * BLK + r];
+        const float inv = 1.f / l;
+        const long long grow = static_cast<long long>(row0) + qt * BLK + r;
+        __nv_bfloat16* dst = p.out + (grow * p.nh + h) * HD + half * OC;
+#pragma unroll
+        for (int j = 0; j < OC; j += 8) {
+          uint4 o;
+          o.x = pack_bf16x2(O[j] * inv, O[j + 1] * inv);
+          o.y = pack_bf16x2(O[j + 2] * inv, O[j + 3] * inv);
+          o.z = pack_bf16x2(O[j + 4] * inv, O[j + 5] * inv);
+          o.w = pack_bf16x2(O[j + 6] * inv, O[j + 7] * inv);
+          *reinterpret_cast<uint4*>(dst + j) = o;
+        }
+        if (half == 0) p.lse[(static_cast<long long>(b) * p.nh + h) * p.S + qt * BLK + r] = (m + log2f(l)) * kLn2;
+      }
     }
   }
   tc_fence_before();
@@ -324,29 +391,53 @@ struct BwdParams {
   unsigned long long timeout_ns;
 };
 
+// Shared-memory plan of the backward kernel: K | V | Q | dO [2] | P | dS | barriers
+template <int HD>
+struct BwdSmem {
+  static constexpr int TILE_BYTES = (HD / 64) * BLOCK_BYTES;
+  static constexpr int K = 0;
+  static constexpr int V = K + TILE_BYTES;
+  static constexpr int Q = V + TILE_BYTES;
+  static constexpr int DO = Q + TILE_BYTES;
+  static constexpr int P = DO + 2 * TILE_BYTES;
+  static constexpr int DS = P + 2 * BLOCK_BYTES;
+  static constexpr int BARS = DS + 2 * BLOCK_BYTES;
+  static constexpr int END = BARS + 128;
+};
+
 template <int HD>
 __global__ void __launch_bounds__(ATTN_THREADS, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO,
-                     const BwdParams p) {
+                     const __grid_constant__ CUtensorMap tmDQ, const BwdParams p, const int smem_bytes) {
+  using L = BwdSmem<HD>;
   constexpr int KB = HD / 64;
-  constexpr int TILE_BYTES = KB * BLOCK_BYTES;
+  constexpr int TILE_BYTES = L::TILE_BYTES;
+  constexpr int OC = HD / 2;  // gradient columns handled by one row thread
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sK = smem;
-  uint8_t* sV = sK + TILE_BYTES;
-  uint8_t* sQ = sV + TILE_BYTES;
-  uint8_t* sDO = sQ + TILE_BYTES;
-  uint8_t* sP = sDO + TILE_BYTES;       // 128 x 128 bf16, rows = queries, columns = keys
-  uint8_t* sDS = sP + 2 * BLOCK_BYTES;  // same shape
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + 2 * BLOCK_BYTES);
+  if (smem + L::END > smem_raw + smem_bytes) {
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, ST_BAD_ARGUMENT);
+    return;
+  }
+  uint8_t* sK = smem + L::K;
+  uint8_t* sV = smem + L::V;
+  uint8_t* sQ = smem + L::Q;
+  uint8_t* sDO = smem + L::DO;  // [2]
+  uint8_t* sP = smem + L::P;    // 128 x 128 bf16, rows = queries, columns = keys
+  uint8_t* sDS = smem + L::DS;  // same shape
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BARS);
   uint64_t* kv_full = bars;
-  uint64_t* qdo_full = bars + 1;
-  uint64_t* qdo_empty = bars + 2;
-  uint64_t* sdp_full = bars + 3;
-  uint64_t* sdp_empty = bars + 4;
-  uint64_t* pds_full = bars + 5;
-  uint64_t* dq_full = bars + 6;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  uint64_t* q_full = bars + 1;
+  uint64_t* q_empty = bars + 2;
+  uint64_t* do_full = bars + 3;   // [2]
+  uint64_t* do_empty = bars + 5;  // [2]
+  uint64_t* sdp_full = bars + 7;
+  uint64_t* sdp_empty = bars + 8;
+  uint64_t* pds_full = bars + 9;
+  uint64_t* dq_full = bars + 10;
+  uint64_t* stg_full = bars + 11;   // every row thread has put its piece of dQ into the staging area
+  uint64_t* stg_empty = bars + 12;  // the reduce-add copies have read the staging area
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -365,18 +456,25 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(kv_full, 1);
-    mbar_init(qdo_full, 1);
-    mbar_init(qdo_empty, 1);
+    mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&do_full[s], 1);
+      mbar_init(&do_empty[s], 1);
+    }
     mbar_init(sdp_full, 1);
-    mbar_init(sdp_empty, 128);
-    mbar_init(pds_full, 128);
+    mbar_init(sdp_empty, ROW_THREADS);
+    mbar_init(pds_full, ROW_THREADS);
     mbar_init(dq_full, 1);
+    mbar_init(stg_full, ROW_THREADS);
+    mbar_init(stg_empty, 1);
     fence_mbar_init();
     tma_prefetch_desc(&tmQKV);
     tma_prefetch_desc(&tmDO);
+    tma_prefetch_desc(&tmDQ);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);  // S, then dQ [0,128)   dP [128,256)   dV [256,384)   dK [384,512)
+    tmem_alloc(tmem_slot, 512);  // S [0,128)   dP, then dQ [128,256)   dV [256,384)   dK [384,512)
     tmem_relinquish();
   }
   tc_fence_before();
@@ -400,13 +498,18 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
       for (int s = 0; s < n_steps; ++s) {
         const int hq = hk * G + s / q_tiles;
         const int qt = kt + s % q_tiles;
-        if (!mbar_wait(qdo_empty, (s & 1) ^ 1u, wc, ST_TIMEOUT_SMEM_EMPTY)) break;
-        mbar_arrive_expect_tx(qdo_full, 2 * TILE_BYTES);
+        const int st = s & 1;
+        // dO runs one step ahead (two buffers); Q follows as soon as dK of the previous step has read it
+        if (!mbar_wait(&do_empty[st], ((s >> 1) & 1) ^ 1u, wc, ST_TIMEOUT_SMEM_EMPTY)) break;
+        mbar_arrive_expect_tx(&do_full[st], TILE_BYTES);
 #pragma unroll
-        for (int kb = 0; kb < KB; ++kb) {
-          tma_load_2d(sQ + kb * BLOCK_BYTES, &tmQKV, qdo_full, hq * HD + 64 * kb, row0 + qt * BLK);
-          tma_load_2d(sDO + kb * BLOCK_BYTES, &tmDO, qdo_full, hq * HD + 64 * kb, row0 + qt * BLK);
-        }
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_2d(sDO + st * TILE_BYTES + kb * BLOCK_BYTES, &tmDO, &do_full[st], hq * HD + 64 * kb, row0 + qt * BLK);
+        if (!mbar_wait(q_empty, (s & 1) ^ 1u, wc, ST_TIMEOUT_SMEM_EMPTY)) break;
+        mbar_arrive_expect_tx(q_full, TILE_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+          tma_load_2d(sQ + kb * BLOCK_BYTES, &tmQKV, q_full, hq * HD + 64 * kb, row0 + qt * BLK);
       }
     }
   } else if (warp == 1) {
@@ -414,12 +517,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
       const uint32_t idesc_s = make_idesc_bf16(BLK, BLK, 0, 0);   // S, dP: both operands K-major
       const uint32_t idesc_t = make_idesc_bf16(BLK, HD, 1, 1);    // dV, dK: both operands MN-major
       const uint32_t idesc_q = make_idesc_bf16(BLK, HD, 0, 1);    // dQ: dS K-major, K tile MN-major
-      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), do_addr = smem_u32(sDO);
+      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ);
       const uint32_t p_addr = smem_u32(sP), ds_addr = smem_u32(sDS);
-      bool ok = mbar_wait(kv_full, 0, wc, ST_TIMEOUT_SMEM_FULL);
-      for (int s = 0; ok && s < n_steps; ++s) {
-        if (!mbar_wait(qdo_full, s & 1, wc, ST_TIMEOUT_SMEM_FULL)) break;
-        if (!mbar_wait(sdp_empty, (s & 1) ^ 1u, wc, ST_TIMEOUT_TMEM_EMPTY)) break;
+      auto issue_s = [&](int s) -> bool {  // S = Q K^T of step s; the S columns are free once P / dS are written
+        if (!mbar_wait(q_full, s & 1, wc, ST_TIMEOUT_SMEM_FULL)) return false;
         tc_fence_after();
 #pragma unroll
         for (int kb = 0; kb < KB; ++kb) {
@@ -429,6 +530,16 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
                          idesc_s, (kb | k) != 0 ? 1u : 0u);
           }
         }
+        return true;
+      };
+      bool ok = mbar_wait(kv_full, 0, wc, ST_TIMEOUT_SMEM_FULL);
+      if (ok && n_steps > 0) ok = issue_s(0);
+      for (int s = 0; ok && s < n_steps; ++s) {
+        const int st = s & 1;
+        const uint32_t do_addr = smem_u32(sDO + st * TILE_BYTES);
+        if (!mbar_wait(&do_full[st], (s >> 1) & 1, wc, ST_TIMEOUT_SMEM_FULL)) break;
+        if (!mbar_wait(sdp_empty, (s & 1) ^ 1u, wc, ST_TIMEOUT_TMEM_EMPTY)) break;  // dQ of step s-1 was read
+        tc_fence_after();
 #pragma unroll
         for (int kb = 0; kb < KB; ++kb) {
 #pragma unroll
@@ -437,27 +548,32 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
                          desc_kmajor(v_addr + kb * BLOCK_BYTES, k), idesc_s, (kb | k) != 0 ? 1u : 0u);
           }
         }
-        umma_commit(sdp_full);
+        umma_commit(sdp_full);  // covers S of this step as well (issued earlier)
         if (!mbar_wait(pds_full, s & 1, wc, ST_TIMEOUT_SMEM_FULL)) break;
         tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 8; ++k)  // dV[key, d] += sum over queries P[query, key] dO[query, d]
-          umma_bf16_ss(tmem_base + 2 * BLK, desc_mnmajor(p_addr, k), desc_mnmajor(do_addr, k), idesc_t,
-                       (s | k) != 0 ? 1u : 0u);
 #pragma unroll
         for (int k = 0; k < 8; ++k)  // dK[key, d] += sum over queries dS[query, key] Q[query, d]
           umma_bf16_ss(tmem_base + 3 * BLK, desc_mnmajor(ds_addr, k), desc_mnmajor(q_addr, k), idesc_t,
                        (s | k) != 0 ? 1u : 0u);
-        umma_commit(qdo_empty);  // Q and dO may be replaced while dQ is computed
+        umma_commit(q_empty);  // Q may be replaced
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // dV[key, d] += sum over queries P[query, key] dO[query, d]
+          umma_bf16_ss(tmem_base + 2 * BLK, desc_mnmajor(p_addr, k), desc_mnmajor(do_addr, k), idesc_t,
+                       (s | k) != 0 ? 1u : 0u);
+        umma_commit(&do_empty[st]);
 #pragma unroll
         for (int k = 0; k < 8; ++k)  // dQ[query, d] = sum over keys dS[query, key] K[key, d]
-          umma_bf16_ss(tmem_base, desc_kmajor(ds_addr + (k >> 2) * BLOCK_BYTES, k & 3), desc_mnmajor(k_addr, k),
+          umma_bf16_ss(tmem_base + BLK, desc_kmajor(ds_addr + (k >> 2) * BLOCK_BYTES, k & 3), desc_mnmajor(k_addr, k),
                        idesc_q, k != 0 ? 1u : 0u);
         umma_commit(dq_full);
+        // S of the next step runs while the row threads carry this step's dQ to global memory
+        if (s + 1 < n_steps && !issue_s(s + 1)) break;
       }
     }
   } else {
+    // two threads per query row: `half` 0 handles key columns 0-63 and gradient columns [0, HD/2), `half` 1 the rest
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quad * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     bool ok = true;
@@ -470,61 +586,77 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_con
       if (!mbar_wait(sdp_full, s & 1, wc, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
       const int limit = (qt == kt) ? r : BLK;  // keys above `limit` lie in the future of this query
+      // P and dS double as the staging area of the previous step's dQ: its reduce-add copies must have read it
+      if (s > 0 && !mbar_wait(stg_empty, (s - 1) & 1, wc, ST_TIMEOUT_SMEM_EMPTY)) { ok = false; break; }
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
+        const int col0 = half * 64 + c * 32;
         uint32_t sv[32], dp[32];
-        tmem_ld_32x32b_x32(tmem_base + lane_base + c * 32, sv);
-        tmem_ld_32x32b_x32(tmem_base + lane_base + BLK + c * 32, dp);
+        tmem_ld_32x32b_x32(tmem_base + lane_base + col0, sv);
+        tmem_ld_32x32b_x32(tmem_base + lane_base + BLK + col0, dp);
         tmem_ld_wait();
         uint32_t pw[16], dw[16];
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
           float p0 = ex2_approx(fmaf(__uint_as_float(sv[j]), p.scale_log2, -lse2));
           float p1 = ex2_approx(fmaf(__uint_as_float(sv[j + 1]), p.scale_log2, -lse2));
-          if (c * 32 + j > limit) p0 = 0.f;
-          if (c * 32 + j + 1 > limit) p1 = 0.f;
+          if (col0 + j > limit) p0 = 0.f;
+          if (col0 + j + 1 > limit) p1 = 0.f;
           const float d0 = p0 * (__uint_as_float(dp[j]) - dlt) * p.scale;
           const float d1 = p1 * (__uint_as_float(dp[j + 1]) - dlt) * p.scale;
           pw[j >> 1] = pack_bf16x2(p0, p1);
           dw[j >> 1] = pack_bf16x2(d0, d1);
         }
-        store_swizzled_32(sP, r, c * 32, pw);
-        store_swizzled_32(sDS, r, c * 32, dw);
+        store_swizzled_32(sP, r, col0, pw);
+        store_swizzled_32(sDS, r, col0, dw);
       }
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(pds_full);
       if (!mbar_wait(dq_full, s & 1, wc, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      float* dq_row = p.dq + ((static_cast<long long>(row0) + qt * BLK + r) * p.nh + hq) * HD;
+      // dQ leaves through the P / dS area (free once dq_full has completed): pieces of 128 rows x 32 fp32 columns in
+      // the 128-byte swizzle, added to the fp32 query gradient by TMA (the addition happens in L2, whole lines at a
+      // time)
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = 0; c < OC / 32; ++c) {
         uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_base + lane_base + c * 32, v);
+        tmem_ld_32x32b_x32(tmem_base + lane_base + BLK + half * OC + c * 32, v);
         tmem_ld_wait();
+        uint8_t* row = sP + (half * (OC / 32) + c) * BLOCK_BYTES + r * 128;
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + c * 32 + j),
-                       "f"(__uint_as_float(v[j])), "f"(__uint_as_float(v[j + 1])), "f"(__uint_as_float(v[j + 2])),
-                       "f"(__uint_as_float(v[j + 3]))
-                       : "memory");
-        }
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<uint4*>(row + ((j ^ (r & 7)) << 4)) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
       }
       tc_fence_before();
       mbar_arrive(sdp_empty);
+      fence_proxy_async_smem();
+      mbar_arrive(stg_full);
+      if (threadIdx.x == 64) {
+        if (mbar_wait(stg_full, s & 1, wc, ST_TIMEOUT_SMEM_FULL)) {
+#pragma unroll
+          for (int piece = 0; piece < HD / 32; ++piece)
+            tma_reduce_add_3d(&tmDQ, sP + piece * BLOCK_BYTES, hq * HD + piece * 32, row0 + qt * BLK, 0);
+          bulk_commit_group();
+          bulk_wait_group_read<0>();
+        }
+        mbar_arrive(stg_empty);
+      }
+      __syncwarp();
     }
+    if (threadIdx.x == 64) bulk_wait_group<0>();  // the additions have been performed before the CTA ends
     if (ok && n_steps > 0) {
       // the last dq_full covered every MMA of the loop: dV and dK are complete
       const long long grow = static_cast<long long>(row0) + kt * BLK + r;
-      __nv_bfloat16* dv_row = p.dv + (grow * p.nkv + hk) * HD;
-      __nv_bfloat16* dk_row = p.dk + (grow * p.nkv + hk) * HD;
+      __nv_bfloat16* dv_row = p.dv + (grow * p.nkv + hk) * HD + half * OC;
+      __nv_bfloat16* dk_row = p.dk + (grow * p.nkv + hk) * HD + half * OC;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         __nv_bfloat16* dst = which == 0 ? dv_row : dk_row;
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int c = 0; c < OC / 32; ++c) {
           uint32_t v[32];
-          tmem_ld_32x32b_x32(tmem_base + lane_base + (2 + which) * BLK + c * 32, v);
+          tmem_ld_32x32b_x32(tmem_base + lane_base + (2 + which) * BLK + half * OC + c * 32, v);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
@@ -589,22 +721,55 @@ cudaError_t make_tile_map(CUtensorMap* out, const void* ptr, long long rows, lon
   return cudaSuccess;
 }
 
+// fp32 row-major [rows, cols] as a rank-3 map [1, rows, cols]; box = 32 columns x 128 rows, 128-byte swizzle: the
+// destination of the reduce-add copies that carry dQ out of the staging area
+cudaError_t make_reduce_map(CUtensorMap* out, const void* ptr, long long rows, long long cols) {
+  EncodeTiledFn enc = attn_encode_fn();
+  if (enc == nullptr) return cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0 || (cols * 4) % 16 != 0 || rows <= 0 || cols <= 0)
+    return cudaErrorInvalidValue;
+  cuuint64_t gdim[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), 1u};
+  cuuint64_t gstride[2] = {static_cast<cuuint64_t>(cols) * 4, static_cast<cuuint64_t>(rows) * cols * 4};
+  cuuint32_t box[3] = {32u, static_cast<cuuint32_t>(BLK), 1u};
+  cuuint32_t estride[3] = {1u, 1u, 1u};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(ptr), gdim, gstride, box, estride,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    std::fprintf(stderr, "cmoe: cuTensorMapEncodeTiled (attention dq) failed (%d) rows=%lld cols=%lld\n",
+                 static_cast<int>(r), rows, cols);
+    return cudaErrorInvalidValue;
+  }
+  return cudaSuccess;
+}
+
 // One CTA per SM in every configuration: each CTA allocates all 512 TMEM columns, so a second resident CTA would
 // only wait for the first one's columns.
 constexpr int kMinSmem = 120 * 1024;
 
+constexpr int kMaxSmem = 227 * 1024;  // per-CTA limit of sm_100
+
+// The kernels align their plan to 1024 bytes inside the dynamic allocation and check that it fits: ask for the
+// plan plus a full alignment step where the limit allows (the head-dimension-128 forward plan ends 896 bytes
+// below the limit).
+constexpr int clamp_smem(int plan_end) {
+  int want = plan_end + 1024;
+  if (want < kMinSmem) want = kMinSmem;
+  return want > kMaxSmem ? kMaxSmem : want;
+}
 template <int HD>
 constexpr int fwd_smem_bytes() {
-  return (5 * (HD / 64) + 2) * BLOCK_BYTES + 1024 + 256;
+  return clamp_smem(FwdSmem<HD>::END);
 }
 template <int HD>
 constexpr int bwd_smem_bytes() {
-  return (4 * (HD / 64) + 4) * BLOCK_BYTES + 1024 + 256;
+  return clamp_smem(BwdSmem<HD>::END);
 }
+static_assert(FwdSmem<128>::END <= kMaxSmem && BwdSmem<128>::END <= kMaxSmem, "shared-memory plan exceeds the SM");
 
 template <int HD>
 cudaError_t launch_fwd_t(const AttnFwdArgs& a, const CUtensorMap& tm, const FwdParams& p, cudaStream_t stream) {
-  constexpr int smem = fwd_smem_bytes<HD>() > kMinSmem ? fwd_smem_bytes<HD>() : kMinSmem;
+  constexpr int smem = fwd_smem_bytes<HD>();
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
@@ -612,14 +777,14 @@ cudaError_t launch_fwd_t(const AttnFwdArgs& a, const CUtensorMap& tm, const FwdP
   });
   if (attr_err != cudaSuccess) return attr_err;
   dim3 grid(a.S / BLK, a.nh, a.B);
-  attention_fwd_kernel<HD><<<grid, ATTN_THREADS, smem, stream>>>(tm, p);
+  attention_fwd_kernel<HD><<<grid, ATTN_THREADS, smem, stream>>>(tm, p, smem);
   return cudaGetLastError();
 }
 
 template <int HD>
-cudaError_t launch_bwd_t(const AttnBwdArgs& a, const CUtensorMap& tq, const CUtensorMap& td, const BwdParams& p,
-                         cudaStream_t stream) {
-  constexpr int smem = bwd_smem_bytes<HD>() > kMinSmem ? bwd_smem_bytes<HD>() : kMinSmem;
+cudaError_t launch_bwd_t(const AttnBwdArgs& a, const CUtensorMap& tq, const CUtensorMap& td, const CUtensorMap& tdq,
+                         const BwdParams& p, cudaStream_t stream) {
+  constexpr int smem = bwd_smem_bytes<HD>();
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
@@ -627,7 +792,7 @@ cudaError_t launch_bwd_t(const AttnBwdArgs& a, const CUtensorMap& tq, const CUte
   });
   if (attr_err != cudaSuccess) return attr_err;
   dim3 grid(a.S / BLK, a.nkv, a.B);
-  attention_bwd_kernel<HD><<<grid, ATTN_THREADS, smem, stream>>>(tq, td, p);
+  attention_bwd_kernel<HD><<<grid, ATTN_THREADS, smem, stream>>>(tq, td, tdq, p, smem);
   return cudaGetLastError();
 }
 
@@ -671,6 +836,9 @@ cudaError_t launch_attention_bwd(const AttnBwdArgs& a, cudaStream_t stream) {
   if (e != cudaSuccess) return e;
   e = make_tile_map(&td, a.dout, rows, static_cast<long long>(a.nh) * a.hd);
   if (e != cudaSuccess) return e;
+  CUtensorMap tdq;
+  e = make_reduce_map(&tdq, a.dq, rows, static_cast<long long>(a.nh) * a.hd);
+  if (e != cudaSuccess) return e;
   {
     const long long warps = rows * a.nh;
     const int threads = 256;
@@ -694,7 +862,7 @@ cudaError_t launch_attention_bwd(const AttnBwdArgs& a, cudaStream_t stream) {
   p.scale_log2 = p.scale * kLog2e;
   p.status = a.status;
   p.timeout_ns = a.timeout_ns ? a.timeout_ns : kDefaultTimeoutNs;
-  return a.hd == 128 ? launch_bwd_t<128>(a, tq, td, p, stream) : launch_bwd_t<64>(a, tq, td, p, stream);
+  return a.hd == 128 ? launch_bwd_t<128>(a, tq, td, tdq, p, stream) : launch_bwd_t<64>(a, tq, td, tdq, p, stream);
 }
 
 }  // namespace cmoe
