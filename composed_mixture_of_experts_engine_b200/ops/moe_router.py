@@ -249,6 +249,15 @@ def moe_topk_route(tokens: torch.Tensor, gate_w: torch.Tensor, k: int, force_ref
 # --------------------------------------------------------------------------------------------------
 # module
 # --------------------------------------------------------------------------------------------------
+def _fused_stage_bytes(num_experts: int) -> int:
+    """Shared memory of one pipeline stage of the fused router kernel (csrc/router.cu): a 128-token x 64-wide bf16
+    slice of the activations plus the matching slice of the gate weights, experts padded to a multiple of 64.
+    Reported on every path as the on-chip working set per block, like the reference's theoretical figure
+    (pkg/kernels/moe_router.py:703-714)."""
+    e_chunks = max(1, (num_experts + 63) // 64)
+    return 128 * 64 * 2 + e_chunks * 64 * 64 * 2
+
+
 @dataclass
 class RouterProfile:
     sram_bytes_per_block: int = 0
@@ -319,7 +328,7 @@ class MoERouter(nn.Module):
         aux = float(pend["aux_loss"]) if pend.get("aux_loss") is not None else 0.0
         mean = float(counts.mean())
         return RouterProfile(
-            sram_bytes_per_block=pend.get("sram", 0),
+            sram_bytes_per_block=_fused_stage_bytes(E),
             achieved_bandwidth_gbps=(bytes_moved / (kernel_ms * 1e6)) if kernel_ms > 0 else 0.0,
             kernel_ms=kernel_ms,
             used_triton=False,

@@ -76,9 +76,10 @@ def compute_capacity_drop_mask(idx: torch.Tensor, num_experts: int, capacity: in
 class _SwiGLUExpert(nn.Module):
     """``w_down(silu(w_gate(x)) * w_up(x))`` with the intermediate kept sharded over the tensor-parallel group."""
 
-    def __init__(self, hidden: int, ffn: int, topology: Optional[ParallelTopology] = None,
+    def __init__(self, hidden_dim: int, ffn_dim: int, topology: Optional[ParallelTopology] = None,
                  dtype: Optional[torch.dtype] = None, device=None):
         super().__init__()
+        hidden, ffn = hidden_dim, ffn_dim
         self.hidden, self.ffn = hidden, ffn
         self.w_gate = ColumnParallelLinear(hidden, ffn, bias=False, topology=topology, dtype=dtype, device=device,
                                            gather_output=False)
@@ -238,11 +239,18 @@ class DistributedMoELayer(nn.Module):
     def _experts_are_views(self) -> bool:
         return len(self.experts) == len(self.local_expert_ids) and all(isinstance(e, _ExpertView) for e in self.experts)
 
-    def _expert_to_rank(self, expert_id: int) -> int:
-        """EP rank that owns ``expert_id`` (contiguous blocks, remainder on the lowest ranks)."""
+    def _expert_to_rank(self, expert_id):
+        """EP rank that owns ``expert_id`` (contiguous blocks, remainder on the lowest ranks).  Takes an int and
+        returns an int, or takes an integer tensor of any shape and returns a tensor of ranks of that shape
+        (reference: pkg/distributed/moe_layer.py:362-389)."""
         ep = self.topology.ep_size
         per, rem = divmod(self.num_experts, ep)
         boundary = rem * (per + 1)
+        if torch.is_tensor(expert_id):
+            e = expert_id.long()
+            low = torch.div(e, per + 1, rounding_mode="floor")
+            high = rem + torch.div(e - boundary, max(per, 1), rounding_mode="floor")
+            return torch.where(e < boundary, low, high)
         if expert_id < boundary:
             return expert_id // (per + 1)
         return rem + (expert_id - boundary) // max(per, 1)

@@ -89,6 +89,27 @@ class PipelineStage:
         for req in dist.batch_isend_irecv(ops):
             req.wait()
 
+    _HEADER_DTYPES = (torch.float32, torch.bfloat16, torch.float16, torch.float64, torch.int64, torch.int32)
+    _HEADER_LEN = 12  # count, dtype code, rank, up to 9 extents
+
+    def _send_header(self, m: int, shape: Sequence[int], dtype: torch.dtype, device: torch.device) -> None:
+        if len(shape) > self._HEADER_LEN - 3:
+            raise ValueError(f"activation rank {len(shape)} does not fit the pipeline header")
+        vals = [m, self._HEADER_DTYPES.index(dtype), len(shape), *shape]
+        vals += [0] * (self._HEADER_LEN - len(vals))
+        self._exchange(send_next=torch.tensor(vals, dtype=torch.int64, device=device))
+
+    def _recv_header(self, device: torch.device) -> Tuple[int, Tuple[int, ...], torch.dtype]:
+        """Receive the header from the previous stage and pass a zero-count header on at once (the real one for the
+        next stage follows this stage's first forward, when the shape of its output is known)."""
+        buf = torch.empty(self._HEADER_LEN, dtype=torch.int64, device=device)
+        self._exchange(recv_prev=buf)
+        vals = buf.tolist()
+        m, code, nd = int(vals[0]), int(vals[1]), int(vals[2])
+        if m == 0 and not self.is_last:
+            self._send_header(0, (), torch.float32, device)
+        return m, tuple(int(v) for v in vals[3: 3 + nd]), self._HEADER_DTYPES[code]
+
     # ---- single steps -------------------------------------------------------------------------
     def forward_step(self, micro_batch: torch.Tensor) -> torch.Tensor:
         """Apply this stage's module (in a multi-process pipeline: receive, apply, send)."""
@@ -143,8 +164,19 @@ class PipelineStage:
         if not self._multi_process:
             raise RuntimeError("run_1f1b_distributed requires pp_size > 1 and dist.is_initialized(). "
                                "Use run_1f1b() for single-process scheduling.")
-        m = num_microbatches if num_microbatches is not None else len(micro_batches)
+        # Callers that give neither a count nor a shape use the reference's convention
+        # (pkg/distributed/pipeline_parallel.py:126-179): only the first stage holds micro-batches, later stages pass
+        # an empty list and learn the count, shape and dtype from a small header that travels down the pipeline ahead
+        # of the first activation.  All stages of one call must use the same convention.
+        announce = num_microbatches is None and activation_shape is None
+        device = device or (self.topology.device if self.topology is not None else torch.device("cpu"))
+        if announce and not self.is_first:
+            m, activation_shape, activation_dtype = self._recv_header(device)
+        else:
+            m = num_microbatches if num_microbatches is not None else len(micro_batches)
         if m == 0:
+            if announce and self.is_first and not self.is_last:
+                self._send_header(0, (), torch.float32, device)
             return [], []
         if not self.is_first:
             if activation_shape is None:
@@ -152,9 +184,8 @@ class PipelineStage:
                     raise ValueError("non-first stages need activation_shape or a template microbatch")
                 activation_shape = tuple(micro_batches[0].shape)
                 activation_dtype = activation_dtype or micro_batches[0].dtype
-                device = device or micro_batches[0].device
+                device = micro_batches[0].device
             activation_dtype = activation_dtype or torch.float32
-            device = device or (self.topology.device if self.topology is not None else torch.device("cpu"))
 
         import inspect
 
@@ -199,6 +230,8 @@ class PipelineStage:
         # warm-up forwards
         for i in range(warm):
             out = fwd(i, recv_buf)
+            if announce and i == 0 and not self.is_last:
+                self._send_header(m, tuple(out.shape), out.dtype, device)
             nxt = None
             if not self.is_first and (i + 1 < m):
                 nxt = new_act()

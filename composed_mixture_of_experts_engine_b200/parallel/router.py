@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import logging
 import math
+import warnings
 from dataclasses import dataclass
 
 import torch
@@ -44,8 +45,9 @@ class MoERouterInterface(nn.Module):
         if capacity_factor <= 0:
             raise ValueError("capacity_factor must be positive")
         if capacity_factor < 1.0:
-            log.warning("capacity_factor=%.2f < 1.0: tokens will be dropped even under perfect balance",
-                        capacity_factor)
+            warnings.warn(
+                f"capacity_factor={capacity_factor} < 1.0 will silently drop tokens even under perfect balance; "
+                "consider a value of at least 1.0", UserWarning, stacklevel=2)
         self.hidden_dim, self.num_experts, self.top_k = hidden_dim, num_experts, top_k
         self.capacity_factor = capacity_factor
         from ..ops.moe_router import MoERouter

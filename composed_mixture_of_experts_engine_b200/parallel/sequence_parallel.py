@@ -5,10 +5,12 @@
 (all-gather forward).  Same names and argument order as the reference
 (pkg/distributed/sequence_parallel.py:56-166).
 
-``next_weight``: a projection applied row-wise commutes with slicing the sequence, so the fused variant returns
-``F.linear(x_shard, next_weight)`` and needs no collective at all.  (The reference's fused variant summed
-different sequence chunks with an all-reduce, ``sequence_parallel.py:129-134``, which is not the same
-function as slice-then-project.)
+``next_weight``: the fused variant distributes the projection that follows over the group.  Every rank projects
+its own ``S/tp`` rows with ``next_weight`` and the results are all-gathered along the sequence, so every rank
+returns ``F.linear(x, next_weight)`` of the full sequence, ``[B, S, F]``, having computed ``1/tp`` of it.  This is
+the behaviour the reference documents and tests (tests/test_sequence_parallel_v03.py:139-196); its own fused
+variant all-reduced different sequence chunks (pkg/distributed/sequence_parallel.py:129-134), which is not that
+function.
 """
 
 from __future__ import annotations
@@ -40,6 +42,9 @@ def scatter_to_sequence_parallel(x: torch.Tensor, topology: Optional[ParallelTop
         x = C.split(x, seq_dim, tp_process_group(topology))
     if next_weight is not None:
         x = F.linear(x, next_weight)
+        if tp > 1:
+            # every rank holds the same full-sequence gradient afterwards: the backward keeps this rank's slice
+            x = C.all_gather(x, seq_dim, tp_process_group(topology), reduce_scatter_grad=False)
     return x
 
 

@@ -200,7 +200,7 @@ class MoEConfig(BaseModel):
             raw = yaml.safe_load(fh)
         if not isinstance(raw, dict):
             raise ConfigValidationError(
-                f"Config file {p} did not parse to a mapping (got {type(raw).__name__}); is the YAML valid?"
+                f"Config file {p} did not parse to a dict (got {type(raw).__name__}); is the YAML valid?"
             )
         return cls.from_dict(raw, source=str(p))
 

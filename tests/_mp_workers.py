@@ -139,9 +139,8 @@ def sp_linears(rank, world):
     y2 = F.linear(F.silu(F.linear(x2, Wc)), Wr)
     y2.sum().backward()
     fused = scatter_to_sequence_parallel(x_full, topo, next_weight=Wc)
-    S = 8 // world
     return {"shape": list(xs.shape), "y": float((y - y2).abs().max()), "dx": float((x.grad - x2.grad).abs().max()),
-            "fused": float((fused - F.linear(x_full[:, rank * S:(rank + 1) * S], Wc)).abs().max())}
+            "fused": float((fused - F.linear(x_full, Wc)).abs().max())}
 
 
 def pp_1f1b(rank, world, m):
@@ -413,3 +412,26 @@ def gpu_tp_sp(rank, world, transport="auto"):
         out[f"dwr{it}"] = rel(row.weight.grad, wr.grad[:, rank * sh:(rank + 1) * sh])
     check_status(dev)
     return out
+
+
+def pp_announced(rank, world, m):
+    """The reference's calling convention (tests/test_pipeline_parallel.py:174-243): only stage 0 holds the
+    micro-batches, later stages pass an empty list and no shape; count, shape and dtype travel in a header."""
+    import torch
+    import torch.nn as nn
+
+    from composed_mixture_of_experts_engine_b200.parallel import PipelineStage, build_topology
+
+    topo = build_topology(dp_size=1, ep_size=1, tp_size=1, pp_size=world, device_type="cpu")
+    mod = nn.Linear(6, 4 if rank == 0 else 4, bias=False) if rank == 0 else nn.Linear(4, 4, bias=False)
+    with torch.no_grad():
+        mod.weight.fill_(0.5)
+    stage = PipelineStage(rank, world, mod, topo)
+    mbs = [torch.ones(3, 6) for _ in range(m)] if rank == 0 else []
+    outs, losses = stage.run_1f1b_distributed(mbs, loss_fn=lambda o: o.sum())
+    expect = 6 * 0.5 * (4 * 0.5) ** (world - 1)
+    return {"n_out": len(outs), "n_loss": len(losses),
+            "out": max((float((o - expect).abs().max()) for o in outs), default=0.0),
+            "shape": list(outs[0].shape) if outs else [],
+            "grad": float(mod.weight.grad.abs().sum()) if mod.weight.grad is not None else 0.0}
+

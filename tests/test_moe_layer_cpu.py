@@ -89,6 +89,8 @@ def test_standalone_swiglu_expert():
     x = torch.randn(4, 16)
     want = F.linear(F.silu(F.linear(x, e.w_gate.weight)) * F.linear(x, e.w_up.weight), e.w_down.weight)
     assert torch.allclose(e(x), want, atol=1e-6)
+    by_name = _SwiGLUExpert(hidden_dim=16, ffn_dim=32, topology=None)  # the reference's keyword names
+    assert by_name.w_gate.weight.shape == (32, 16) and by_name.w_down.weight.shape == (16, 32)
 
 
 @pytest.mark.parametrize("ids,want", [([0, 0, 1, 0, 1, 2], [0, 1, 0, 2, 1, 0]), ([5], [0]), ([], []),
@@ -151,6 +153,11 @@ def test_expert_to_rank_round_trip():
     for r in range(3):
         for e in topo.experts_on_rank(10, r):
             assert layer._expert_to_rank(e) == r
+    # tensor in, tensor of ranks out (the reference's calling convention, pkg/distributed/moe_layer.py:362-389)
+    ids = torch.arange(10).view(2, 5)
+    ranks = layer._expert_to_rank(ids)
+    assert ranks.shape == ids.shape and ranks.dtype == torch.int64
+    assert ranks.flatten().tolist() == [layer._expert_to_rank(int(e)) for e in ids.flatten()]
 
 
 def test_tp1_linears_equal_nn_linear():

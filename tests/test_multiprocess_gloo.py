@@ -81,6 +81,19 @@ def test_pipeline_1f1b(world, m):
     assert res[0]["n_loss"] == 0
 
 
+@pytest.mark.parametrize("world,m", [(2, 4), (3, 2), (2, 0)])
+def test_pipeline_1f1b_count_and_shape_announced_by_the_first_stage(world, m):
+    """Later stages called with an empty list learn the micro-batch count and the activation shape from the header
+    (the reference's own two-rank test of this convention fails in the reference)."""
+    res = _spawn("pp_announced", world, m)
+    last = res[world - 1]
+    assert last["n_out"] == m and last["n_loss"] == m and last["out"] < 1e-5
+    if m:
+        assert last["shape"] == [3, 4]
+        assert all(out["grad"] > 0 for out in res.values())
+    assert res[0]["n_out"] == 0
+
+
 def test_trainer_cpu_smoke_ep2():
     """Two gloo ranks, ep=2, tiny decoder, fp32 AdamW, 20 steps: finite, decreasing loss; replicas stay in sync."""
     res = _spawn("trainer_steps", 2, str(CONFIGS / "cpu_smoke_ep2.yaml"), 20, timeout=600)

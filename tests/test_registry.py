@@ -81,3 +81,20 @@ def test_decoder_is_causal():
     ids2[0, -1] = (ids2[0, -1] + 1) % 128
     a, b = m(ids), m(ids2)
     assert torch.allclose(a[0, :-1], b[0, :-1], atol=1e-6) and not torch.allclose(a[0, -1], b[0, -1])
+
+
+def test_sm100_attention_shape_gate_is_off_by_default(monkeypatch):
+    """The hand-written attention kernels are opt-in and only take sequence lengths that are multiples of 128 and
+    head dimensions 64 / 128; everything else stays on the library path."""
+    import torch
+
+    from composed_mixture_of_experts_engine_b200.ops import attention_sm100 as A
+
+    monkeypatch.delenv("CMOE_ATTN_SM100", raising=False)
+    assert not A.enabled()
+    monkeypatch.setenv("CMOE_ATTN_SM100", "1")
+    assert A.enabled()
+    assert A.shape_supported(4096, 16, 16, 128) and A.shape_supported(256, 32, 8, 64)
+    assert not A.shape_supported(100, 4, 4, 64) and not A.shape_supported(256, 4, 3, 64)
+    q = torch.randn(1, 128, 2, 64)  # CPU tensors never qualify
+    assert not A.supported(q, q, q)

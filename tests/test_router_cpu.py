@@ -94,6 +94,7 @@ def test_module_forward_profile_and_grads():
     assert r.gate_w.grad is not None and torch.isfinite(r.gate_w.grad).all() and x.grad.abs().sum() > 0
     p = r.last_profile
     assert p.used_triton is False and p.used_fused_kernel is False
+    assert p.sram_bytes_per_block == 128 * 64 * 2 + 64 * 64 * 2  # one stage of the fused kernel's tiles
     assert p.tokens_per_expert_mean == pytest.approx(100 / 8)
     assert p.expert_load_imbalance == pytest.approx(float(cnt.max()) / (100 / 8))
     assert p.router_z_loss == pytest.approx(_compute_router_z_loss(r._last_logits), rel=1e-4)
@@ -125,6 +126,8 @@ def test_interface_validation_and_budget():
         assert ri.capacity_budget(n) == want == math.ceil(1.25 * n * 2 / 8)
     with pytest.raises(ValueError):
         MoERouterInterface(32, 4, 8)
+    with pytest.warns(UserWarning, match="silently drop tokens"):
+        MoERouterInterface(32, 4, 2, capacity_factor=0.9)
     torch.randn(4, 32)
     stats.combine_weights.sum()
     x = torch.randn(16, 32, requires_grad=True)
