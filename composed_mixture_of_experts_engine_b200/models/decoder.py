@@ -14,7 +14,6 @@ stage: final norm and LM head).
 
 from __future__ import annotations
 
-import math
 from typing import Dict, List, Optional, Tuple
 
 import torch

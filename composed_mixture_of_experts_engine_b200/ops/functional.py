@@ -9,7 +9,6 @@ RoPE and attention are additions (the reference model has neither).
 
 from __future__ import annotations
 
-import math
 from typing import Optional, Tuple
 
 import torch
@@ -17,7 +16,7 @@ import torch.nn.functional as F
 
 from . import _ext, kernels
 from . import attention_sm100 as _attn_sm100
-from .kernels import EPI_STORE, EPI_SWIGLU_BWD, EPI_SWIGLU_FWD, GEMM_GROUPED_K, GEMM_GROUPED_M, MoEPlan
+from .kernels import EPI_SWIGLU_BWD, EPI_SWIGLU_FWD, GEMM_GROUPED_K, GEMM_GROUPED_M, MoEPlan
 
 
 def on_device_path(*tensors: torch.Tensor) -> bool:

@@ -18,7 +18,6 @@ moments in the optimizer) is one kernel launch per parameter group:
 
 from __future__ import annotations
 
-import math
 from typing import Dict, Iterable, List, Optional, Tuple
 
 import torch

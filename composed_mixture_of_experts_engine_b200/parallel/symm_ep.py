@@ -28,7 +28,6 @@ scatter loop of pkg/distributed/moe_layer.py:318-353.
 from __future__ import annotations
 
 import os
-from typing import Optional
 
 import torch
 import torch.distributed as dist

@@ -33,3 +33,20 @@ def test_reference_arm_without_a_gpu_reports_unavailable_and_exits_zero():
     assert out.returncode == 0
     rec = json.loads([ln for ln in out.stdout.splitlines() if ln.startswith("{")][-1])
     assert rec["impl"] == "reference" and "unavailable" in rec
+
+
+def test_loss_curves_fall_together_with_the_reference():
+    """Equal weights, equal batches, equal optimizer: both curves fall and stay close (the reference's layer picks
+    experts by row position, so the curves are near, not identical)."""
+    if not (ROOT / "baseline" / "_ref" / "pkg").is_dir():
+        pytest.skip("baseline/_ref is not installed")
+    out = subprocess.run([sys.executable, str(ROOT / "benchmarks" / "loss_parity.py"), "--steps", "60"],
+                         capture_output=True, text=True, timeout=600, cwd=str(ROOT))
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    ref_first, ours_first = line["first_loss"]
+    ref_last, ours_last = line["last_loss"]
+    assert abs(ref_first - ours_first) < 0.1
+    assert ref_last < ref_first - 0.5 and ours_last < ours_first - 0.5
+    assert line["max_abs_diff"] < 0.5
+

@@ -2,7 +2,6 @@
 (reference: tests/test_distributed.py, test_capacity_dropping.py, test_tensor_parallel.py,
 test_sequence_parallel_v03.py)."""
 
-import math
 
 import pytest
 import torch

@@ -1,7 +1,6 @@
 """Property-based invariants (Hypothesis, 50 examples each): conservation, normalisation, index range, finiteness over
 input scales, complete and balanced expert ownership, config validity (reference: tests/test_properties.py)."""
 
-import math
 
 import pytest
 import torch
