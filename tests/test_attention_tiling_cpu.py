@@ -1,0 +1,99 @@
+"""CPU restatement (fp64) of the tile schedules of csrc/attention.cu, checked against plain causal attention.
+
+The forward keeps, per query row, a running maximum in the base-2 domain, a running sum and an output row that is
+rescaled by ``alpha`` of the *previous* tile when that tile's partial product is added (the partial product of tile
+i is read back while tile i+1 is in its softmax).  The backward walks the query tiles at or below a key tile's
+diagonal and forms P from the saved log-sum-exp, dS = P (dP - delta) scale, and the three gradient products.
+These tests pin that arithmetic independently of the GPU; the kernels themselves are tested in
+tests/test_gpu_attention.py.
+"""
+
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+BLK = 128
+
+
+def _reference(q, k, v):
+    S, hd = q.shape
+    scores = (q @ k.T) / math.sqrt(hd)
+    mask = torch.ones(S, S, dtype=torch.bool).tril()
+    scores = scores.masked_fill(~mask, float("-inf"))
+    return torch.softmax(scores, -1) @ v, torch.logsumexp(scores, -1)
+
+
+def _forward_tiled(q, k, v):
+    S, hd = q.shape
+    T = S // BLK
+    sl2 = math.log2(math.e) / math.sqrt(hd)
+    out = torch.zeros_like(q)
+    lse = torch.zeros(S, dtype=q.dtype)
+    rows = torch.arange(BLK)
+    for qt in range(T):
+        Q = q[qt * BLK:(qt + 1) * BLK]
+        O = torch.zeros(BLK, hd, dtype=q.dtype)
+        m = torch.full((BLK,), -float("inf"), dtype=q.dtype)
+        l = torch.zeros(BLK, dtype=q.dtype)
+        alpha_saved = torch.zeros(BLK, dtype=q.dtype)
+        pv = [None, None]
+        for i in range(qt + 1):
+            st = i & 1
+            s = Q @ k[i * BLK:(i + 1) * BLK].T
+            limit = rows if i == qt else torch.full((BLK,), BLK)
+            valid = torch.arange(BLK)[None, :] <= limit[:, None]
+            mx = s.masked_fill(~valid, -float("inf")).max(-1).values
+            m_new = torch.maximum(m, mx * sl2)
+            alpha = torch.exp2(m - m_new)
+            p = torch.exp2(s * sl2 - m_new[:, None]) * valid
+            l = l * alpha + p.sum(-1)
+            m = m_new
+            pv[st] = p @ v[i * BLK:(i + 1) * BLK]
+            if i > 0:
+                O = O * alpha_saved[:, None] + pv[st ^ 1]
+            alpha_saved = alpha
+        O = O * alpha_saved[:, None] + pv[qt & 1]
+        out[qt * BLK:(qt + 1) * BLK] = O / l[:, None]
+        lse[qt * BLK:(qt + 1) * BLK] = (m + torch.log2(l)) * math.log(2)
+    return out, lse
+
+
+def _backward_tiled(q, k, v, out, lse, go):
+    S, hd = q.shape
+    T = S // BLK
+    sc = 1 / math.sqrt(hd)
+    sl2 = sc * math.log2(math.e)
+    delta = (go * out).sum(-1)
+    dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)
+    rows = torch.arange(BLK)
+    for kt in range(T):
+        K, V = k[kt * BLK:(kt + 1) * BLK], v[kt * BLK:(kt + 1) * BLK]
+        for qt in range(kt, T):
+            sl = slice(qt * BLK, (qt + 1) * BLK)
+            s, dp = q[sl] @ K.T, go[sl] @ V.T
+            limit = rows if qt == kt else torch.full((BLK,), BLK)
+            valid = torch.arange(BLK)[None, :] <= limit[:, None]
+            p = torch.exp2(s * sl2 - (lse[sl] * math.log2(math.e))[:, None]) * valid
+            ds = p * (dp - delta[sl][:, None]) * sc
+            dv[kt * BLK:(kt + 1) * BLK] += p.T @ go[sl]
+            dk[kt * BLK:(kt + 1) * BLK] += ds.T @ q[sl]
+            dq[sl] += ds @ K
+    return dq, dk, dv
+
+
+@pytest.mark.parametrize("S,hd", [(128, 64), (384, 64), (512, 128)])
+def test_tile_schedules_match_plain_causal_attention(S, hd):
+    torch.manual_seed(0)
+    q, k, v, go = (torch.randn(S, hd, dtype=torch.float64) for _ in range(4))
+    ref, lse_ref = _reference(q, k, v)
+    out, lse = _forward_tiled(q, k, v)
+    assert (out - ref).abs().max() < 1e-12 and (lse - lse_ref).abs().max() < 1e-12
+
+    qa, ka, va = (t.clone().requires_grad_() for t in (q, k, v))
+    _reference(qa, ka, va)[0].backward(go)
+    dq, dk, dv = _backward_tiled(q, k, v, out, lse, go)
+    for got, want in ((dq, qa.grad), (dk, ka.grad), (dv, va.grad)):
+        assert (got - want).abs().max() < 1e-11
