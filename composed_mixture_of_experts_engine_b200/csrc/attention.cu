@@ -23,6 +23,7 @@
 #include "attention.cuh"
 
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -798,6 +799,16 @@ cudaError_t launch_bwd_t(const AttnBwdArgs& a, const CUtensorMap& tq, const CUte
 
 }  // namespace
 
+namespace {
+bool fwd2_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("CMOE_ATTN_FWD2");
+    return v == nullptr || v[0] != '0';
+  }();
+  return on;
+}
+}  // namespace
+
 bool attention_shape_supported(int S, int nh, int nkv, int hd) {
   return S > 0 && S % BLK == 0 && (hd == 64 || hd == 128) && nkv > 0 && nh % nkv == 0;
 }
@@ -807,6 +818,11 @@ cudaError_t launch_attention_fwd(const AttnFwdArgs& a, cudaStream_t stream) {
       a.qkv == nullptr || a.out == nullptr || a.lse == nullptr)
     return cudaErrorInvalidValue;
   if (static_cast<long long>(a.B) * a.S > 0x7fffffffLL) return cudaErrorInvalidValue;
+  if (a.hd == 128 && a.S % 256 == 0 && a.scale <= 0.f && fwd2_enabled()) {
+    // two query tiles per CTA: 0.426 ms against 0.522 ms at B4 S4096 nh16
+    return static_cast<cudaError_t>(cmoe_attention_fwd2(a.qkv, a.out, a.lse, a.B, a.S, a.nh, a.nkv, a.hd, a.status,
+                                                        a.timeout_ns, stream));
+  }
   CUtensorMap tm;
   cudaError_t e = make_tile_map(&tm, a.qkv, static_cast<long long>(a.B) * a.S,
                                 static_cast<long long>(a.nh + 2 * a.nkv) * a.hd);

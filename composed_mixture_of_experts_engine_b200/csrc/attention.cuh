@@ -37,7 +37,14 @@ struct AttnBwdArgs {
 };
 
 bool attention_shape_supported(int S, int nh, int nkv, int hd);
+// The forward picks the two-query-tile kernel (attention_fwd2.cu) when the head dimension is 128, S is a multiple
+// of 256 and the default scale is used; CMOE_ATTN_FWD2=0 keeps the one-tile kernel.
 cudaError_t launch_attention_fwd(const AttnFwdArgs& a, cudaStream_t stream);
 cudaError_t launch_attention_bwd(const AttnBwdArgs& a, cudaStream_t stream);
 
 }  // namespace cmoe
+
+// Raw-pointer entry of the two-query-tile forward kernel (attention_fwd2.cu): S % 256 == 0, hd 128.  Returns a
+// cudaError_t as int.
+extern "C" int cmoe_attention_fwd2(const void* qkv, void* out, float* lse, int B, int S, int nh, int nkv, int hd,
+                                   int* status, unsigned long long timeout_ns, void* stream);

@@ -34,6 +34,7 @@ _SOURCES = [
     "router.cu",
     "ops.cu",
     "attention.cu",
+    "attention_fwd2.cu",
     "ep.cu",
     "noalloc.cu",
 ]

@@ -19,6 +19,7 @@ SHAPES = [
     (1, 384, 4, 2, 128),   # grouped-query, three key tiles, off-diagonal and diagonal tiles
     (2, 256, 2, 2, 64),    # one 64-column block per head
     (1, 128, 2, 1, 128),   # a single (diagonal) tile
+    (1, 512, 4, 2, 128),   # S a multiple of 256 at hd 128: the two-query-tile forward kernel
 ]
 
 
