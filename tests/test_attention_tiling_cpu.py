@@ -61,6 +61,43 @@ def _forward_tiled(q, k, v):
     return out, lse
 
 
+def _forward_lazy_rescale(q, k, v, threshold=8.0):
+    """The two-query-tile kernel (csrc/attention_fwd2.cu): O accumulates across key tiles and is rescaled only when
+    the row maximum has grown by more than ``threshold`` (base 2) since the value the probabilities are taken
+    against was last moved; in between that value is stale and the probabilities exceed 1 by at most 2^threshold."""
+    S, hd = q.shape
+    T = S // BLK
+    sl2 = math.log2(math.e) / math.sqrt(hd)
+    out = torch.zeros_like(q)
+    lse = torch.zeros(S, dtype=q.dtype)
+    rows = torch.arange(BLK)
+    rescales = 0
+    for qt in range(T):
+        Q = q[qt * BLK:(qt + 1) * BLK]
+        O = torch.zeros(BLK, hd, dtype=q.dtype)
+        m_used = torch.full((BLK,), -float("inf"), dtype=q.dtype)
+        l = torch.zeros(BLK, dtype=q.dtype)
+        for i in range(qt + 1):
+            s = Q @ k[i * BLK:(i + 1) * BLK].T
+            limit = rows if i == qt else torch.full((BLK,), BLK)
+            valid = torch.arange(BLK)[None, :] <= limit[:, None]
+            mx = s.masked_fill(~valid, -float("inf")).max(-1).values
+            m_new = torch.maximum(m_used, mx * sl2)
+            grow = (m_new - m_used) > threshold
+            alpha = torch.where(grow, torch.exp2(m_used - m_new), torch.ones_like(m_new))
+            m_used = torch.where(grow, m_new, m_used)
+            p = torch.exp2(s * sl2 - m_used[:, None]) * valid
+            assert float(p.max()) <= 2.0 ** threshold * (1 + 1e-9)
+            l = l * alpha + p.sum(-1)
+            if i > 0:
+                rescales += int(grow.any())
+                O = O * alpha[:, None]
+            O = O + p @ v[i * BLK:(i + 1) * BLK]
+        out[qt * BLK:(qt + 1) * BLK] = O / l[:, None]
+        lse[qt * BLK:(qt + 1) * BLK] = (m_used + torch.log2(l)) * math.log(2)
+    return out, lse, rescales
+
+
 def _backward_tiled(q, k, v, out, lse, go):
     S, hd = q.shape
     T = S // BLK
@@ -97,3 +134,15 @@ def test_tile_schedules_match_plain_causal_attention(S, hd):
     dq, dk, dv = _backward_tiled(q, k, v, out, lse, go)
     for got, want in ((dq, qa.grad), (dk, ka.grad), (dv, va.grad)):
         assert (got - want).abs().max() < 1e-11
+
+
+def test_lazy_rescale_schedule_is_exact_and_rescales_rarely():
+    torch.manual_seed(1)
+    S, hd = 1024, 128
+    q, k, v = (torch.randn(S, hd, dtype=torch.float64) for _ in range(3))
+    ref, lse_ref = _reference(q, k, v)
+    out, lse, rescales = _forward_lazy_rescale(q, k, v)
+    assert (out - ref).abs().max() < 1e-12 and (lse - lse_ref).abs().max() < 1e-12
+    tiles_after_first = sum(qt for qt in range(S // BLK))
+    assert rescales < tiles_after_first // 2
+
