@@ -12,6 +12,8 @@
 // 2-9 run the softmax with two threads per query row: each keeps the running maximum (exchanged once per tile),
 // its part of the running sum and half of the output row in registers (O = O * alpha + P V, read back tile by tile).
 //
+// (Head dimension 128 with S a multiple of 256 takes the two-query-tile forward of attention_fwd2.cu instead.)
+//
 // Backward: one CTA per (128 key rows, kv head, batch) loops over the query heads of its group and the query
 // tiles at or below the diagonal: S = Q K^T and dP = dO V^T, then P and dS = P (dP - delta) scale in shared
 // memory, then dK += dS^T Q, dV += P^T dO (accumulators stay in TMEM for the whole loop) and dQ = dS K, which the
