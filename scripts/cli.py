@@ -73,6 +73,16 @@ def cmd_benchmark(cuda: bool = False, json_out: Optional[str] = None) -> int:
     return run_benchmark.main(argv)
 
 
+def cmd_plan(config: str, world: Optional[int] = None) -> int:
+    """Per-GPU memory plan of a configuration against the 180 GB of a B200."""
+    from composed_mixture_of_experts_engine_b200.utils.config import MoEConfig
+    from composed_mixture_of_experts_engine_b200.utils.memory import format_plan, plan_memory
+
+    plan = plan_memory(MoEConfig.from_yaml(config), world)
+    print(format_plan(plan))
+    return 0 if plan["fits"] else 1
+
+
 def cmd_info() -> int:
     import torch
 
@@ -107,6 +117,10 @@ if typer is not None:
         raise typer.Exit(cmd_benchmark(cuda, json_out))
 
     @app.command()
+    def plan(config: str = typer.Option(..., "--config", "-c"), world: Optional[int] = typer.Option(None, "--world")):
+        raise typer.Exit(cmd_plan(config, world))
+
+    @app.command()
     def validate(paths: List[str] = typer.Argument(...)):
         raise typer.Exit(cmd_validate(paths))
 
@@ -121,12 +135,15 @@ def main() -> int:
         return 0
     argv = sys.argv[1:]
     if not argv:
-        print("usage: cli.py train|benchmark|validate|info ...", file=sys.stderr)
+        print("usage: cli.py train|benchmark|validate|plan|info ...", file=sys.stderr)
         return 2
     if argv[0] == "validate":
         return cmd_validate(argv[1:])
     if argv[0] == "info":
         return cmd_info()
+    if argv[0] == "plan":
+        return cmd_plan(argv[argv.index("--config") + 1],
+                        int(argv[argv.index("--world") + 1]) if "--world" in argv else None)
     if argv[0] == "benchmark":
         return cmd_benchmark("--cuda" in argv)
     if argv[0] == "train":

@@ -51,3 +51,31 @@ def test_accountant_history_and_window():
     assert acc.running_mfu == pytest.approx(sum(h.mfu for h in acc.history) / 5)
     assert "tok/s" in acc.summary_str() and not acc.is_above_target()
     assert MFUAccountant(1.0).summary_str() == "MFU: no data"
+
+
+def test_memory_plan_matches_the_model_arithmetic_and_a_measured_peak():
+    """Parameter totals of the two full-size configurations (6.92 B and 46.7 B) and the one-GPU plan of the
+    OLMoE-shaped model against the peak allocation measured on a B200 (154.7 GB at micro-batch 4)."""
+    from pathlib import Path
+
+    from composed_mixture_of_experts_engine_b200.utils.config import MoEConfig
+    from composed_mixture_of_experts_engine_b200.utils.memory import format_plan, parameter_counts, plan_memory
+
+    configs = Path(__file__).resolve().parent.parent / "configs"
+    olmoe = MoEConfig.from_yaml(configs / "olmoe_1b7b.yaml")
+    mixtral = MoEConfig.from_yaml(configs / "mixtral_8x7b.yaml")
+    assert parameter_counts(olmoe)["total"] / 1e9 == pytest.approx(6.92, abs=0.01)
+    assert parameter_counts(olmoe)["active_per_token"] / 1e9 == pytest.approx(1.18, abs=0.01)
+    assert parameter_counts(mixtral)["total"] / 1e9 == pytest.approx(46.7, abs=0.05)
+    d = olmoe.to_dict()
+    d["parallelism"].update(data_parallel=1, expert_parallel=1)
+    one = plan_memory(MoEConfig.from_dict(d), 1)
+    assert one["total_gb"] == pytest.approx(154.7, rel=0.05) and one["fits"]
+    eight = plan_memory(olmoe, 8)
+    assert eight["total_gb"] < one["total_gb"] / 2 and eight["ep_buffers_gb"] > 0
+    plan = plan_memory(mixtral, 8)
+    assert plan["fits"] and plan["params_local_b"] == pytest.approx(46.7 / 8, rel=0.05)
+    assert "fits" in format_plan(plan)
+    d = mixtral.to_dict()
+    d["parallelism"].update(data_parallel=1, expert_parallel=1, tensor_parallel=1, pipeline_parallel=1)
+    assert not plan_memory(MoEConfig.from_dict(d), 1)["fits"]
