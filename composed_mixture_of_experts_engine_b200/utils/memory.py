@@ -14,7 +14,7 @@ block (sequence parallelism divides the norm / residual region by ``tp``).  The 
 from __future__ import annotations
 
 import math
-from typing import Dict, Optional
+from typing import Dict, Optional, Tuple
 
 from .config import MoEConfig
 
@@ -29,8 +29,7 @@ def _attention_dims(cfg: MoEConfig):
     m = cfg.model
     if m.arch != "moe_decoder":
         return 0, 0, 0
-    heads = m.num_heads or max(1, m.hidden_dim // 128)
-    return heads, (m.num_kv_heads or heads), (m.head_dim or m.hidden_dim // heads)
+    return m.resolved_num_heads, m.resolved_num_kv_heads, m.resolved_head_dim
 
 
 def parameter_counts(cfg: MoEConfig) -> Dict[str, int]:
@@ -51,12 +50,19 @@ def parameter_counts(cfg: MoEConfig) -> Dict[str, int]:
             "active_per_token": dense - V * H + L * m.top_k * 3 * H * F}
 
 
-def plan_memory(cfg: MoEConfig, world: Optional[int] = None, ep_buffer_factor: float = 1.5) -> Dict[str, float]:
-    """Gigabytes per GPU by category for ``cfg`` on ``world`` ranks (default: the configured world size)."""
+def plan_memory(cfg: MoEConfig, world: Optional[int] = None, ep_buffer_factor: float = 1.5,
+                mesh: Optional[Tuple[int, int, int, int, bool]] = None) -> Dict[str, float]:
+    """Gigabytes per GPU by category for ``cfg`` on ``world`` ranks (default: the configured world size).
+    ``mesh`` = (dp, ep, tp, pp, ep_from_dp) overrides the configured degrees (the trainer refits them to the
+    number of ranks it was started with)."""
     par, m, t = cfg.parallelism, cfg.model, cfg.training
-    dp, ep, tp, pp = par.data_parallel, par.expert_parallel, par.tensor_parallel, par.pipeline_parallel
-    ep_from_dp = bool(getattr(par, "ep_from_dp", False))
-    world = world or par.world_size
+    if mesh is not None:
+        dp, ep, tp, pp, ep_from_dp = mesh
+        world = world or (dp * tp * pp if ep_from_dp else dp * ep * tp * pp)
+    else:
+        dp, ep, tp, pp = par.data_parallel, par.expert_parallel, par.tensor_parallel, par.pipeline_parallel
+        ep_from_dp = bool(par.ep_from_dp)
+        world = world or par.world_size
     counts = parameter_counts(cfg)
     # what one rank holds
     dense_local = counts["dense"] / (tp * pp)

@@ -129,6 +129,14 @@ def main(argv=None) -> int:
         wandb_init_kwargs={"project": args.wandb_project} if args.wandb_project else None)
     logger.log_config(cfg.to_dict())
 
+    if rank == 0:
+        from composed_mixture_of_experts_engine_b200.utils.memory import format_plan, plan_memory
+
+        plan = plan_memory(cfg, topo.world_size, mesh=(topo.dp_size, topo.ep_size, topo.tp_size, topo.pp_size,
+                                                       topo.ep_from_dp))
+        on_gpu = topo.device.type == "cuda"
+        (log.warning if on_gpu and not plan["fits"] else log.info)("memory plan per GPU\n%s", format_plan(plan))
+
     is_decoder = m.arch == "moe_decoder"
     if is_decoder:
         flops_per_token = exact_train_flops_per_token(m.hidden_dim, m.num_layers, m.ffn_dim, m.num_experts, m.top_k,
