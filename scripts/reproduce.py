@@ -3,9 +3,11 @@
     python scripts/reproduce.py [--gpu]
 
 CPU claims: token conservation (0 violations in 100 seeds), router agreement with the fp64 oracle
-(atol = rtol = 1e-5), checkpoint round trip (bit exact), CPU smoke training (finite, decreasing loss).
-``--gpu`` adds: fused router agreement with the oracle on bf16 inputs and the kernel timings of
-``benchmarks/kernel_cases.py`` against the measured roofline (printed, not asserted).
+(atol = rtol = 1e-5), checkpoint round trip (bit exact), CPU smoke training (finite, decreasing loss), every shipped
+configuration validates, the memory plan against the model arithmetic and a measured peak, the loss curve next to
+the unmodified reference's.  ``--gpu`` adds: fused router agreement with the oracle on bf16 inputs, the attention
+kernels' timings against the recorded ones, and the kernel timings of ``benchmarks/kernel_cases.py`` against the
+measured roofline (printed, not asserted).
 """
 
 from __future__ import annotations
@@ -84,6 +86,56 @@ def smoke_training():
     return out.returncode == 0 and len(losses) == 5 and all(l == l for l in losses), {"losses": losses}
 
 
+@claim("every shipped configuration validates; top_k > num_experts is rejected with the field path")
+def config_validation():
+    from composed_mixture_of_experts_engine_b200.utils.config import ConfigValidationError, MoEConfig
+
+    names = sorted(p.name for p in (ROOT / "configs").glob("*.yaml"))
+    for n in names:
+        MoEConfig.from_yaml(ROOT / "configs" / n)
+    try:
+        MoEConfig.from_dict({"model": {"top_k": 8, "num_experts": 4}})
+    except ConfigValidationError as exc:
+        return "top_k" in str(exc), {"configs": names}
+    return False, {"reason": "invalid config was accepted"}
+
+
+@claim("memory plan: 6.92 B / 46.7 B parameters; one-GPU plan of the headline model within 5 % of the measured 154.7 GB")
+def memory_plan():
+    from composed_mixture_of_experts_engine_b200.utils.config import MoEConfig
+    from composed_mixture_of_experts_engine_b200.utils.memory import parameter_counts, plan_memory
+
+    olmoe = MoEConfig.from_yaml(ROOT / "configs" / "olmoe_1b7b.yaml")
+    mixtral = MoEConfig.from_yaml(ROOT / "configs" / "mixtral_8x7b.yaml")
+    d = olmoe.to_dict()
+    d["parallelism"].update(data_parallel=1, expert_parallel=1)
+    one = plan_memory(MoEConfig.from_dict(d), 1)["total_gb"]
+    detail = {"olmoe_b": parameter_counts(olmoe)["total"] / 1e9, "mixtral_b": parameter_counts(mixtral)["total"] / 1e9,
+              "one_gpu_gb": one, "mixtral_8gpu_gb": plan_memory(mixtral, 8)["total_gb"]}
+    ok = abs(detail["olmoe_b"] - 6.92) < 0.01 and abs(detail["mixtral_b"] - 46.7) < 0.05 and abs(one / 154.7 - 1) < 0.05
+    return ok and plan_memory(mixtral, 8)["fits"], detail
+
+
+@claim("loss curve next to the unmodified reference's: both fall, largest gap below 0.5 over 60 steps")
+def loss_parity():
+    if not (ROOT / "baseline" / "_ref" / "pkg").is_dir():
+        return True, {"skipped": "baseline/_ref is not installed"}
+    out = subprocess.run([sys.executable, str(ROOT / "benchmarks" / "loss_parity.py"), "--steps", "60"],
+                         capture_output=True, text=True, timeout=900, cwd=str(ROOT))
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    fell = all(last < first - 0.5 for first, last in zip(line["first_loss"], line["last_loss"]))
+    return out.returncode == 0 and fell and line["max_abs_diff"] < 0.5, line
+
+
+@claim("hand-written attention: numerics within bf16 tolerance of the library path; forward <= 0.65 ms, backward <= "
+       "1.8 ms at B4 S4096 16 heads hd128 (1.5 x the recorded 0.426 / 1.19 ms)")
+def gpu_attention():
+    out = subprocess.run([sys.executable, str(ROOT / "benchmarks" / "attention_bench.py")], capture_output=True,
+                         text=True, timeout=600, cwd=str(ROOT))
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    return out.returncode == 0 and line["fwd_ms"] <= 0.65 and line["bwd_ms"] <= 1.8, line
+
+
 @claim("fused sm_100a router agrees with the oracle on bf16 inputs (>= 99.5% identical rows)")
 def gpu_router():
     from composed_mixture_of_experts_engine_b200.ops.moe_router import _reference_route_fp64, moe_topk_route
@@ -100,9 +152,10 @@ def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpu", action="store_true")
     args = ap.parse_args()
-    checks = [conservation, router_numerics, checkpoint_round_trip, smoke_training]
+    checks = [conservation, router_numerics, checkpoint_round_trip, smoke_training, config_validation, memory_plan,
+              loss_parity]
     if args.gpu:
-        checks.append(gpu_router)
+        checks += [gpu_router, gpu_attention]
     failed = 0
     for fn in checks:
         try:
