@@ -146,3 +146,63 @@ def test_lazy_rescale_schedule_is_exact_and_rescales_rarely():
     tiles_after_first = sum(qt for qt in range(S // BLK))
     assert rescales < tiles_after_first // 2
 
+
+
+class _FakeExt:
+    """PyTorch stand-in for the extension's attention entry points (same argument lists), so that the autograd glue
+    around them can be checked without a GPU."""
+
+    @staticmethod
+    def _split(qkv, nh, nkv):
+        return qkv[:, :, :nh], qkv[:, :, nh: nh + nkv], qkv[:, :, nh + nkv:]
+
+    def attention_fwd(self, qkv, nh, nkv, out, lse, status, timeout_ns):
+        q, k, v = self._split(qkv.double(), nh, nkv)
+        S, hd = q.shape[1], q.shape[3]
+        kk = k.repeat_interleave(nh // nkv, 2)
+        vv = v.repeat_interleave(nh // nkv, 2)
+        scores = torch.einsum("bqhd,bkhd->bhqk", q, kk) / math.sqrt(hd)
+        mask = torch.ones(S, S, dtype=torch.bool).tril()
+        scores = scores.masked_fill(~mask, float("-inf"))
+        out.copy_(torch.einsum("bhqk,bkhd->bqhd", torch.softmax(scores, -1), vv).to(out.dtype))
+        lse.copy_(torch.logsumexp(scores, -1).to(lse.dtype))
+
+    def attention_bwd(self, qkv, nh, nkv, out, dout, lse, delta, dq, dk, dv, status, timeout_ns):
+        with torch.enable_grad():  # called from inside an autograd backward, where recording is off
+            x = qkv.double().requires_grad_()
+            q, k, v = self._split(x, nh, nkv)
+            S, hd = q.shape[1], q.shape[3]
+            scores = torch.einsum("bqhd,bkhd->bhqk", q, k.repeat_interleave(nh // nkv, 2)) / math.sqrt(hd)
+            scores = scores.masked_fill(~torch.ones(S, S, dtype=torch.bool).tril(), float("-inf"))
+            o = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(scores, -1), v.repeat_interleave(nh // nkv, 2))
+            (g,) = torch.autograd.grad(o, x, dout.double())
+        gq, gk, gv = self._split(g, nh, nkv)
+        assert float(dq.abs().max()) == 0.0  # the kernel accumulates into dq: the caller must hand in zeros
+        dq.add_(gq.to(dq.dtype))
+        dk.copy_(gk.to(dk.dtype))
+        dv.copy_(gv.to(dv.dtype))
+
+
+def test_packed_attention_autograd_glue_with_a_stand_in_extension(monkeypatch):
+    """``attention_sm100._PackedAttentionFn`` (allocation of out / lse / dq / dk / dv, zeroed dq, packing of the
+    three gradients along the head axis) against plain autograd, with the kernels replaced by PyTorch."""
+    from composed_mixture_of_experts_engine_b200.ops import _ext, attention_sm100 as A
+    from composed_mixture_of_experts_engine_b200.ops import kernels
+    from composed_mixture_of_experts_engine_b200.ops.attention import attention_reference
+
+    monkeypatch.setattr(_ext, "ext", lambda: _FakeExt())
+    monkeypatch.setattr(kernels, "status_word", lambda device: torch.zeros(1, dtype=torch.int32))
+    torch.manual_seed(0)
+    B, S, nh, nkv, hd = 2, 128, 4, 2, 64
+    qkv = torch.randn(B, S, nh + 2 * nkv, hd, dtype=torch.bfloat16).float().requires_grad_()
+    go = torch.randn(B, S, nh, hd)
+
+    x = qkv.detach().to(torch.bfloat16).requires_grad_()
+    out = A.packed_causal_attention(x, nh, nkv)
+    out.backward(go.to(torch.bfloat16))
+
+    ref = attention_reference(qkv[:, :, :nh], qkv[:, :, nh: nh + nkv], qkv[:, :, nh + nkv:])
+    ref.backward(go)
+    assert out.shape == (B, S, nh, hd) and x.grad.shape == qkv.shape
+    assert (out.float() - ref).abs().max() < 3e-2
+    assert (x.grad.float() - qkv.grad).norm() / qkv.grad.norm() < 2e-2
