@@ -51,6 +51,9 @@ def parse_args():
     ap.add_argument("--config", default=str(ROOT / "configs" / "olmoe_1b7b.yaml"))
     ap.add_argument("--micro-batch", type=int, default=MICRO_BATCH)
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
+    ap.add_argument("--keep-mesh", action="store_true",
+                    help="keep the configuration's own dp / ep / tp / pp mesh (its world size must equal the number "
+                         "of ranks) instead of dp = ep = N; for configurations other than the headline one")
     ap.add_argument("--tiny", action="store_true",
                     help="self-test of the reference arm with toy dimensions (runs on CPU too); never a bench value")
     return ap.parse_args()
@@ -180,14 +183,22 @@ def run_ours(args) -> dict:
     cfg = MoEConfig.from_yaml(args.config)
     d = cfg.to_dict()
     accum = max(1, args.seqs_per_gpu // args.micro_batch)
-    d["parallelism"].update(data_parallel=n, expert_parallel=n, tensor_parallel=1, pipeline_parallel=1, ep_from_dp=True)
+    if args.keep_mesh:
+        if cfg.parallelism.world_size != n:
+            raise SystemExit(f"--keep-mesh: {args.config} describes {cfg.parallelism.world_size} ranks, started {n}")
+        replicas = cfg.parallelism.data_parallel
+    else:
+        d["parallelism"].update(data_parallel=n, expert_parallel=n, tensor_parallel=1, pipeline_parallel=1,
+                                ep_from_dp=True)
+        replicas = n
     d["training"].update(micro_batch_size=args.micro_batch, gradient_accumulation_steps=accum,
-                         global_batch_size=args.micro_batch * accum * n, warmup_steps=0, max_steps=10_000)
+                         global_batch_size=args.micro_batch * accum * replicas, warmup_steps=0, max_steps=10_000)
     cfg = MoEConfig.from_dict(d)
     trainer = Trainer(cfg)
     dev = trainer.device
     m = cfg.model
-    gen = torch.Generator().manual_seed(1234 + rank)
+    # ranks of one data-parallel replica (tensor / pipeline peers) see the same sequences
+    gen = torch.Generator().manual_seed(1234 + (trainer.topology.dp_rank if args.keep_mesh else rank))
     n_batches = 2
     host = [trainer.synthetic_batch(gen, pinned=True) for _ in range(n_batches)]
     resident = [(a.to(dev), b.to(dev)) for a, b in host]
@@ -217,7 +228,7 @@ def run_ours(args) -> dict:
 
     check_status(dev)
 
-    tokens_step = trainer.tokens_per_step_per_rank * n
+    tokens_step = trainer.tokens_per_step_global if args.keep_mesh else trainer.tokens_per_step_per_rank * n
     per_step_ms = ms_dev / args.steps
     value = tokens_step / (per_step_ms / 1e3)
     e2e_value = tokens_step / (ms_e2e / args.steps / 1e3)
@@ -242,13 +253,19 @@ def run_ours(args) -> dict:
         "data": "synthetic uniform-random token ids; random-init weights N(0,0.02)",
         "impl": "ours",
         "config": {
-            "model": "OLMoE-1B-7B-shaped (V50304 d2048 L16 h16 S4096 E64 F1024 top8, aux 0.01)",
-            "global_batch": args.micro_batch * accum * n,
+            "model": ("OLMoE-1B-7B-shaped (V50304 d2048 L16 h16 S4096 E64 F1024 top8, aux 0.01)"
+                      if Path(args.config).name == "olmoe_1b7b.yaml" else
+                      f"{Path(args.config).stem} (V{m.vocab_size} d{m.hidden_dim} L{m.num_layers} "
+                      f"h{m.resolved_num_heads}/{m.resolved_num_kv_heads} S{m.sequence_length} E{m.num_experts} "
+                      f"F{m.ffn_dim} top{m.top_k})"),
+            "global_batch": args.micro_batch * accum * replicas,
             "global_batch_tokens": tokens_step,
             "seq_len": m.sequence_length,
             "micro_batch": args.micro_batch,
             "grad_accum": accum,
-            "parallelism": f"dp{n} x ep{n} (ep carved from dp), sharded optimizer state",
+            "parallelism": (f"dp{n} x ep{n} (ep carved from dp), sharded optimizer state" if not args.keep_mesh else
+                            f"dp{cfg.parallelism.data_parallel} x ep{cfg.parallelism.expert_parallel} x "
+                            f"tp{cfg.parallelism.tensor_parallel} x pp{cfg.parallelism.pipeline_parallel}"),
             "optimizer": "AdamW fp32 master + moments, global-norm clip 1.0",
             "attention": ("hand-written tcgen05 kernels (CMOE_ATTN_SM100=1)"
                           if os.environ.get("CMOE_ATTN_SM100", "0") == "1" else "library (cuDNN fused attention)"),
