@@ -105,3 +105,15 @@ def test_gqa_validation():
     assert cfg.model.resolved_head_dim == 128 and cfg.model.resolved_num_kv_heads == 8
     with pytest.raises(ConfigValidationError):
         MoEConfig.from_dict({"model": dict(hidden_dim=4096, num_heads=32, num_kv_heads=5)})
+
+
+def test_cli_plan_reports_fit_and_misfit(capsys):
+    """``cli.py plan``: exit status 0 with the per-GPU table for a configuration that fits a B200, 1 for one that
+    does not (the reference's default dimensions on dp8 x ep8)."""
+    from scripts import cli
+
+    assert cli.cmd_plan(str(CONFIGS / "mixtral_8x7b.yaml")) == 0
+    out = capsys.readouterr().out
+    assert "dp2 x ep2 x tp2 x pp2" in out and "fits" in out
+    assert cli.cmd_plan(str(CONFIGS / "default.yaml")) == 1
+    assert "DOES NOT FIT" in capsys.readouterr().out
