@@ -206,3 +206,40 @@ def test_packed_attention_autograd_glue_with_a_stand_in_extension(monkeypatch):
     assert out.shape == (B, S, nh, hd) and x.grad.shape == qkv.shape
     assert (out.float() - ref).abs().max() < 3e-2
     assert (x.grad.float() - qkv.grad).norm() / qkv.grad.norm() < 2e-2
+
+
+# ---- shared-memory operand layout ------------------------------------------------------------------------------
+def _swizzle128(byte_offset: int) -> int:
+    """128-byte swizzle of a 1024-byte-aligned block: bits 4-6 of the offset are XORed with bits 7-9."""
+    return byte_offset ^ (((byte_offset >> 7) & 7) << 4)
+
+
+def _store_swizzled(mat: dict, r: int, col: int, value) -> None:
+    """Where ``store_swizzled_32`` of csrc/attention.cu puts element (r, col) of a [128 x 128] bf16 matrix: two
+    blocks of [128 rows x 64 columns], 16-byte piece j of a row at piece j ^ (r % 8)."""
+    block, c = divmod(col, 64)
+    piece, within = divmod(c, 8)
+    mat[block * 128 * 128 + r * 128 + ((piece ^ (r & 7)) << 4) + within * 2] = value
+
+
+def test_probability_tile_serves_as_k_major_and_as_mn_major_operand():
+    """The P / dS tile is written once and read twice by the tensor cores: as a K-major A operand (rows = queries,
+    contraction over keys: P V, dS K) and as an MN-major A operand (M = keys, contraction over queries: P^T dO,
+    dS^T Q).  Both canonical 128-byte-swizzle layouts must address the byte the store put there: K-major rows are
+    128 bytes apart with eight-row groups 1024 bytes apart; MN-major k-rows are 128 bytes apart, 64-element M
+    chunks one block (16 KiB) apart."""
+    mem = {}
+    for r in range(128):
+        for c in range(128):
+            _store_swizzled(mem, r, c, (r, c))
+    block_bytes = 128 * 128
+    for r in range(0, 128, 7):
+        for c in range(0, 128, 5):
+            # K-major: element (m = r, k = c) of the 64-wide K block c // 64
+            off = (c // 64) * block_bytes + _swizzle128((r // 8) * 1024 + (r % 8) * 128 + (c % 64) * 2)
+            assert mem[off] == (r, c)
+            # MN-major: element (m = c, k = r): chunk c // 64 at LBO = one block, k-row r at 128 bytes
+            off = (c // 64) * block_bytes + _swizzle128((r // 8) * 1024 + (r % 8) * 128 + (c % 64) * 2)
+            assert mem[off] == (r, c)
+    # every byte pair written exactly once
+    assert len(mem) == 128 * 128
