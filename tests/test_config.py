@@ -117,3 +117,46 @@ def test_cli_plan_reports_fit_and_misfit(capsys):
     assert "dp2 x ep2 x tp2 x pp2" in out and "fits" in out
     assert cli.cmd_plan(str(CONFIGS / "default.yaml")) == 1
     assert "DOES NOT FIT" in capsys.readouterr().out
+
+
+def test_lr_schedule_and_parallelism_refit():
+    """``lr_at``: linear warm-up, cosine decay to 10 % (reference train.py:108-113).  ``fit_parallelism``: a
+    configured mesh that matches the world is kept, otherwise data parallelism (then expert parallelism) shrinks to
+    what the started ranks allow, like the reference's train.py:173-186."""
+    import math
+
+    from composed_mixture_of_experts_engine_b200.engine import fit_parallelism, lr_at
+
+    assert lr_at(0, 1.0, 10, 100) == pytest.approx(0.1) and lr_at(9, 1.0, 10, 100) == pytest.approx(1.0)
+    assert lr_at(10, 1.0, 10, 100) == pytest.approx(1.0)
+    assert lr_at(55, 1.0, 10, 100) == pytest.approx(0.1 + 0.9 * 0.5 * (1 + math.cos(math.pi * 0.5)))
+    assert lr_at(100, 1.0, 10, 100) == pytest.approx(0.1) and lr_at(10_000, 1.0, 10, 100) == pytest.approx(0.1)
+    assert lr_at(5, 2.0, 0, 10) == pytest.approx(2.0 * (0.1 + 0.9 * 0.5 * (1 + math.cos(math.pi * 0.5))))
+
+    def cfg(**par):
+        return MoEConfig.from_dict({"model": {"num_experts": 8}, "parallelism": par})
+
+    mixtral = cfg(data_parallel=2, expert_parallel=2, tensor_parallel=2, pipeline_parallel=2, ep_from_dp=True)
+    assert fit_parallelism(mixtral, 8) == (2, 2, 2, 2, True)
+    assert fit_parallelism(mixtral, 1) == (1, 1, 1, 1, True)
+    assert fit_parallelism(mixtral, 4) == (1, 1, 2, 2, True)          # tp x pp kept, one replica left
+    olmoe = cfg(data_parallel=8, expert_parallel=8, ep_from_dp=True)
+    assert fit_parallelism(olmoe, 4) == (4, 4, 1, 1, True) and fit_parallelism(olmoe, 2) == (2, 2, 1, 1, True)
+    assert fit_parallelism(olmoe, 6) == (6, 2, 1, 1, True)            # ep must divide dp and the expert count
+    classic = cfg(data_parallel=2, expert_parallel=4)
+    assert fit_parallelism(classic, 8) == (2, 4, 1, 1, False)
+    assert fit_parallelism(classic, 4) == (1, 4, 1, 1, False) and fit_parallelism(classic, 2) == (1, 2, 1, 1, False)
+
+
+def test_mark_expert_params_tags_only_the_stacked_expert_weights():
+    from composed_mixture_of_experts_engine_b200.models import build_model
+    from composed_mixture_of_experts_engine_b200.parallel import build_topology
+    from composed_mixture_of_experts_engine_b200.parallel.data_parallel import apply_fsdp2, mark_expert_params
+
+    c = MoEConfig.from_yaml(CONFIGS / "smoke.yaml")
+    topo = build_topology(dp_size=1, ep_size=1, device_type="cpu")
+    model = build_model(c, topo)
+    assert mark_expert_params(model) == 2 * c.model.num_layers
+    tagged = {n for n, p in model.named_parameters() if getattr(p, "is_expert_param", False)}
+    assert tagged == {f"blocks.{i}.moe.{w}" for i in range(c.model.num_layers) for w in ("w13", "w2")}
+    assert apply_fsdp2(model, topo) is model  # dp == 1: nothing else to set up
