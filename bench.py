@@ -269,6 +269,8 @@ def run_ours(args) -> dict:
             "optimizer": "AdamW fp32 master + moments, global-norm clip 1.0",
             "attention": ("hand-written tcgen05 kernels (CMOE_ATTN_SM100=1)"
                           if os.environ.get("CMOE_ATTN_SM100", "0") == "1" else "library (cuDNN fused attention)"),
+            "dense_gemms": "hand-written two-SM tcgen05 GEMM (attention projections, LM head: forward, input and "
+                           "weight gradients)",
             "l2": "no explicit flush: every microbatch streams 13.8 GB of bf16 weights and >1 GB of activations "
                   "per layer, far larger than the 126 MB L2",
         },

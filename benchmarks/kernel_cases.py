@@ -7,7 +7,7 @@ launches with CUDA events (an L2-sized buffer is overwritten between launches) a
 achieved bandwidth / throughput and the fraction of the measured peaks (MEASURED_PEAKS.json).  The same command
 line under ``ncu -k regex:<kernel> -c 1`` captures one launch of the case.
 
-Cases: adamw, rmsnorm, router (config-2 shape: T16384 d4096 E64 top2), gemm_dense, grouped_fwd1, grouped_fwd2,
+Cases: adamw, rmsnorm, router (config-2 shape: T16384 d4096 E64 top2), gemm_dense, dense_shapes, grouped_fwd1, grouped_fwd2,
 grouped_dgrad, grouped_wgrad, gather, combine.
 """
 
@@ -115,6 +115,29 @@ def main():
         fl = 2 * M * N * K
         out.update(ms=ms, tflops=fl / ms / 1e9, frac_of_peak=fl / ms / 1e9 / tflops_peak, cublas_ms=lib,
                    cublas_tflops=fl / lib / 1e9)
+    elif args.case == "dense_shapes":
+        # the projections and the LM head of the headline model: forward, input gradient, weight gradient
+        # (rows, in features, out features); each against torch.matmul (cuBLAS) on the same operands
+        rows_out = []
+        for (M, K, N) in ((16384, 2048, 6144), (16384, 2048, 2048), (4096, 2048, 50304)):
+            x = torch.randn(M, K, device=dev, dtype=bf)
+            w = (torch.randn(N, K, device=dev) * 0.02).to(bf)
+            dy = torch.randn(M, N, device=dev, dtype=bf)
+            y = torch.empty(M, N, device=dev, dtype=bf)
+            dx = torch.empty(M, K, device=dev, dtype=bf)
+            dw = torch.zeros(N, K, device=dev, dtype=torch.float32)
+            dw16 = torch.empty(N, K, device=dev, dtype=bf)
+            fl = 2 * M * N * K
+            for name, own, lib in (
+                    ("fwd", lambda: kernels.linear_nt(x, w, out=y), lambda: torch.matmul(x, w.t(), out=y)),
+                    ("dgrad", lambda: kernels.linear_nn(dy, w, out=dx), lambda: torch.matmul(dy, w, out=dx)),
+                    ("wgrad", lambda: kernels.linear_tn_acc(dy, x, dw), lambda: torch.matmul(dy.t(), x, out=dw16))):
+                a, b = time_launches(own, args.iters), time_launches(lib, args.iters)
+                rows_out.append({"shape": [M, K, N], "op": name, "ms": round(a, 4), "tflops": round(fl / a / 1e9, 1),
+                                 "cublas_ms": round(b, 4), "cublas_tflops": round(fl / b / 1e9, 1),
+                                 "of_cublas": round(b / a, 3), "frac_of_peak": round(fl / a / 1e9 / tflops_peak, 3)})
+            del x, w, dy, y, dx, dw, dw16
+        out.update(cases=rows_out)
     elif args.case.startswith("grouped_") or args.case in ("gather", "combine"):
         E, H, F = 64, 2048, 1024
         R = args.rows // shrink

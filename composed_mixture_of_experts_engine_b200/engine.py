@@ -173,7 +173,7 @@ class Trainer:
 
     @property
     def tokens_per_step_global(self) -> int:
-        return self.tokens_per_step_per_rank * self.topology.dp_size
+        return self.tokens_per_step_per_rank * self.topology.data_replicas
 
     def synthetic_batch(self, generator: Optional[torch.Generator] = None, pinned: bool = True
                         ) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -239,23 +239,25 @@ class Trainer:
         return total
 
     def _reduce_grads_library(self) -> None:
-        """Average gradients over the data-parallel replicas (CPU / fp32 path with a stock optimizer)."""
+        """Average gradients over the ranks that saw different data (CPU / fp32 path with a stock optimizer):
+        dense parameters over the dense-replica group (data-parallel ranks, and expert-parallel ranks too when
+        expert parallelism is a mesh axis of its own), expert parameters over the replicas of the same experts;
+        an expert's gradient already sums the tokens its expert-parallel group sent it."""
         topo = self.topology
-        if not dist.is_initialized() or topo.dp_size == 1:
+        if not dist.is_initialized() or topo.data_replicas == 1:
             return
-        from .parallel.mesh import dp_process_group, edp_process_group
+        from .parallel.mesh import ddp_process_group, edp_process_group
 
-        dp_group, edp_group = dp_process_group(topo), edp_process_group(topo)
+        ddp_group, edp_group = ddp_process_group(topo), edp_process_group(topo)
         for p in self.model.parameters():
             if p.grad is None:
                 continue
             if getattr(p, "is_expert_param", False):
                 if edp_group is not None:
                     dist.all_reduce(p.grad, group=edp_group)
-                p.grad.div_(topo.dp_size)
-            elif dp_group is not None:
-                dist.all_reduce(p.grad, group=dp_group)
-                p.grad.div_(topo.dp_size)
+            elif ddp_group is not None:
+                dist.all_reduce(p.grad, group=ddp_group)
+            p.grad.div_(topo.data_replicas)
 
     def _clip_grads_library(self, max_norm: float) -> None:
         """Global-norm clipping where every rank arrives at the same norm: replicated parameters count once,

@@ -96,37 +96,53 @@ class DecoderBlock(nn.Module):
 
 
 class _LMHeadLossFn(torch.autograd.Function):
-    """sum-CE(h @ W^T, targets) * scale without keeping the logits: forward and gradients chunk by chunk."""
+    """sum-CE(h @ W^T, targets) * scale without keeping the logits: per chunk of rows one tcgen05 GEMM for the
+    logits, the cross-entropy kernel (loss sum, logits overwritten by their gradient), and - only when a gradient
+    will be asked for - the two gradient GEMMs (``dh`` with W read N-major, ``dW`` added into an fp32 buffer by the
+    TMA reduce-add epilogue).  ``backward`` scales both by the incoming gradient; ``dW`` goes to ``W.main_grad``
+    when the optimizer gave the weight one."""
 
     @staticmethod
     def forward(ctx, h, weight, targets, scale, chunk):
-        from ..ops import _ext
+        from ..ops import _ext, kernels
 
         ext = _ext.ext()
         N = h.shape[0]
+        need_dh, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         loss = torch.zeros(1, device=h.device, dtype=torch.float32)
-        dh = torch.empty_like(h)
-        dw = torch.zeros_like(weight)
+        dh = torch.empty_like(h) if need_dh else None
+        dw = torch.empty(weight.shape, device=h.device, dtype=torch.float32) if need_dw else None
         for a in range(0, N, chunk):
             b = min(a + chunk, N)
-            logits = h[a:b] @ weight.t()
+            logits = kernels.linear_nt(h[a:b], weight)
             ext.cross_entropy(logits, targets[a:b], loss, scale)  # logits now hold d(loss)/d(logits)
-            torch.mm(logits, weight, out=dh[a:b])
-            dw.addmm_(logits.t(), h[a:b])
-        ctx.save_for_backward(dh, dw)
+            if need_dh:
+                kernels.linear_nn(logits, weight, out=dh[a:b])
+            if need_dw:
+                kernels.linear_tn_acc(logits, h[a:b], dw, accumulate=a > 0)
+        ctx.save_for_backward(dh, dw, weight)
         return loss[0] * scale
 
     @staticmethod
     def backward(ctx, g):
-        dh, dw = ctx.saved_tensors
-        return dh * g.to(dh.dtype), dw * g.to(dw.dtype), None, None, None
+        dh, dw, weight = ctx.saved_tensors
+        if dh is not None:
+            dh = dh * g.to(dh.dtype)
+        if dw is not None:
+            main = getattr(weight, "main_grad", None)
+            if main is not None:
+                main.addcmul_(dw, g.to(torch.float32))
+                dw = None
+            else:
+                dw = (dw * g.to(torch.float32)).to(weight.dtype)
+        return dh, dw, None, None, None
 
 
 def lm_head_loss(h: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor, scale: float, chunk: int = 4096
                  ) -> torch.Tensor:
     """``scale * sum_t CE(h_t @ W^T, target_t)``; h [N, H], weight [V, H], targets [N] (negative = ignored)."""
-    if OF.on_device_path(h, weight) and weight.shape[0] % 8 == 0:
-        return _LMHeadLossFn.apply(h.contiguous(), weight, targets.contiguous(), scale, chunk)
+    if OF.linear_supported(h, weight):
+        return _LMHeadLossFn.apply(OF.rows_for_tma(h), weight, targets.contiguous(), scale, chunk)
     logits = F.linear(h, weight).float()
     return F.cross_entropy(logits, targets, reduction="sum", ignore_index=-100) * scale
 
@@ -192,7 +208,7 @@ class MoEDecoder(nn.Module):
         x = self.final_hidden(x)
         if self.sequence_parallel:
             x = C.all_gather(x, 1, tp_process_group(self.topology), reduce_scatter_grad=False)
-        return self.lm_head(x)
+        return OF.linear(x, self.lm_head.weight)
 
     def loss(self, ids_or_hidden: torch.Tensor, targets: torch.Tensor, scale: Optional[float] = None
              ) -> torch.Tensor:
@@ -241,5 +257,13 @@ def finalize_sequence_parallel_grads(model: nn.Module, topology: ParallelTopolog
         return
     group = tp_process_group(topology)
     for p in model.parameters():
-        if getattr(p, "sequence_parallel_grad", False) and p.grad is not None:
+        if not getattr(p, "sequence_parallel_grad", False):
+            continue
+        main = getattr(p, "main_grad", None)
+        if main is not None:  # fused optimizer: kernel-accumulated and autograd parts meet in the fp32 buffer
+            if p.grad is not None:
+                main.add_(p.grad)
+                p.grad = None
+            dist.all_reduce(main, group=group)
+        elif p.grad is not None:
             dist.all_reduce(p.grad, group=group)

@@ -55,6 +55,62 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5) -> torch.T
     return rmsnorm_reference(x, weight, eps)
 
 
+# ------------------------------------------------------------------------------------------ dense linear
+def rows_for_tma(t: torch.Tensor) -> torch.Tensor:
+    """``t`` [rows, cols] as a contiguous tensor whose first element sits on a 16-byte boundary (what a TMA
+    tensor map needs); a copy only when the view it was given does not already qualify."""
+    if not t.is_contiguous():
+        return t.contiguous()
+    return t if t.data_ptr() % 16 == 0 else t.clone()
+
+
+class _LinearFn(torch.autograd.Function):
+    """``y = x @ W^T`` on the two-SM tcgen05 GEMM: forward K-major x K-major, input gradient with W read
+    N-major (no transposed copy), weight gradient as a contraction over the rows whose fp32 result is added into
+    ``W.main_grad`` by the kernel's TMA reduce-add epilogue when the optimizer gave the parameter one."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        K = x.shape[-1]
+        x2 = rows_for_tma(x.reshape(-1, K))
+        y = kernels.linear_nt(x2, weight)
+        ctx.save_for_backward(x2, weight)
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        N, K = weight.shape
+        dy2 = rows_for_tma(dy.reshape(-1, N))
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = kernels.linear_nn(dy2, weight).view(*dy.shape[:-1], K)
+        if ctx.needs_input_grad[1]:
+            main = getattr(weight, "main_grad", None)
+            if main is not None:
+                kernels.linear_tn_acc(dy2, x2, main)
+            else:
+                dw = kernels.linear_tn(dy2, x2).to(weight.dtype)
+        return dx, dw
+
+
+def linear_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """The tcgen05 GEMM takes this projection: CUDA bf16, feature counts that are multiples of 8 (TMA rows start
+    on 16-byte boundaries), a contiguous weight whose storage starts on a 16-byte boundary."""
+    return (on_device_path(x, weight) and weight.dim() == 2 and weight.is_contiguous()
+            and weight.shape[0] % 8 == 0 and weight.shape[1] % 8 == 0 and weight.data_ptr() % 16 == 0
+            and x.shape[-1] == weight.shape[1] and x.numel() > 0)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ weight^T (+ bias)`` with ``weight`` [out, in] (the ``nn.Linear`` contraction).  Reference counterpart:
+    the ``F.linear`` calls of pkg/distributed/tensor_parallel.py:121,197 and pkg/models/moe.py:186 (cuBLAS there)."""
+    if linear_supported(x, weight):
+        y = _LinearFn.apply(x, weight)
+        return y if bias is None else y + bias
+    return F.linear(x, weight, bias)
+
+
 # ------------------------------------------------------------------------------------------ RoPE
 def rope_tables(seq_len: int, head_dim: int, theta: float, device: torch.device) -> Tuple[torch.Tensor, torch.Tensor]:
     inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))

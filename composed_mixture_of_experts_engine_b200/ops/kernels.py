@@ -112,6 +112,22 @@ def linear_nn(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     return gemm(x, w, out, M=M, N=N, K=K, b_mn=True, accumulate=accumulate)
 
 
+_offsets_cache: Dict[Tuple[int, Tuple[int, ...]], torch.Tensor] = {}
+
+
+def _offsets_i32(device: torch.device, offs: Tuple[int, ...]) -> torch.Tensor:
+    """Device copy of a short host list of row offsets, made once per distinct list (a fresh ``torch.tensor``
+    per call would be a pageable host-to-device copy in the middle of the backward pass)."""
+    key = (device.index or 0, offs)
+    t = _offsets_cache.get(key)
+    if t is None:
+        if len(_offsets_cache) > 256:
+            _offsets_cache.clear()
+        t = torch.tensor(offs, device=device, dtype=torch.int32)
+        _offsets_cache[key] = t
+    return t
+
+
 def linear_tn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False,
               splits: int = 0) -> torch.Tensor:
     """out[M, N] (fp32) = a[R, M]^T @ b[R, N]: the weight-gradient contraction over R rows.
@@ -125,8 +141,8 @@ def linear_tn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = No
         tiles = ((M + 127) // 128) * ((N + 255) // 256)
         splits = max(1, min(R // 512 if R >= 512 else 1, (148 + tiles - 1) // tiles))
     chunk = ((R + splits - 1) // splits + 63) // 64 * 64
-    offs = [min(i * chunk, R) for i in range(splits)] + [R]
-    offs_t = torch.tensor(offs, device=a.device, dtype=torch.int32)
+    offs = tuple(min(i * chunk, R) for i in range(splits)) + (R,)
+    offs_t = _offsets_i32(a.device, offs)
     part = torch.empty(splits, M, N, device=a.device, dtype=torch.float32)
     gemm(a, b, part, mode=GEMM_GROUPED_K, M=M, N=N, a_mn=True, b_mn=True, groups=splits, group_offsets=offs_t,
          d_group_stride=M * N)
@@ -138,6 +154,16 @@ def linear_tn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = No
     else:
         out.copy_(red)
     return out
+
+
+def linear_tn_acc(a: torch.Tensor, b: torch.Tensor, acc: torch.Tensor, accumulate: bool = True) -> torch.Tensor:
+    """acc[M, N] (fp32, in place) += a[R, M]^T @ b[R, N] with the addition done by the kernel's TMA reduce-add
+    epilogue (no read-modify-write pass over ``acc`` on the SMs, no temporary); ``accumulate=False`` stores."""
+    R, M = a.shape
+    N = b.shape[1]
+    gemm(a, b, acc, mode=GEMM_GROUPED_K, M=M, N=N, a_mn=True, b_mn=True, groups=1,
+         group_offsets=_offsets_i32(a.device, (0, R)), d_group_stride=M * N, accumulate=accumulate)
+    return acc
 
 
 _overflow: Dict[int, torch.Tensor] = {}

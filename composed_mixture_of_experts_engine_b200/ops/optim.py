@@ -6,8 +6,8 @@ fp32 reduction).  Here the same mixed-precision contract (bf16 parameters in the
 moments in the optimizer) is one kernel launch per parameter group:
 
 * parameters are re-pointed into one flat bf16 buffer per group, gradients into one flat buffer
-  (bf16 for autograd-produced gradients, fp32 ``main_grad`` for the expert weights whose gradients the grouped
-  GEMM kernels accumulate directly);
+  (fp32 ``main_grad``: the GEMM kernels add the weight gradients of experts, projections and LM head into it
+  directly; what autograd leaves in ``p.grad`` - norm weights, router gates, embedding - is added at step time);
 * the global gradient norm is a device scalar (sum-of-squares kernel), so clipping needs no host round trip;
 * with data parallelism the flat gradient is reduce-scattered, the update runs on this rank's shard only, and
   the updated bf16 parameters are all-gathered (ZeRO-style sharding of master weights and moments).  Expert
@@ -94,8 +94,14 @@ class _FlatGroup:
         return segs
 
     def reassign_grads(self) -> None:
-        """Point ``p.grad`` back into the flat buffer (something set it to None or to a fresh tensor)."""
+        """Bring gradients that autograd left in ``p.grad`` into the flat buffer.  fp32 groups: added to
+        ``main_grad`` (where the GEMM kernels already accumulated the matrix gradients) and dropped; bf16 groups:
+        ``p.grad`` is pointed back at its slice of the flat buffer."""
         if self.flat_g.dtype == torch.float32:
+            for p in self.params:
+                if p.grad is not None:
+                    p.main_grad.add_(p.grad)
+                    p.grad = None
             return
         for p, off in zip(self.params, self.offsets):
             view = self.flat_g[off:off + p.numel()].view(p.shape)
@@ -220,19 +226,21 @@ def build_optimizer(model: nn.Module, lr: float, weight_decay: float = 0.1, beta
             [{"params": decay, "weight_decay": weight_decay}, {"params": no_decay, "weight_decay": 0.0}],
             lr=lr, betas=betas, eps=eps)
 
-    from ..parallel.mesh import dp_process_group, edp_process_group
+    from ..parallel.mesh import ddp_process_group, edp_process_group
 
     expert = [(n, p) for n, p in params if getattr(p, "is_expert_param", False)]
     dense = [(n, p) for n, p in params if not getattr(p, "is_expert_param", False)]
     dp_group = expert_dp_group = None
-    if topology is not None and dist.is_initialized() and topology.dp_size > 1:
-        dp_group = dp_process_group(topology)
+    if topology is not None and dist.is_initialized() and topology.world_size > 1:
+        dp_group = ddp_process_group(topology)  # None when the group has one rank
         expert_dp_group = edp_process_group(topology)
     groups: List[_FlatGroup] = []
     if dense:
-        groups.append(_FlatGroup("dense", [p for _, p in dense], torch.bfloat16,
+        # fp32 gradient buffer: the weight-gradient GEMMs of the projections and of the LM head add into it with
+        # TMA reduce-add across microbatches; vector parameters' autograd gradients are added at step time
+        groups.append(_FlatGroup("dense", [p for _, p in dense], torch.float32,
                                  [not _no_decay(n, p) for n, p in dense], shard_group=dp_group, topology=topology,
-                                 axis="dp"))
+                                 axis="ddp"))
     if expert:
         groups.append(_FlatGroup("expert", [p for _, p in expert], torch.float32, [True] * len(expert),
                                  shard_group=expert_dp_group, topology=topology, axis="edp"))

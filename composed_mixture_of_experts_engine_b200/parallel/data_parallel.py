@@ -8,7 +8,8 @@ be reduced across replicas of the same experts.  Here the model keeps whole bf16
 (they fit: 180 GB of HBM per GPU) and the *optimizer* shards the fp32 master weights and moments over the
 data-parallel group: gradients are reduce-scattered (fp32 accumulation, 1/dp scale), the update runs on the
 shard, the bf16 parameters are all-gathered (``ops/optim.py``, ``symm_dp.py``).  Dense parameters use the
-full data-parallel group, expert parameters the expert-data-parallel group (``edp``).
+dense-replica group (``ddp``: the data-parallel group, times the expert-parallel group when that is a mesh axis of
+its own), expert parameters the expert-data-parallel group (``edp``).
 
 This function marks the parameters with their reduction group, makes all replicas start from identical
 values, and optionally casts the model to the mixed-precision compute dtype.
@@ -22,7 +23,7 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
-from .mesh import ParallelTopology, dp_process_group, edp_process_group
+from .mesh import ParallelTopology, ddp_process_group, edp_process_group
 
 __all__ = ["apply_fsdp2", "mark_expert_params"]
 
@@ -45,10 +46,13 @@ def apply_fsdp2(model: nn.Module, topology: Optional[ParallelTopology],
     mark_expert_params(model)
     if mixed_precision_dtype is not None and mixed_precision_dtype != torch.float32:
         model.to(mixed_precision_dtype)
-    if topology is None or topology.dp_size == 1 or topology.mesh is None or not dist.is_initialized():
+    if (topology is None or topology.mesh is None or not dist.is_initialized()
+            or (topology.data_replicas == 1 and topology.axis_size("edp") == 1)):
         return model
-    dp_group, edp_group = dp_process_group(topology), edp_process_group(topology)
-    dp_src = topology.axis_ranks("dp")[0]
+    # dense parameters are replicated over every rank that draws its own data: the data-parallel group, and the
+    # expert-parallel group too when it is a mesh axis of its own (its ranks exchange tokens, not dense weights)
+    dp_group, edp_group = ddp_process_group(topology), edp_process_group(topology)
+    dp_src = topology.axis_ranks("ddp")[0]
     edp_src = topology.axis_ranks("edp")[0]
     with torch.no_grad():
         for p in model.parameters():

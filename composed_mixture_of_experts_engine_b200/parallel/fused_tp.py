@@ -16,8 +16,8 @@ These replace the reference's gather / all-reduce call sites C4-C7 (pkg/distribu
 from __future__ import annotations
 
 import torch
-import torch.nn.functional as F
 
+from ..ops import functional as OF
 from . import collectives as C
 from .mesh import ParallelTopology, tp_process_group
 
@@ -36,7 +36,7 @@ def allgather_linear(x: torch.Tensor, w: torch.Tensor, topo: ParallelTopology, s
         from . import symm_tp
 
         return symm_tp.allgather_linear(x, w, topo, seq_dim)
-    return F.linear(C.all_gather(x, seq_dim, group, reduce_scatter_grad=True), w)
+    return OF.linear(C.all_gather(x, seq_dim, group, reduce_scatter_grad=True), w)
 
 
 def linear_reduce_scatter(x: torch.Tensor, w: torch.Tensor, topo: ParallelTopology, seq_dim: int = 1) -> torch.Tensor:
@@ -45,4 +45,4 @@ def linear_reduce_scatter(x: torch.Tensor, w: torch.Tensor, topo: ParallelTopolo
         from . import symm_tp
 
         return symm_tp.linear_reduce_scatter(x, w, topo, seq_dim)
-    return C.reduce_scatter(F.linear(x, w), seq_dim, group)
+    return C.reduce_scatter(OF.linear(x, w), seq_dim, group)

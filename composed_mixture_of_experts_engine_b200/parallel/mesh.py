@@ -33,6 +33,7 @@ __all__ = [
     "ep_process_group",
     "dp_process_group",
     "edp_process_group",
+    "ddp_process_group",
 ]
 
 _TP_GROUPS: Dict[Tuple[int, ...], "dist.ProcessGroup"] = {}
@@ -129,7 +130,28 @@ class ParallelTopology:
             if self.ep_from_dp:
                 return [self.rank_of(d, tp, pp) for d in range(self.dp_size) if d % self.ep_size == ep]
             return [self.rank_of(d, tp, pp, ep) for d in range(self.dp_size)]
+        if axis == "ddp":  # ranks that hold the same dense parameters and see different data
+            if self.ep_from_dp:
+                return self.axis_ranks("dp")
+            return [self.rank_of(d, tp, pp, e) for d in range(self.dp_size) for e in range(self.ep_size)]
         raise KeyError(axis)
+
+    def axis_size(self, axis: str) -> int:
+        if axis in ("dp", "tp", "pp", "ep"):
+            return {"dp": self.dp_size, "tp": self.tp_size, "pp": self.pp_size, "ep": self.ep_size}[axis]
+        return len(self.axis_ranks(axis))
+
+    @property
+    def data_replicas(self) -> int:
+        """How many ranks draw different data for the same dense parameters: ``dp`` when the expert-parallel group
+        is carved out of the data-parallel axis, ``dp * ep`` when it is an axis of its own (every expert-parallel
+        rank feeds its own tokens into the exchange)."""
+        return self.dp_size if self.ep_from_dp else self.dp_size * self.ep_size
+
+    @property
+    def data_rank(self) -> int:
+        """This rank's index among the ``data_replicas`` (what a data loader seeds or shards by)."""
+        return self.axis_ranks("ddp").index(self.rank)
 
     # ---- expert ownership ---------------------------------------------------------------------
     def experts_on_rank(self, total_experts: int, ep_rank: int) -> List[int]:
@@ -163,8 +185,7 @@ class ParallelTopology:
 
 
 def _axis_group(topology: ParallelTopology, axis: str, cache: Dict[Tuple[int, ...], "dist.ProcessGroup"]):
-    size = {"tp": topology.tp_size, "pp": topology.pp_size, "ep": topology.ep_size, "dp": topology.dp_size,
-            "edp": len(topology.axis_ranks("edp"))}[axis]
+    size = topology.axis_size(axis)
     if size == 1 or not dist.is_initialized():
         return None
     if topology.mesh is not None and axis in topology.mesh:  # type: ignore[operator]
@@ -204,11 +225,24 @@ def edp_process_group(topology: ParallelTopology):
     return _axis_group(topology, "edp", _EDP_GROUPS)
 
 
+_DDP_GROUPS: Dict[Tuple[int, ...], "dist.ProcessGroup"] = {}
+
+
+def ddp_process_group(topology: ParallelTopology):
+    """Ranks holding replicas of this rank's dense parameters (their gradients are reduced over these): the
+    data-parallel group, times the expert-parallel group when that is an axis of its own."""
+    return _axis_group(topology, "ddp", _DDP_GROUPS)
+
+
 def _build_axis_groups(probe: ParallelTopology) -> AxisGroups:
     """Create every axis group of every rank, in an order that is the same on all ranks."""
     groups = AxisGroups()
     world = probe.world_size
-    for axis in ("dp", "tp", "pp", "ep", "edp"):
+    for axis in ("dp", "tp", "pp", "ep", "edp", "ddp"):
+        if axis == "ddp" and probe.ep_from_dp:  # the same ranks as "dp": share its communicator
+            if "dp" in groups:
+                groups.add("ddp", groups.get_group("dp"), groups.ranks("dp"))
+            continue
         seen = set()
         for r in range(world):
             t = ParallelTopology(world, r, probe.dp_size, probe.ep_size, probe.tp_size, probe.pp_size,

@@ -18,8 +18,8 @@ from __future__ import annotations
 from typing import Optional
 
 import torch
-import torch.nn.functional as F
 
+from ..ops import functional as OF
 from . import collectives as C
 from .mesh import ParallelTopology, tp_process_group
 
@@ -41,7 +41,7 @@ def scatter_to_sequence_parallel(x: torch.Tensor, topology: Optional[ParallelTop
             raise ValueError(f"sequence length ({S}) must be divisible by tp_size ({tp}) for sequence parallelism")
         x = C.split(x, seq_dim, tp_process_group(topology))
     if next_weight is not None:
-        x = F.linear(x, next_weight)
+        x = OF.linear(x, next_weight)
         if tp > 1:
             # every rank holds the same full-sequence gradient afterwards: the backward keeps this rank's slice
             x = C.all_gather(x, seq_dim, tp_process_group(topology), reduce_scatter_grad=False)

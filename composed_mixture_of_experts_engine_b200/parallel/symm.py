@@ -25,10 +25,10 @@ _DISABLED_REASON: Optional[str] = None
 
 
 def _axis_group(topo: ParallelTopology, axis: str):
-    from .mesh import edp_process_group
+    from .mesh import ddp_process_group, edp_process_group
 
     return {"ep": ep_process_group, "tp": tp_process_group, "dp": dp_process_group,
-            "edp": edp_process_group}[axis](topo)
+            "edp": edp_process_group, "ddp": ddp_process_group}[axis](topo)
 
 
 def enabled_for(topo: Optional[ParallelTopology], axis: str) -> bool:
@@ -37,8 +37,7 @@ def enabled_for(topo: Optional[ParallelTopology], axis: str) -> bool:
         return False
     if os.environ.get("CMOE_DISABLE_PEER_KERNELS", "0") == "1" or _DISABLED_REASON is not None:
         return False
-    size = {"ep": topo.ep_size, "tp": topo.tp_size, "dp": topo.dp_size,
-            "edp": len(topo.axis_ranks("edp"))}[axis]
+    size = topo.axis_size(axis)
     if size <= 1 or topo.device.type != "cuda":
         return False
     if dist.get_backend() != "nccl":
@@ -118,6 +117,8 @@ class SymmGroup:
 
 
 def group_for(topo: ParallelTopology, axis: str) -> SymmGroup:
+    if axis == "ddp" and topo.ep_from_dp:
+        axis = "dp"  # the same ranks and the same communicator: one set of flag words
     ranks = tuple(topo.axis_ranks(axis))
     key = (axis, ranks)
     g = _GROUPS.get(key)

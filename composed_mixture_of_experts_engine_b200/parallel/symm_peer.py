@@ -52,9 +52,7 @@ def available(topology: Optional[ParallelTopology], axis: str) -> bool:
         return False
     if topology.pp_size > 1:
         return False  # several microbatches of one layer are in flight under 1F1B; per-layer buffers assume one
-    size = {"ep": topology.ep_size, "tp": topology.tp_size, "dp": topology.dp_size,
-            "edp": len(topology.axis_ranks("edp"))}[axis]
-    return 1 < size <= 16
+    return 1 < topology.axis_size(axis) <= 16
 
 
 def _push() -> bool:

@@ -13,6 +13,8 @@ input features (weight ``[out, in/tp]``).  Signatures follow the reference
   row layer reduce-scatters its output along the sequence dimension.
 * On CUDA with bf16 tensors and a symmetric-memory context the gather / reduce run inside the GEMM
   kernels over NVLink peer memory (``fused_tp``); otherwise the collectives of ``collectives.py`` run.
+* The local contraction is ``ops.functional.linear``: the two-SM tcgen05 GEMM on CUDA bf16 tensors (forward,
+  input gradient and weight gradient), ``F.linear`` on CPU / fp32.
 """
 
 from __future__ import annotations
@@ -22,8 +24,8 @@ from typing import Optional
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 
+from ..ops import functional as OF
 from . import collectives as C
 from .mesh import ParallelTopology, tp_process_group
 
@@ -68,9 +70,9 @@ class ColumnParallelLinear(nn.Module):
 
                 y = allgather_linear(x, self.weight, self.topology, self.seq_dim)
             else:
-                y = F.linear(C.copy_to_group(x, group), self.weight)
+                y = OF.linear(C.copy_to_group(x, group), self.weight)
         else:
-            y = F.linear(x, self.weight)
+            y = OF.linear(x, self.weight)
         if self.gather_output and self.tp_size > 1:
             y = C.all_gather(y, y.dim() - 1, group, reduce_scatter_grad=False)
             if self.bias is not None:
@@ -107,7 +109,7 @@ class RowParallelLinear(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.tp_size == 1:
-            return F.linear(x, self.weight, self.bias)
+            return OF.linear(x, self.weight, self.bias)
         group = tp_process_group(self.topology)
         if x.shape[-1] == self.in_features and self.in_features != self.in_per_rank:
             x = C.split(x, x.dim() - 1, group)  # full input: take this rank's feature slice
@@ -119,7 +121,7 @@ class RowParallelLinear(nn.Module):
 
             y = linear_reduce_scatter(x, self.weight, self.topology, self.seq_dim)
         else:
-            y = C.all_reduce(F.linear(x, self.weight), group)
+            y = C.all_reduce(OF.linear(x, self.weight), group)
         if self.bias is not None:
             y = y + self.bias
         return y

@@ -2,8 +2,7 @@
 
 The trainer keeps whole bf16 parameters of the layers a rank owns (dense parameters replicated over data
 parallelism, sliced by tensor and pipeline parallelism; experts additionally divided over expert parallelism), one
-gradient buffer of the same extent (bf16 for autograd-produced gradients, fp32 ``main_grad`` for the expert weights
-the grouped GEMMs accumulate into) and fp32 master weights plus two moments sharded over the ranks that hold the
+fp32 gradient buffer of the same extent (``main_grad``, which the weight-gradient GEMMs add into) and fp32 master weights plus two moments sharded over the ranks that hold the
 same parameters (``ops/optim.py``).  Activations are estimated per micro-batch from the saved tensors of one decoder
 block (sequence parallelism divides the norm / residual region by ``tp``).  The reference has no such planner.
 
@@ -71,7 +70,7 @@ def plan_memory(cfg: MoEConfig, world: Optional[int] = None, ep_buffer_factor: f
     dense_replicas = dp if ep_from_dp else dp * ep
     expert_replicas = max(1, dp // ep) if ep_from_dp else dp
     weights = 2 * (dense_local + experts_local)
-    grads = 2 * dense_local + 4 * experts_local
+    grads = 4 * (dense_local + experts_local)
     optim = 12 * (dense_local / dense_replicas + experts_local / expert_replicas)
     # activations of one micro-batch, all blocks of this stage kept for the backward (no recomputation)
     S, H, F, K = m.sequence_length, m.hidden_dim, m.ffn_dim, m.top_k

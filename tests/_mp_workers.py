@@ -258,6 +258,36 @@ def trainer_hybrid(rank, world, dp, ep, tp, pp, steps):
             "replicated": {k: v.detach().double().flatten()[:64].tolist() for k, v in replicated.items()}}
 
 
+def trainer_ep_axis(rank, world, dp, ep, steps):
+    """Expert parallelism as a mesh axis of its own (``ep_from_dp=False``): every expert-parallel rank draws its own
+    data, so the dense parameters are replicated over dp x ep ranks and must stay identical on all of them."""
+    import torch
+
+    from composed_mixture_of_experts_engine_b200.engine import Trainer
+    from composed_mixture_of_experts_engine_b200.utils.config import MoEConfig
+
+    cfg = MoEConfig.from_dict({
+        "model": dict(arch="moe_decoder", hidden_dim=32, num_layers=2, num_heads=2, num_experts=4, top_k=2,
+                      ffn_dim=64, vocab_size=128, sequence_length=16, dtype="float32", aux_loss_coeff=0.01,
+                      init_std=0.02),
+        "training": dict(micro_batch_size=2, gradient_accumulation_steps=1, global_batch_size=2 * dp * ep,
+                         max_steps=50, warmup_steps=0, learning_rate=5e-3, grad_clip=1.0, seed=0),
+        "parallelism": dict(data_parallel=dp, expert_parallel=ep, tensor_parallel=1, pipeline_parallel=1,
+                            ep_from_dp=False)})
+    tr = Trainer(cfg, device_type="cpu")
+    gen = torch.Generator().manual_seed(tr.topology.data_rank)  # every data replica its own tokens
+    losses = []
+    for _ in range(steps):
+        ids, tgt = tr.synthetic_batch(gen, pinned=False)
+        losses.append(float(tr.train_step(ids, tgt)))
+    blk = tr.model.blocks[0]
+    dense = {"gate": blk.moe.router.gate_w, "norm": blk.norm.weight, "wqkv": blk.attn.wqkv.weight,
+             "embed": tr.model.embed.weight}
+    return {"losses": losses, "data_rank": tr.topology.data_rank, "data_replicas": tr.topology.data_replicas,
+            "dense": {k: v.detach().double().flatten()[:96].tolist() for k, v in dense.items()},
+            "expert": blk.moe.w13.detach().double().flatten()[:32].tolist()}
+
+
 # -------------------------------------------------------------------------------------------------- GPU workers
 def _set_transport(transport):
     """"nccl", "auto" (peer memory, results pushed by the GEMM epilogues), "auto-pull" (peer memory, pulled) or

@@ -135,18 +135,75 @@ def test_fused_adamw_matches_torch_adamw_with_clipping():
     for step in range(3):
         grads = [torch.randn_like(p) * 3 for p in net.parameters()]
         for p, g, r in zip(net.parameters(), grads, ref):
-            p.grad.copy_(g)
+            p.main_grad.copy_(g)  # the optimizer's fp32 gradient buffer (what the weight-gradient GEMMs add into)
             r.grad = g.float().clone()
         torch.nn.utils.clip_grad_norm_(ref, 1.0)
         ropt.step()
         opt.step()
-        assert all(float(p.grad.abs().max()) == 0.0 for p in net.parameters())  # gradients cleared by the kernel
+        assert all(float(p.main_grad.abs().max()) == 0.0 for p in net.parameters())  # cleared by the kernel
     for g in opt.groups:
         pass
     masters = opt.groups[0].master
     flat_ref = torch.cat([r.detach().reshape(-1) for r in ref])
     assert torch.allclose(masters[: flat_ref.numel()], flat_ref, atol=2e-5, rtol=1e-4)
     assert torch.equal(list(net.parameters())[0].detach(), ref[0].detach().to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("rows,K,N", [(512, 256, 384), (1000, 2048, 520), (4096, 2048, 6144)])
+def test_linear_op_forward_and_gradients_match_fp32(rows, K, N):
+    """``ops.functional.linear`` (tcgen05 GEMMs for y, dx and dW) against fp32 matmuls of the same bf16 inputs,
+    first with autograd-owned gradients, then with the weight gradient accumulated into an fp32 ``main_grad``
+    over two backward passes (the TMA reduce-add epilogue)."""
+    from composed_mixture_of_experts_engine_b200.ops import functional as OF
+
+    torch.manual_seed(11)
+    x = (torch.randn(2, rows // 2, K, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_()
+    dy = torch.randn(2, rows // 2, N, device="cuda").to(torch.bfloat16)
+    assert OF.linear_supported(x, w)
+    y = OF.linear(x, w)
+    y.backward(dy)
+    xf, wf, dyf = x.detach().float(), w.detach().float(), dy.float()
+    assert _rel(y, xf @ wf.t()) < 1e-2
+    assert _rel(x.grad, dyf @ wf) < 1e-2
+    want_dw = dyf.reshape(-1, N).t() @ xf.reshape(-1, K)
+    assert _rel(w.grad, want_dw) < 1e-2
+    # accumulate into main_grad: two backward passes add up, p.grad stays untouched
+    w2 = w.detach().clone().requires_grad_()
+    w2.main_grad = torch.zeros(N, K, device="cuda", dtype=torch.float32)
+    for _ in range(2):
+        OF.linear(x.detach(), w2).backward(dy)
+    assert w2.grad is None
+    assert _rel(w2.main_grad, 2 * want_dw) < 1e-2
+
+
+@pytest.mark.parametrize("with_main_grad", [False, True])
+def test_lm_head_loss_matches_fp32_cross_entropy(with_main_grad):
+    """The chunked LM-head loss (logits GEMM, cross-entropy kernel, dh and dW GEMMs per chunk of rows) vs
+    ``F.cross_entropy`` on fp32 logits; chunk 256 forces several chunks and a ragged last one; V is not a
+    multiple of the GEMM tile."""
+    from composed_mixture_of_experts_engine_b200.models.decoder import lm_head_loss
+
+    torch.manual_seed(12)
+    n, H, V = 1000, 256, 1160
+    h = (torch.randn(n, H, device="cuda") * 0.7).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(V, H, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_()
+    if with_main_grad:
+        w.main_grad = torch.zeros(V, H, device="cuda", dtype=torch.float32)
+    tgt = torch.randint(0, V, (n,), device="cuda")
+    loss = lm_head_loss(h, w, tgt, 1.0 / n, chunk=256)
+    (loss * 2.0).backward()  # an upstream factor must reach both gradients
+    hf = h.detach().float().requires_grad_()
+    wf = w.detach().float().requires_grad_()
+    ref = torch.nn.functional.cross_entropy(hf @ wf.t(), tgt, reduction="sum") / n
+    (ref * 2.0).backward()
+    assert abs(float(loss) - float(ref)) < 2e-2
+    assert _rel(h.grad, hf.grad) < 3e-2
+    got_dw = w.main_grad if with_main_grad else w.grad
+    assert (w.grad is None) == with_main_grad
+    assert _rel(got_dw, wf.grad) < 3e-2
+    with torch.no_grad():  # evaluation: no gradient work, same value
+        assert abs(float(lm_head_loss(h, w, tgt, 1.0 / n, chunk=256)) - float(loss)) < 1e-5
 
 
 def test_trainer_loss_decreases_and_is_deterministic():

@@ -124,6 +124,21 @@ def test_trainer_hybrid_tp_sp_pp(dp, ep, tp, pp):
             assert diff < 1e-6, (name, diff)
 
 
+def test_dense_parameters_stay_identical_when_ep_is_its_own_axis():
+    """dp=1 x ep=2 with ``ep_from_dp=False``: each rank trains on its own tokens; the router gate, the norms, the
+    attention projections and the embedding must be bit-identical on both ranks after a few optimizer steps (they
+    are broadcast at start-up and their gradients are averaged over the dp x ep ranks), while the expert weights,
+    which are different experts, are not."""
+    res = _spawn("trainer_ep_axis", 2, 1, 2, 4, timeout=600)
+    a, b = res[0], res[1]
+    assert a["data_replicas"] == b["data_replicas"] == 2
+    assert {a["data_rank"], b["data_rank"]} == {0, 1}
+    for name in a["dense"]:
+        assert a["dense"][name] == b["dense"][name], name
+    assert a["expert"] != b["expert"]
+    assert a["losses"] != b["losses"]  # different data on the two ranks
+
+
 def test_moe_layer_tensor_parallel_matches_unsliced():
     res = _spawn("moe_layer_tp", 2)
     for r, out in res.items():

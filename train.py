@@ -66,6 +66,15 @@ def _smoke_config(cfg: MoEConfig) -> MoEConfig:
     return MoEConfig.from_dict(d)
 
 
+def _check_kernel_status(trainer: Trainer) -> None:
+    """Raise ``KernelTimeoutError`` if any kernel since the last check gave up on a bounded wait (a peer that never
+    arrived, a tile that never landed): from that step on the exchanged rows cannot be trusted, so the run must
+    not go on training on them, let alone checkpoint them over the last good state."""
+    from composed_mixture_of_experts_engine_b200.ops.kernels import check_status
+
+    check_status(trainer.device)
+
+
 def _routing_block(trainer: Trainer, cfg: MoEConfig, mfu: float) -> dict:
     """Telemetry of the first MoE layer of this rank (one device read)."""
     layers = trainer.model.moe_layers() if hasattr(trainer.model, "moe_layers") else []
@@ -167,7 +176,8 @@ def main(argv=None) -> int:
             log.warning("could not resume from step %s (%s); starting fresh", latest, exc)
     trainer.step_index = start_step
 
-    gen = torch.Generator().manual_seed(t.seed + 7919 * rank + 104729 * start_step)
+    # one data stream per data replica: tensor- and pipeline-parallel peers of a replica must see the same tokens
+    gen = torch.Generator().manual_seed(t.seed + 7919 * topo.data_rank + 104729 * start_step)
     for layer in (trainer.model.moe_layers() if hasattr(trainer.model, "moe_layers") else [])[:1]:
         layer.enable_timing(True)
         layer.router.profile_timing = True
@@ -188,13 +198,14 @@ def main(argv=None) -> int:
             loss = float(loss_t)  # the only host wait of the loop
             if use_cuda:
                 torch.cuda.synchronize()
+                _check_kernel_status(trainer)  # a bounded device wait that ran out must stop the run here
             now = time.perf_counter()
             dt = (now - t_log) / steps_since_log
             t_log, steps_since_log = now, 0
             res = mfu_acct.end_step(tokens_per_step, step_time_sec=dt)
             blocks = _routing_block(trainer, cfg, res.mfu)
             rec = StepRecord(
-                step=step, loss=loss, mfu=res.mfu, tokens_per_sec=res.tokens_per_sec * topo.dp_size,
+                step=step, loss=loss, mfu=res.mfu, tokens_per_sec=res.tokens_per_sec * topo.data_replicas,
                 kernel=blocks["kernel"], collective=blocks["collective"],
                 infra={"async_ckpt_commit_ms": harness.async_ckpt.last_commit_ms,
                        "active_nodes": len(harness.state.alive_ranks()), "ep_world_size": topo.ep_size,
@@ -205,6 +216,8 @@ def main(argv=None) -> int:
                 profile_rows.append({"step": step, "step_ms": dt * 1e3, "tokens_per_sec": rec.tokens_per_sec,
                                      "mfu": res.mfu, "loss": loss, **blocks["collective"]})
         if t.ckpt_interval > 0 and step > 0 and step % t.ckpt_interval == 0:
+            if use_cuda:
+                _check_kernel_status(trainer)  # never write weights that a timed-out exchange may have corrupted
             harness.checkpoint(trainer.model, trainer.optimizer, step)
         if step > 0 and step % 50 == 0:
             dead = harness.health_check()
@@ -214,12 +227,10 @@ def main(argv=None) -> int:
                 trainer.topology = new_topo
 
     if t.max_steps > start_step:
+        if use_cuda:
+            _check_kernel_status(trainer)
         harness.checkpoint(trainer.model, trainer.optimizer, t.max_steps)
     harness.shutdown()
-    if use_cuda:
-        from composed_mixture_of_experts_engine_b200.ops.kernels import check_status
-
-        check_status(trainer.device)
     logger.close()
     if args.profile and rank == 0 and profile_rows:
         out_dir = Path(os.environ.get("MOE_PROFILE_DIR", str(ROOT / "benchmarks")))
