@@ -5,6 +5,8 @@
 
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 #include "ops.cuh"
 
 namespace {
@@ -15,7 +17,7 @@ namespace {
 static __device__ __align__(256) int g_plan_scratch[CMOE_NOALLOC_SCRATCH_WORDS];
 
 constexpr int kMaxDevices = 64;
-int* g_scratch_addr[kMaxDevices] = {nullptr};
+std::atomic<int*> g_scratch_addr[kMaxDevices];  // zero-initialised; filled on the first call per device
 
 // Device address of the scratch array on the current device (looked up on the first call per device).
 cudaError_t scratch_for_current_device(int** out) {
@@ -23,13 +25,13 @@ cudaError_t scratch_for_current_device(int** out) {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
-  if (g_scratch_addr[dev] == nullptr) {
-    int* ptr = nullptr;
+  int* ptr = g_scratch_addr[dev].load(std::memory_order_acquire);
+  if (ptr == nullptr) {  // two threads racing here both ask the runtime and both get the same address
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_plan_scratch);
     if (e != cudaSuccess) return e;
-    g_scratch_addr[dev] = ptr;
+    g_scratch_addr[dev].store(ptr, std::memory_order_release);
   }
-  *out = g_scratch_addr[dev];
+  *out = ptr;
   return cudaSuccess;
 }
 
@@ -42,11 +44,12 @@ extern "C" size_t cmoe_moe_plan_noalloc_words(long long n_slots, int n_local, in
 extern "C" int cmoe_moe_plan_noalloc(const int* topk_idx, long long n_slots, int K, int num_experts, int expert_lo,
                                      int n_local, int per_k_bins, int capacity, long long cap_rows, int* slot_row,
                                      int* row_slot, int* group_offsets, int* tile_group, int* num_m_tiles,
-                                     int* counts_kept, void* cuda_stream, int* cuda_error) {
+                                     int* counts_kept, int* overflow, void* cuda_stream, int* cuda_error) {
   if (cuda_error) *cuda_error = 0;
   if (topk_idx == nullptr || slot_row == nullptr || row_slot == nullptr || group_offsets == nullptr ||
       tile_group == nullptr || num_m_tiles == nullptr || counts_kept == nullptr || n_slots <= 0 || K <= 0 ||
-      n_local <= 0 || num_experts <= 0 || cap_rows <= 0 || cap_rows % 128 != 0)
+      n_local <= 0 || num_experts <= 0 || cap_rows <= 0 || cap_rows % 128 != 0 || expert_lo < 0 ||
+      static_cast<long long>(expert_lo) + n_local > num_experts || capacity < 0)
     return CMOE_NOALLOC_BAD_ARGUMENT;
   if (cmoe::moe_plan_scratch_words(n_slots, n_local, K, per_k_bins) > CMOE_NOALLOC_SCRATCH_WORDS)
     return CMOE_NOALLOC_TOO_LARGE;
@@ -70,6 +73,7 @@ extern "C" int cmoe_moe_plan_noalloc(const int* topk_idx, long long n_slots, int
     a.tile_group = tile_group;
     a.num_m_tiles = num_m_tiles;
     a.counts_kept = counts_kept;
+    a.overflow = overflow;  // may be null: the kernels then only skip the slots that do not fit
     a.scratch = scratch;  // the histogram pass zeroes the words it uses, so stale contents do no harm
     e = cmoe::launch_moe_plan(a, static_cast<cudaStream_t>(cuda_stream));
   }

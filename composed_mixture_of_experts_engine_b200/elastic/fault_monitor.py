@@ -253,44 +253,84 @@ def _torch_loads(payload: bytes) -> Any:
 
 
 class _PinnedStager:
-    """Copies a nest of tensors to host memory; CUDA tensors go through pinned buffers on a side stream."""
+    """Copies a nest of tensors to host memory; CUDA tensors go through pinned buffers on a side stream.
+
+    The pinned buffers are kept: a snapshot takes an idle set (one buffer per tensor of the nest, found again by
+    its path), the writer thread hands the set back once the bytes are serialised, so steady-state saves do no
+    ``cudaHostAlloc`` (each one is a device-wide synchronisation and takes milliseconds per gigabyte).  As many
+    sets exist as snapshots were ever in flight at once (bounded by the checkpoint queue).
+
+    The training stream is not made to wait for the copy.  What must not happen is that the next optimizer step
+    overwrites parameters or moments that are still being read: ``guard()`` makes the current stream wait for the
+    last copy, and the checkpointer calls it from a pre-step hook of the optimizer (or right after the snapshot,
+    for an optimizer without such hooks).  The forward and backward passes of the next step overlap the copy."""
 
     def __init__(self) -> None:
         self._streams: Dict[int, Any] = {}
+        self._idle: List[Dict[str, torch.Tensor]] = []
+        self._lock = threading.Lock()
+        self._pending: Optional[Any] = None  # event of the last snapshot that nothing has waited for yet
+        self.allocations = 0  # pinned buffers created so far (tests and telemetry)
 
-    def snapshot(self, obj: Any):
-        """Returns (host copy of ``obj``, CUDA event or None).  Only enqueues work; does not wait for the GPU."""
-        devices = set()
+    def _take_set(self) -> Dict[str, torch.Tensor]:
+        with self._lock:
+            return self._idle.pop() if self._idle else {}
 
-        def walk(o):
+    def release(self, bufset: Optional[Dict[str, torch.Tensor]]) -> None:
+        if bufset is not None:
+            with self._lock:
+                self._idle.append(bufset)
+
+    def snapshot(self, obj: Any, defer_guard: bool = False):
+        """Returns (host copy of ``obj``, (start, end) CUDA events or None, buffer set).  Only enqueues work; does
+        not wait for the GPU.  With ``defer_guard`` the caller promises to call :meth:`guard` before anything
+        overwrites the source tensors."""
+        bufset = self._take_set()
+        used = [False]
+
+        def walk(o, path):
             if isinstance(o, torch.Tensor):
                 if o.is_cuda:
-                    devices.add(o.device.index)
-                    host = torch.empty(o.shape, dtype=o.dtype, device="cpu", pin_memory=True)
+                    used[0] = True
+                    host = bufset.get(path)
+                    if host is None or host.shape != o.shape or host.dtype != o.dtype:
+                        host = torch.empty(o.shape, dtype=o.dtype, device="cpu", pin_memory=True)
+                        bufset[path] = host
+                        self.allocations += 1
                     host.copy_(o.detach(), non_blocking=True)
                     return host
                 return o.detach().clone()
             if isinstance(o, dict):
-                return {k: walk(v) for k, v in o.items()}
+                return {k: walk(v, f"{path}/{k}") for k, v in o.items()}
             if isinstance(o, (list, tuple)):
-                return type(o)(walk(v) for v in o)
+                return type(o)(walk(v, f"{path}/{i}") for i, v in enumerate(o))
             return o
 
         if not torch.cuda.is_available():
-            return walk(obj), None
+            return walk(obj, ""), None, None
         dev = torch.cuda.current_device()
         side = self._streams.setdefault(dev, torch.cuda.Stream(device=dev))
         main = torch.cuda.current_stream(dev)
         side.wait_stream(main)
         with torch.cuda.stream(side):
-            host = walk(obj)
-            ev = torch.cuda.Event()
-            ev.record(side)
-        if not devices:
-            return host, None
-        # later work of the training stream (the next optimizer step) must not overwrite what is being copied
-        main.wait_event(ev)
-        return host, ev
+            start = torch.cuda.Event(enable_timing=True)
+            start.record(side)
+            host = walk(obj, "")
+            end = torch.cuda.Event(enable_timing=True)
+            end.record(side)
+        if not used[0]:
+            self.release(bufset)
+            return host, None, None
+        self._pending = end
+        if not defer_guard:
+            self.guard()
+        return host, (start, end), bufset
+
+    def guard(self) -> None:
+        """Make the current stream wait for the last snapshot's copy (no host wait)."""
+        ev, self._pending = self._pending, None
+        if ev is not None and torch.cuda.is_available():
+            torch.cuda.current_stream().wait_event(ev)
 
 
 class AsyncCheckpointer:
@@ -306,8 +346,11 @@ class AsyncCheckpointer:
         self._completed_steps: List[int] = []
         self._lock = threading.Lock()
         self._stager = _PinnedStager()
-        self.last_commit_ms = 0.0
+        self.last_commit_ms = 0.0  # time the training thread spent inside save()
+        self.last_d2h_ms = 0.0     # device time of the last snapshot's device-to-host copies (side stream)
+        self.last_write_ms = 0.0   # serialise + write + mirror time of the last committed step (writer thread)
         self.last_error: Optional[BaseException] = None
+        self._hooked: set = set()
         for i in range(max(1, workers)):
             t = threading.Thread(target=self._worker, name=f"ckpt-writer-{i}", daemon=True)
             t.start()
@@ -316,12 +359,20 @@ class AsyncCheckpointer:
     # ---- state dict helpers ----------------------------------------------------------------------
     @staticmethod
     def _state(model: torch.nn.Module, optimizer) -> Dict[str, Any]:
-        return {"model": dict(model.state_dict()), "optim": optimizer.state_dict() if optimizer is not None else {}}
+        osd = optimizer.state_dict() if optimizer is not None else {}
+        if isinstance(optimizer, torch.optim.Optimizer):
+            # a stock optimizer numbers its parameters; the names make its state addressable by a loader that runs
+            # under another expert-parallel degree (``Optimizer.load_state_dict`` ignores the extra key)
+            name_of = {id(p): n for n, p in model.named_parameters()}
+            osd = dict(osd)
+            osd["param_names"] = [name_of.get(id(p), "") for g in optimizer.param_groups for p in g["params"]]
+        return {"model": dict(model.state_dict()), "optim": osd}
 
     def save(self, model: torch.nn.Module, optimizer, step: int, rank: int = 0,
              extra_meta: Optional[Dict[str, Any]] = None) -> None:
         t0 = time.perf_counter()
-        snapshot, event = self._stager.snapshot(self._state(model, optimizer))
+        snapshot, event, bufset = self._stager.snapshot(self._state(model, optimizer),
+                                                        defer_guard=self._guard_from_optimizer(optimizer))
         meta = {
             "schema_version": CHECKPOINT_SCHEMA_VERSION,
             "step": step,
@@ -333,8 +384,22 @@ class AsyncCheckpointer:
         }
         if extra_meta:
             meta.update(extra_meta)
-        self._q.put(_CheckpointJob(step=step, payload=(snapshot, event), meta=meta))
+        self._q.put(_CheckpointJob(step=step, payload=(snapshot, event, bufset), meta=meta))
         self.last_commit_ms = (time.perf_counter() - t0) * 1000.0
+
+    def _guard_from_optimizer(self, optimizer) -> bool:
+        """True when ``optimizer`` will call the stager's guard before its next step (a pre-step hook, installed
+        once per optimizer): the snapshot then need not stall the training stream."""
+        if optimizer is None or not torch.cuda.is_available():
+            return False
+        reg = getattr(optimizer, "register_step_pre_hook", None)
+        if reg is None:
+            return False
+        if id(optimizer) not in self._hooked:
+            stager = self._stager
+            reg(lambda *args, **kwargs: stager.guard())
+            self._hooked.add(id(optimizer))
+        return True
 
     def latest_step(self) -> Optional[int]:
         steps = [s for s in (_step_of_key(k) for k in self.local.list("ckpts/")) if s is not None]
@@ -391,11 +456,17 @@ class AsyncCheckpointer:
                 break
             try:
                 payload = job.payload
+                t_w = time.perf_counter()
                 if isinstance(payload, tuple):
-                    snapshot, event = payload
-                    if event is not None:
-                        event.synchronize()
-                    payload = _torch_dumps(snapshot)
+                    snapshot, event, bufset = payload
+                    try:
+                        if event is not None:
+                            event[1].synchronize()
+                            self.last_d2h_ms = float(event[0].elapsed_time(event[1]))
+                        payload = _torch_dumps(snapshot)
+                    finally:
+                        self._stager.release(bufset)  # the pinned buffers serve the next snapshot
+                    del snapshot
                 root = f"ckpts/step={job.step:06d}/rank={job.meta.get('rank', 0):06d}"
                 meta_bytes = json.dumps(job.meta).encode("utf-8")
                 self.local.put(f"{root}.pt", payload)
@@ -403,6 +474,7 @@ class AsyncCheckpointer:
                 if self.remote is not None:
                     self.remote.put(f"{root}.pt", payload)
                     self.remote.put(f"{root}.meta.json", meta_bytes)
+                self.last_write_ms = (time.perf_counter() - t_w) * 1000.0
                 with self._lock:
                     self._completed_steps = sorted(set(self._completed_steps + [job.step]))[-self.retention:]
                 self._prune()
@@ -413,14 +485,19 @@ class AsyncCheckpointer:
                 self._q.task_done()
 
     def _prune(self) -> None:
+        """Delete the steps that are OLDER than the oldest retained one, in both tiers.  A step that is not in the
+        retained list but newer than its oldest entry is a save still in flight on another worker (its files
+        exist before it is marked complete): deleting it would lose the newest checkpoint."""
         with self._lock:
-            keep = set(self._completed_steps)
+            if not self._completed_steps:
+                return
+            oldest_kept = min(self._completed_steps)
         for store in (self.local, self.remote):
             if store is None:
                 continue
             for k in store.list("ckpts/"):
                 s = _step_of_key(k)
-                if s is not None and s not in keep:
+                if s is not None and s < oldest_kept:
                     try:
                         store.delete(k)
                     except Exception:
@@ -617,6 +694,8 @@ class ElasticTrainerHarness:
         self.state.register_on_drop(self.state._on_rank_failure)
         self._signals_installed = False
         self.last_reshard_plan: Optional[Dict[int, List[int]]] = None
+        self.recovered_model: Optional[torch.nn.Module] = None
+        self.recovered_optimizer: Any = None
 
     def _init_etcd_rendezvous(self) -> None:
         """Probe an etcd rendezvous (restart epoch tracking); any failure falls back to c10d."""
@@ -656,46 +735,205 @@ class ElasticTrainerHarness:
         return self.state.heartbeat()
 
     def load_resharded(self, model: torch.nn.Module, step: int, old_meta: Dict[str, Any],
-                       new_topo: ParallelTopology, num_experts: int) -> None:
-        """Fill ``model`` (built for ``new_topo``) from files written under another expert-parallel degree.
+                       new_topo: ParallelTopology, num_experts: int, optimizer=None) -> None:
+        """Fill ``model`` (and ``optimizer``), built for ``new_topo``, from files written under another data- /
+        expert-parallel degree (same tensor- and pipeline-parallel degrees).
 
-        Dense parameters come from any old rank's file; the stacked expert weights (``*.w13`` / ``*.w2``) are
-        assembled row by row from the old files that own the experts this rank holds now.
+        Dense parameters come from an old rank with this rank's tensor / pipeline coordinates; the stacked expert
+        weights (``*.w13`` / ``*.w2``) are assembled expert by expert from the old ranks that owned them.  The
+        optimizer state follows its parameters: a stock optimizer's per-parameter moments are re-assembled the same
+        way (by parameter name), the fused optimizer's flat fp32 shards are re-sliced through the layout table
+        that its state dict carries (``FusedAdamW.load_resharded``).
         """
         old_ep = int(old_meta.get("ep_size", 1))
         old_world = int(old_meta.get("world_size", 1))
-        old_probe = ParallelTopology(old_world, 0, int(old_meta.get("dp_size", 1)), old_ep,
-                                     int(old_meta.get("tp_size", 1)), int(old_meta.get("pp_size", 1)),
-                                     ep_from_dp=bool(old_meta.get("ep_from_dp", False)))
-        # one representative global rank per old ep rank
+        old_dims = (int(old_meta.get("dp_size", 1)), old_ep, int(old_meta.get("tp_size", 1)),
+                    int(old_meta.get("pp_size", 1)))
+        carved = bool(old_meta.get("ep_from_dp", False))
+
+        def old_topo(r: int) -> ParallelTopology:
+            return ParallelTopology(old_world, r, old_dims[0], old_dims[1], old_dims[2], old_dims[3],
+                                    ep_from_dp=carved)
+
+        old_probe = old_topo(0)
+        # one representative old global rank per old expert-parallel rank, at this rank's tp / pp coordinates
         rep: Dict[int, int] = {}
         for r in range(old_world):
-            t = ParallelTopology(old_world, r, old_probe.dp_size, old_ep, old_probe.tp_size, old_probe.pp_size,
-                                 ep_from_dp=old_probe.ep_from_dp)
+            t = old_topo(r)
             if t.tp_rank == new_topo.tp_rank and t.pp_rank == new_topo.pp_rank:
                 rep.setdefault(t.ep_rank, r)
-        cache: Dict[int, Dict[str, torch.Tensor]] = {}
+        if not rep:
+            raise RuntimeError("no old rank has this rank's tensor / pipeline coordinates: the tensor- and "
+                               "pipeline-parallel degrees must not change across a recovery")
+        files: Dict[int, Dict[str, Any]] = {}
 
-        def old_model(ep_rank: int) -> Dict[str, torch.Tensor]:
-            if ep_rank not in cache:
-                cache[ep_rank] = self.async_ckpt.load_raw(step, rep[ep_rank])["model"]
-            return cache[ep_rank]
+        def old_file(r: int) -> Dict[str, Any]:
+            if r not in files:
+                files[r] = self.async_ckpt.load_raw(step, r)
+            return files[r]
+
+        def is_expert(name: str) -> bool:
+            return name.rsplit(".", 1)[-1] in ("w13", "w2")
+
+        def owner_of(e: int):
+            """(old ep rank that owned global expert ``e``, its index among that rank's experts)"""
+            for r in range(old_ep):
+                owned = old_probe.experts_on_rank(num_experts, r)
+                if e in owned:
+                    return r, owned.index(e)
+            raise KeyError(e)
 
         mine = new_topo.experts_on_this_rank(num_experts)
+        base_rank = rep[min(rep)]
         sd = model.state_dict()
-        base = old_model(min(rep))
+        base = old_file(base_rank)["model"]
         with torch.no_grad():
             for name, dst in sd.items():
-                if name.rsplit(".", 1)[-1] in ("w13", "w2"):
+                if is_expert(name):
                     for j, e in enumerate(mine):
-                        owner = next(r for r in range(old_ep) if e in old_probe.experts_on_rank(num_experts, r))
-                        local = old_probe.experts_on_rank(num_experts, owner).index(e)
-                        dst[j].copy_(old_model(owner)[name][local])
+                        owner, local = owner_of(e)
+                        dst[j].copy_(old_file(rep[owner])["model"][name][local])
                 elif name in base:
                     dst.copy_(base[name])
+        if optimizer is None:
+            return
+        if isinstance(optimizer, torch.optim.Optimizer):
+            self._reshard_stock_optimizer(model, optimizer, old_file, rep, base_rank, mine, owner_of, is_expert)
+            return
+        if not hasattr(optimizer, "load_resharded"):
+            return
 
-    def recover(self, model: torch.nn.Module, optimizer, num_experts: int) -> ParallelTopology:
-        """evict -> re-form the process group from the environment -> re-own experts -> reload -> resume."""
+        shard_axis = {"dense": "ddp", "expert": "edp"}
+
+        def read_flat(r: int, group: str, lo: int, hi: int) -> Optional[Dict[str, torch.Tensor]]:
+            """Elements [lo, hi) of the flat fp32 state of ``group`` as held by the old model replica of rank ``r``:
+            concatenated from the files of the ranks that shared that replica's optimizer state."""
+            ranks = old_topo(r).axis_ranks(shard_axis.get(group, "ddp"))
+            out: Dict[str, List[torch.Tensor]] = {"master": [], "m": [], "v": []}
+            pos = lo
+            while pos < hi:
+                first = old_file(ranks[0])["optim"]["groups"][group]
+                shard_numel = int(first["numel"]) // int(first["shard_world"])
+                sr = pos // shard_numel
+                g = old_file(ranks[sr])["optim"]["groups"][group]
+                a, b = pos - sr * shard_numel, min(hi, (sr + 1) * shard_numel) - sr * shard_numel
+                for k in out:
+                    out[k].append(g[k][a:b])
+                pos = sr * shard_numel + b
+            return {k: torch.cat(v) for k, v in out.items()}
+
+        def fetch(group: str, pname: str, lo: int, hi: int):
+            groups = old_file(base_rank)["optim"].get("groups", {})
+            if group not in groups:
+                return None
+            layout = {n: (off, numel, shape) for n, off, numel, shape in groups[group]["layout"]}
+            if pname not in layout:
+                return None
+            off, numel, shape = layout[pname]
+            if not is_expert(pname):
+                return read_flat(base_rank, group, off + lo, off + hi)
+            per = numel // max(1, shape[0])  # elements of one expert in the old (and new) stacked tensor
+            parts: Dict[str, List[torch.Tensor]] = {"master": [], "m": [], "v": []}
+            pos = lo
+            while pos < hi:
+                j = pos // per
+                a, b = pos - j * per, min(hi, (j + 1) * per) - j * per
+                owner, local = owner_of(mine[j])
+                got = read_flat(rep[owner], group, off + local * per + a, off + local * per + b)
+                for k in parts:
+                    parts[k].append(got[k])
+                pos = j * per + b
+            return {k: torch.cat(v) for k, v in parts.items()}
+
+        optimizer.load_resharded(fetch, int(old_file(base_rank)["optim"].get("step", 0)))
+        for g in getattr(optimizer, "groups", []):
+            optimizer._publish_params(g)
+
+    @staticmethod
+    def _reshard_stock_optimizer(model, optimizer, old_file, rep, base_rank, mine, owner_of, is_expert) -> None:
+        """Re-assemble a ``torch.optim`` optimizer's per-parameter state by parameter name (see ``load_resharded``)."""
+        name_of = {id(p): n for n, p in model.named_parameters()}
+        new_names = [name_of.get(id(p), "") for g in optimizer.param_groups for p in g["params"]]
+        new_params = [p for g in optimizer.param_groups for p in g["params"]]
+
+        def old_state(r: int, name: str):
+            osd = old_file(r)["optim"]
+            names = osd.get("param_names")
+            if not names or name not in names:
+                return None
+            return osd["state"].get(names.index(name))
+
+        state: Dict[int, Dict[str, Any]] = {}
+        for i, (name, p) in enumerate(zip(new_names, new_params)):
+            if not is_expert(name):
+                st = old_state(base_rank, name)
+                if st is not None:
+                    state[i] = {k: (v.clone() if isinstance(v, torch.Tensor) else v) for k, v in st.items()}
+                continue
+            rows: Dict[str, List[torch.Tensor]] = {}
+            scalars: Dict[str, Any] = {}
+            for e in mine:
+                owner, local = owner_of(e)
+                st = old_state(rep[owner], name)
+                if st is None:
+                    rows = {}
+                    break
+                for k, v in st.items():
+                    if isinstance(v, torch.Tensor) and v.dim() > 0 and v.shape[1:] == p.shape[1:]:
+                        rows.setdefault(k, []).append(v[local])
+                    else:
+                        scalars[k] = v.clone() if isinstance(v, torch.Tensor) else v
+            if rows:
+                state[i] = {**scalars, **{k: torch.stack(v) for k, v in rows.items()}}
+        sd = optimizer.state_dict()
+        sd["state"] = state
+        optimizer.load_state_dict(sd)
+
+    def resume(self, model: torch.nn.Module, optimizer, num_experts: int) -> Optional[int]:
+        """Load the newest checkpoint into ``model`` / ``optimizer`` (built for this harness's topology) and return
+        its step, or ``None`` when there is none.  When the files were written under another mesh (a restart with
+        fewer or more ranks) the experts and the optimizer state are re-owned (``load_resharded``)."""
+        latest = self.async_ckpt.latest_step()
+        if latest is None:
+            return None
+        topo = self.topology
+        try:
+            meta = json.loads(self.async_ckpt._fetch(f"ckpts/step={latest:06d}/rank={0:06d}.meta.json").decode("utf-8"))
+        except FileNotFoundError:
+            meta = {}
+        same = all(int(meta.get(k, getattr(topo, k))) == getattr(topo, k)
+                   for k in ("world_size", "dp_size", "ep_size", "tp_size", "pp_size"))
+        if same:
+            self.async_ckpt.load(model, optimizer, latest, rank=topo.rank)
+        else:
+            self.load_resharded(model, latest, meta, topo, num_experts, optimizer=optimizer)
+        log.info("resumed from step=%d on dp=%d ep=%d tp=%d pp=%d (%s)", latest, topo.dp_size, topo.ep_size,
+                 topo.tp_size, topo.pp_size, "same mesh" if same else "re-sharded")
+        return latest
+
+    def plan_recovery_mesh(self, new_world: int, num_experts: int) -> Dict[str, Any]:
+        """The mesh after a change of the number of ranks: tensor- and pipeline-parallel degrees are kept (the
+        weight slices on disk have those shapes), data parallelism absorbs the change, and the expert-parallel
+        degree becomes the largest divisor that still fits (of the data-parallel degree when it is carved out of
+        it, of what is left of the world otherwise) and divides the experts."""
+        old = self.topology
+        tp, pp = old.tp_size, old.pp_size
+        if new_world % (tp * pp) != 0:
+            raise RuntimeError(f"{new_world} ranks cannot keep tensor parallel {tp} x pipeline parallel {pp}")
+        rest = new_world // (tp * pp)
+        ep = _largest_divisor_le(rest, old.ep_size)
+        while ep > 1 and (num_experts % ep != 0 or rest % ep != 0):
+            ep -= 1
+        dp = rest if old.ep_from_dp else rest // ep
+        return {"dp": dp, "ep": ep, "tp": tp, "pp": pp, "ep_from_dp": old.ep_from_dp}
+
+    def recover(self, model: torch.nn.Module, optimizer, num_experts: int, rebuild=None) -> ParallelTopology:
+        """evict -> re-form the process group from the environment -> re-own experts -> reload -> resume.
+
+        ``rebuild(new_topology) -> (model, optimizer)``: called when the layout changed (the expert tensors of a
+        rank have another leading dimension under another expert-parallel degree, so the old objects cannot hold
+        the new shards); what it returns is filled from the checkpoint and kept in ``recovered_model`` /
+        ``recovered_optimizer``.  Without it the given objects are loaded in place."""
         log.warning("entering recovery on rank=%d", self.topology.rank)
         self.state.begin_recovery()
         if dist.is_initialized():
@@ -703,32 +941,23 @@ class ElasticTrainerHarness:
         new_world = int(os.environ.get("WORLD_SIZE", str(self.topology.world_size)))
         new_rank = int(os.environ.get("RANK", str(self.topology.rank)))
         if new_world > 1:
-            dist.init_process_group(backend="nccl" if torch.cuda.is_available() else "gloo", world_size=new_world,
-                                    rank=new_rank)
-        new_ep = _largest_divisor_le(new_world, self.topology.ep_size)
-        new_dp = new_world // new_ep
-        new_topo = build_topology(new_dp, new_ep, device_type=self.topology.device.type)
+            dist.init_process_group(backend="nccl" if (torch.cuda.is_available() and
+                                                       self.topology.device.type == "cuda") else "gloo",
+                                    world_size=new_world, rank=new_rank)
+        mesh = self.plan_recovery_mesh(new_world, num_experts)
+        old_topo = self.topology
+        new_topo = build_topology(mesh["dp"], mesh["ep"], mesh["tp"], mesh["pp"],
+                                  device_type=self.topology.device.type, ep_from_dp=mesh["ep_from_dp"])
         self.state._rebalance_experts(self.state.alive_ranks(), self.topology.mesh, num_experts)
         self.last_reshard_plan = self.state.reshard(new_topo, num_experts)
-        latest = self.async_ckpt.latest_step()
-        if latest is not None:
-            same_layout = (new_topo.ep_size == self.topology.ep_size and new_topo.world_size == self.topology.world_size)
-            if same_layout:
-                self.async_ckpt.load(model, optimizer, latest, rank=new_topo.rank)
-            else:
-                try:
-                    meta = json.loads(self.local_adapter.get(
-                        f"ckpts/step={latest:06d}/rank={0:06d}.meta.json").decode("utf-8"))
-                except FileNotFoundError:
-                    meta = {"ep_size": self.topology.ep_size, "dp_size": self.topology.dp_size,
-                            "world_size": self.topology.world_size}
-                try:
-                    self.load_resharded(model, latest, meta, new_topo, num_experts)
-                except Exception as exc:
-                    log.warning("resharded load failed (%s); loading this rank's own file", exc)
-                    self.async_ckpt.load(model, optimizer, latest, rank=new_topo.rank)
-            log.info("resumed from step=%d on new topology dp=%d ep=%d", latest, new_dp, new_ep)
-        else:
+        same_layout = (new_topo.ep_size == old_topo.ep_size and new_topo.world_size == old_topo.world_size
+                       and new_topo.dp_size == old_topo.dp_size)
+        if rebuild is not None and not same_layout:
+            model, optimizer = rebuild(new_topo)
+        self.recovered_model, self.recovered_optimizer = model, optimizer
+        self.topology = new_topo
+        latest = self.resume(model, optimizer, num_experts)
+        if latest is None:
             log.warning("no checkpoint found; continuing from the current weights")
         self.state.mark_resumed()
         self.state.topology = new_topo

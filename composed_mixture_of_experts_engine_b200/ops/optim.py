@@ -35,8 +35,9 @@ class _FlatGroup:
     """One flat bf16 parameter buffer + gradient buffer + (sharded) fp32 master / moments."""
 
     def __init__(self, name: str, params: List[nn.Parameter], grad_dtype: torch.dtype, weight_decay_mask: List[bool],
-                 shard_group=None, topology=None, axis: str = "dp"):
+                 shard_group=None, topology=None, axis: str = "dp", param_names: Optional[List[str]] = None):
         self.name, self.params = name, params
+        self.param_names = list(param_names) if param_names is not None else [f"{name}.{i}" for i in range(len(params))]
         dev = params[0].device
         self.shard_group = shard_group
         self.shard_world = dist.get_world_size(shard_group) if shard_group is not None else 1
@@ -127,6 +128,13 @@ class FusedAdamW:
         self.last_grad_norm_sq: Optional[torch.Tensor] = None
         self._norm_groups = list(norm_groups)  # process groups over which the squared norm is summed
         self.param_groups = [{"lr": lr, "params": [p for g in groups for p in g.params]}]
+        self._pre_step_hooks: List = []
+
+    def register_step_pre_hook(self, hook) -> None:
+        """``hook(optimizer, args, kwargs)`` runs at the start of every ``step`` (the ``torch.optim.Optimizer``
+        name and signature).  The asynchronous checkpointer uses it to make the step wait for a snapshot that is
+        still being copied off the device."""
+        self._pre_step_hooks.append(hook)
 
     # -- torch.optim-like surface ----------------------------------------------------------------
     def zero_grad(self, set_to_none: bool = False) -> None:
@@ -136,8 +144,13 @@ class FusedAdamW:
     def state_dict(self) -> Dict:
         return {
             "step": self.step_count,
+            # ``layout`` (parameter name, offset in the flat buffer, element count, shape) lets a loader that runs
+            # under another sharding find any parameter's master weights and moments again
             "groups": {g.name: {"master": g.master, "m": g.m, "v": g.v, "shard_rank": g.shard_rank,
-                                "shard_world": g.shard_world} for g in self.groups},
+                                "shard_world": g.shard_world, "numel": g.numel, "shard_lo": g.shard_lo,
+                                "layout": [(n, off, p.numel(), tuple(p.shape))
+                                           for n, off, p in zip(g.param_names, g.offsets, g.params)]}
+                       for g in self.groups},
             "param_groups": [{"lr": self.lr, "betas": self.betas, "eps": self.eps,
                               "weight_decay": self.weight_decay}],
             "state": {},
@@ -152,6 +165,23 @@ class FusedAdamW:
             for name in ("master", "m", "v"):
                 getattr(g, name).copy_(src[name].to(getattr(g, name).device))
             self._publish_params(g)
+
+    def load_resharded(self, fetch, step: int) -> None:
+        """Fill this rank's shards of master weights and moments from state written under another sharding.
+        ``fetch(group_name, param_name, lo, hi)`` returns ``{"master", "m", "v"}`` for elements [lo, hi) of that
+        parameter as this rank's model holds it now (flattened), or ``None`` when the old state has no such parameter."""
+        self.step_count = int(step)
+        for g in self.groups:
+            lo_s, hi_s = g.shard_lo, g.shard_lo + g.shard_numel
+            for name, off, p in zip(g.param_names, g.offsets, g.params):
+                a, b = max(off, lo_s), min(off + p.numel(), hi_s)
+                if a >= b:
+                    continue
+                src = fetch(g.name, name, a - off, b - off)
+                if src is None:
+                    continue
+                for key in ("master", "m", "v"):
+                    getattr(g, key)[a - lo_s:b - lo_s].copy_(src[key].to(g.master.device))
 
     # -- step ------------------------------------------------------------------------------------
     def _reduce_grads(self, g: _FlatGroup) -> torch.Tensor:
@@ -173,6 +203,8 @@ class FusedAdamW:
     @torch.no_grad()
     def step(self, lr: Optional[float] = None) -> None:
         ext = _ext.ext()
+        for hook in self._pre_step_hooks:
+            hook(self, (), {})
         if lr is not None:
             self.lr = lr
             self.param_groups[0]["lr"] = lr
@@ -240,10 +272,11 @@ def build_optimizer(model: nn.Module, lr: float, weight_decay: float = 0.1, beta
         # TMA reduce-add across microbatches; vector parameters' autograd gradients are added at step time
         groups.append(_FlatGroup("dense", [p for _, p in dense], torch.float32,
                                  [not _no_decay(n, p) for n, p in dense], shard_group=dp_group, topology=topology,
-                                 axis="ddp"))
+                                 axis="ddp", param_names=[n for n, _ in dense]))
     if expert:
         groups.append(_FlatGroup("expert", [p for _, p in expert], torch.float32, [True] * len(expert),
-                                 shard_group=expert_dp_group, topology=topology, axis="edp"))
+                                 shard_group=expert_dp_group, topology=topology, axis="edp",
+                                 param_names=[n for n, _ in expert]))
         # an expert's gradient already sums the contributions of the `ep` ranks whose tokens it served; the
         # objective is the mean over all data-parallel ranks, so 1/ep is still missing after the edp average
         if topology is not None and dist.is_initialized() and topology.ep_size > 1:

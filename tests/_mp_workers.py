@@ -288,6 +288,163 @@ def trainer_ep_axis(rank, world, dp, ep, steps):
             "expert": blk.moe.w13.detach().double().flatten()[:32].tolist()}
 
 
+def _elastic_cfg(dp, ep):
+    from composed_mixture_of_experts_engine_b200.utils.config import MoEConfig
+
+    return MoEConfig.from_dict({
+        "model": dict(arch="moe_decoder", hidden_dim=32, num_layers=2, num_heads=2, num_experts=8, top_k=2,
+                      ffn_dim=48, vocab_size=128, sequence_length=16, dtype="float32", aux_loss_coeff=0.01,
+                      init_std=0.02),
+        "training": dict(micro_batch_size=2, gradient_accumulation_steps=1, global_batch_size=2 * dp, max_steps=50,
+                         warmup_steps=0, learning_rate=5e-3, grad_clip=1.0, seed=0),
+        "parallelism": dict(data_parallel=dp, expert_parallel=ep, tensor_parallel=1, pipeline_parallel=1,
+                            ep_from_dp=True)})
+
+
+def _expert_fingerprints(tr, num_experts):
+    """sha256 of every locally held expert's weights and Adam moments, keyed by global expert id, plus the
+    fingerprints of a few dense tensors and their moments."""
+    import hashlib
+
+    import torch
+
+    def sha(t):
+        return hashlib.sha256(t.detach().contiguous().cpu().numpy().tobytes()).hexdigest()
+
+    mine = tr.topology.experts_on_this_rank(num_experts)
+    state = tr.optimizer.state
+    out = {"experts": {}, "dense": {}}
+    for li, layer in enumerate(tr.model.moe_layers()):
+        for pname, p in (("w13", layer.w13), ("w2", layer.w2)):
+            st = state[p]
+            for j, e in enumerate(mine):
+                out["experts"][f"{li}.{pname}.{e}"] = [sha(p[j]), sha(st["exp_avg"][j]), sha(st["exp_avg_sq"][j])]
+    blk = tr.model.blocks[0]
+    for name, p in (("gate", blk.moe.router.gate_w), ("wqkv", blk.attn.wqkv.weight), ("embed", tr.model.embed.weight)):
+        st = state[p]
+        out["dense"][name] = [sha(p), sha(st["exp_avg"]), sha(st["exp_avg_sq"])]
+    return out
+
+
+def elastic_save(rank, world, ckpt_dir, steps):
+    """Phase 1 of the shrink test: dp = ep = world (ep carved from dp), a few steps, one checkpoint."""
+    import torch
+
+    from composed_mixture_of_experts_engine_b200.elastic.fault_monitor import ElasticConfig, ElasticTrainerHarness
+    from composed_mixture_of_experts_engine_b200.engine import Trainer
+
+    tr = Trainer(_elastic_cfg(world, world), device_type="cpu")
+    gen = torch.Generator().manual_seed(tr.topology.data_rank)
+    for _ in range(steps):
+        ids, tgt = tr.synthetic_batch(gen, pinned=False)
+        tr.train_step(ids, tgt)
+    h = ElasticTrainerHarness(ElasticConfig(ckpt_dir, None, async_workers=1), tr.topology)
+    h.checkpoint(tr.model, tr.optimizer, steps)
+    h.shutdown()
+    return _expert_fingerprints(tr, 8)
+
+
+def elastic_resume(rank, world, ckpt_dir):
+    """Phase 2: half as many ranks build the same model on the smaller mesh and resume from the files of phase 1."""
+    import math
+
+    import torch
+
+    from composed_mixture_of_experts_engine_b200.elastic.fault_monitor import ElasticConfig, ElasticTrainerHarness
+    from composed_mixture_of_experts_engine_b200.engine import Trainer
+
+    tr = Trainer(_elastic_cfg(world, world), device_type="cpu")
+    h = ElasticTrainerHarness(ElasticConfig(ckpt_dir, None, async_workers=1), tr.topology)
+    step = h.resume(tr.model, tr.optimizer, 8)
+    fp = _expert_fingerprints(tr, 8)
+    ids, tgt = tr.synthetic_batch(torch.Generator().manual_seed(tr.topology.data_rank), pinned=False)
+    loss = float(tr.train_step(ids, tgt))  # the re-assembled optimizer state is usable
+    h.shutdown()
+    return {"step": step, "fp": fp, "finite": math.isfinite(loss), "mine": tr.topology.experts_on_this_rank(8)}
+
+
+def _fused_optimizer_on_cpu(model, topo):
+    """The fused optimizer's flat groups built on CPU tensors (its step needs the CUDA kernels, its state layout,
+    sharding and state dict do not), with recognisable values in master / m / v: element i of a dense parameter
+    holds tag(name) + i / n; element i of expert e's slice holds tag(name) + 10 e + i / n."""
+    import zlib
+
+    import torch
+
+    from composed_mixture_of_experts_engine_b200.ops.optim import FusedAdamW, _FlatGroup
+    from composed_mixture_of_experts_engine_b200.parallel.mesh import ddp_process_group, edp_process_group
+
+    params = list(model.named_parameters())
+    dense = [(n, p) for n, p in params if not getattr(p, "is_expert_param", False)]
+    expert = [(n, p) for n, p in params if getattr(p, "is_expert_param", False)]
+    groups = [
+        _FlatGroup("dense", [p for _, p in dense], torch.float32, [True] * len(dense),
+                   shard_group=ddp_process_group(topo), topology=None, param_names=[n for n, _ in dense]),
+        _FlatGroup("expert", [p for _, p in expert], torch.float32, [True] * len(expert),
+                   shard_group=edp_process_group(topo), topology=None, param_names=[n for n, _ in expert])]
+    opt = FusedAdamW(groups, lr=1e-3)
+    mine = topo.experts_on_this_rank(8)
+
+    def expected(name, p):
+        tag = float(zlib.crc32(name.encode()) % 997)
+        if getattr(p, "is_expert_param", False):
+            per = p[0].numel()
+            return torch.cat([tag + 10.0 * e + torch.arange(per, dtype=torch.float32) / per for e in mine])
+        return tag + torch.arange(p.numel(), dtype=torch.float32) / p.numel()
+
+    return opt, expected
+
+
+def fused_reshard_save(rank, world, ckpt_dir):
+    """dp = ep = world (carved): dense state sharded over all ranks, expert state unsharded per owner."""
+    import torch
+
+    from composed_mixture_of_experts_engine_b200.elastic.fault_monitor import ElasticConfig, ElasticTrainerHarness
+    from composed_mixture_of_experts_engine_b200.engine import Trainer
+
+    tr = Trainer(_elastic_cfg(world, world), device_type="cpu", build_optim=False)
+    opt, expected = _fused_optimizer_on_cpu(tr.model, tr.topology)
+    for g in opt.groups:
+        full = torch.zeros(g.numel)
+        for n, off, p in zip(g.param_names, g.offsets, g.params):
+            full[off:off + p.numel()] = expected(n, p)
+        sl = slice(g.shard_lo, g.shard_lo + g.shard_numel)
+        g.master.copy_(full[sl])
+        g.m.copy_(full[sl] + 0.25)
+        g.v.copy_(full[sl] + 0.5)
+    opt.step_count = 11
+    h = ElasticTrainerHarness(ElasticConfig(ckpt_dir, None, async_workers=1), tr.topology)
+    h.checkpoint(tr.model, opt, 11)
+    h.shutdown()
+    return {"dense_shard_world": opt.groups[0].shard_world, "expert_shard_world": opt.groups[1].shard_world}
+
+
+def fused_reshard_load(rank, world, ckpt_dir):
+    import torch
+
+    from composed_mixture_of_experts_engine_b200.elastic.fault_monitor import ElasticConfig, ElasticTrainerHarness
+    from composed_mixture_of_experts_engine_b200.engine import Trainer
+
+    tr = Trainer(_elastic_cfg(world, world), device_type="cpu", build_optim=False)
+    opt, expected = _fused_optimizer_on_cpu(tr.model, tr.topology)
+    h = ElasticTrainerHarness(ElasticConfig(ckpt_dir, None, async_workers=1), tr.topology)
+    step = h.resume(tr.model, opt, 8)
+    h.shutdown()
+    worst = 0.0
+    for g in opt.groups:
+        full = torch.zeros(g.numel)
+        for n, off, p in zip(g.param_names, g.offsets, g.params):
+            full[off:off + p.numel()] = expected(n, p)
+        sl = slice(g.shard_lo, g.shard_lo + g.shard_numel)
+        covered = torch.zeros(g.numel, dtype=torch.bool)
+        for off, p in zip(g.offsets, g.params):
+            covered[off:off + p.numel()] = True  # alignment padding between parameters carries no state
+        mask = covered[sl]
+        for t, shift in ((g.master, 0.0), (g.m, 0.25), (g.v, 0.5)):
+            worst = max(worst, float(((t - (full[sl] + shift)) * mask).abs().max()))
+    return {"step": step, "opt_step": opt.step_count, "worst": worst, "dense_shard_world": opt.groups[0].shard_world}
+
+
 # -------------------------------------------------------------------------------------------------- GPU workers
 def _set_transport(transport):
     """"nccl", "auto" (peer memory, results pushed by the GEMM epilogues), "auto-pull" (peer memory, pulled) or

@@ -206,6 +206,43 @@ def test_lm_head_loss_matches_fp32_cross_entropy(with_main_grad):
         assert abs(float(lm_head_loss(h, w, tgt, 1.0 / n, chunk=256)) - float(loss)) < 1e-5
 
 
+def test_async_checkpoint_of_device_state_reuses_pinned_buffers_and_does_not_stall(tmp_path):
+    """Snapshot of a CUDA model + fused optimizer: the device-to-host copies run on a side stream into pinned
+    buffers that the second save reuses (no new pinned allocation), the optimizer's pre-step hook (not the save)
+    orders the next update after the copy, and what lands on disk is the state at the time of the save, not the
+    state after the update that was enqueued right behind it."""
+    from composed_mixture_of_experts_engine_b200.elastic.fault_monitor import AsyncCheckpointer, LocalNVMeAdapter
+    from composed_mixture_of_experts_engine_b200.ops.optim import build_optimizer
+
+    torch.manual_seed(21)
+    net = torch.nn.Sequential(torch.nn.Linear(512, 1024, bias=False), torch.nn.Linear(1024, 512, bias=False)
+                              ).cuda().to(torch.bfloat16)
+    opt = build_optimizer(net, lr=1e-2, weight_decay=0.0)
+    ck = AsyncCheckpointer(LocalNVMeAdapter(str(tmp_path / "l")), None, retention=4, workers=1)
+    want = {}
+    for step in (1, 2, 3):
+        for p in net.parameters():
+            p.main_grad.normal_()
+        opt.step()
+        want[step] = {k: v.detach().clone() for k, v in net.state_dict().items()}
+        master = opt.groups[0].master.clone()
+        ck.save(net, opt, step)
+        if step == 1:
+            first_allocs = ck._stager.allocations
+        # the very next update is enqueued while the copy may still be running; its hook must order it behind
+        for p in net.parameters():
+            p.main_grad.normal_()
+        opt.step()
+        ck._q.join()
+        got = ck.load_raw(step)
+        for k, v in want[step].items():
+            assert torch.equal(got["model"][k], v.cpu()), (step, k)
+        assert torch.equal(got["optim"]["groups"]["dense"]["master"], master.cpu())
+    assert first_allocs > 0 and ck._stager.allocations == first_allocs  # saves 2 and 3 reused the pinned set
+    assert len(opt._pre_step_hooks) == 1 and ck.last_d2h_ms > 0.0
+    ck.shutdown()
+
+
 def test_trainer_loss_decreases_and_is_deterministic():
     from composed_mixture_of_experts_engine_b200.engine import Trainer
     from composed_mixture_of_experts_engine_b200.utils.config import MoEConfig

@@ -139,6 +139,40 @@ def test_dense_parameters_stay_identical_when_ep_is_its_own_axis():
     assert a["losses"] != b["losses"]  # different data on the two ranks
 
 
+def test_elastic_shrink_4_to_2_ranks_re_owns_experts_and_adam_moments(tmp_path):
+    """Four ranks (dp = ep = 4, ep carved from dp) train and checkpoint; two ranks (dp = ep = 2) resume from those
+    files.  Every expert's weights AND Adam moments must arrive bit-identical at its new owner, dense tensors and
+    their moments likewise, and the next optimizer step must run."""
+    ckpt = str(tmp_path / "ckpt")
+    before = _spawn("elastic_save", 4, ckpt, 3, timeout=600)
+    after = _spawn("elastic_resume", 2, ckpt, timeout=600)
+    want = {}
+    for r in range(4):
+        want.update(before[r]["experts"])
+    assert len(want) == 2 * 2 * 8  # layers x tensors x experts
+    seen = {}
+    for r in range(2):
+        assert after[r]["step"] == 3 and after[r]["finite"]
+        assert after[r]["mine"] == list(range(4 * r, 4 * r + 4))
+        seen.update(after[r]["fp"]["experts"])
+        assert after[r]["fp"]["dense"] == before[0]["dense"]
+    assert seen == want
+
+
+def test_fused_optimizer_flat_shards_are_re_sliced_by_parameter_name(tmp_path):
+    """The fused optimizer keeps fp32 master weights and moments as flat shards (dense state cut over all
+    data-parallel ranks, expert state per owner).  Written by 4 ranks, read by 2: every element of every new shard
+    must be the value its (parameter, expert, index) had, wherever the old cut put it."""
+    ckpt = str(tmp_path / "ckpt")
+    before = _spawn("fused_reshard_save", 4, ckpt, timeout=600)
+    assert before[0]["dense_shard_world"] == 4 and before[0]["expert_shard_world"] == 1
+    after = _spawn("fused_reshard_load", 2, ckpt, timeout=600)
+    for r in range(2):
+        assert after[r]["step"] == 11 and after[r]["opt_step"] == 11
+        assert after[r]["dense_shard_world"] == 2
+        assert after[r]["worst"] == 0.0
+
+
 def test_moe_layer_tensor_parallel_matches_unsliced():
     res = _spawn("moe_layer_tp", 2)
     for r, out in res.items():

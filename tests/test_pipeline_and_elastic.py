@@ -125,6 +125,36 @@ def test_retention_and_remote_fallback(tmp_path):
     assert "ckpts/step=000005/rank=000000.pt" in local.list("ckpts/")
 
 
+def test_pruning_never_deletes_a_newer_step_that_is_still_being_written(tmp_path):
+    """Four writers, retention 1, a remote tier whose writes take a random few milliseconds: steps complete out of
+    order, and a worker that finishes step s prunes while step s+1 is half written.  The newest step must survive
+    in both tiers, and nothing older than the retained step may be left behind."""
+    import random
+    import time
+
+    class Jittery(LocalNVMeAdapter):
+        def put(self, key, payload):
+            time.sleep(random.Random(hash(key) & 0xFFFF).random() * 0.02)
+            super().put(key, payload)
+
+    m, opt = _model_and_opt()
+    local, remote = LocalNVMeAdapter(str(tmp_path / "l")), Jittery(str(tmp_path / "r"), use_odirect=False)
+    ck = AsyncCheckpointer(local, remote, retention=1, workers=4)
+    for s in range(1, 21):
+        ck.save(m, opt, s)
+    ck.shutdown()
+    assert ck.last_error is None
+    for store in (local, remote):
+        keys = store.list("ckpts/")
+        assert "ckpts/step=000020/rank=000000.pt" in keys and "ckpts/step=000020/rank=000000.meta.json" in keys
+        assert all(int(k.split("step=")[1][:6]) >= 17 for k in keys)  # stragglers of in-flight saves at most
+    m2, _ = _model_and_opt()
+    ck2 = AsyncCheckpointer(local, remote, workers=1)
+    assert ck2.latest_step() == 20
+    ck2.load(m2, None, 20)
+    ck2.shutdown()
+
+
 def test_save_does_not_wait_for_slow_storage(tmp_path):
     class Slow(LocalNVMeAdapter):
         def put(self, key, payload):

@@ -27,7 +27,7 @@ def _lib():
     fn = lib.cmoe_moe_plan_noalloc
     fn.restype = ctypes.c_int
     fn.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
-                   ctypes.c_int, ctypes.c_int, ctypes.c_longlong] + [ctypes.c_void_p] * 6 + \
+                   ctypes.c_int, ctypes.c_int, ctypes.c_longlong] + [ctypes.c_void_p] * 7 + \
                   [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]
     lib.cmoe_moe_plan_noalloc_words.restype = ctypes.c_size_t
     lib.cmoe_moe_plan_noalloc_words.argtypes = [ctypes.c_longlong, ctypes.c_int, ctypes.c_int, ctypes.c_int]
@@ -57,14 +57,16 @@ def test_noalloc_plan_matches_regular_entry_point(N, K, E, cap):
         ext.moe_plan(idx, K, E, 0, E, bool(per_k), cap, want["slot_row"], want["row_slot"], want["group_offsets"],
                      want["tile_group"], want["num_m_tiles"], want["counts_kept"], scratch, None)
         got = _outputs(N * K, E, cap_rows)
+        dropped = torch.zeros(1, device="cuda", dtype=torch.int32)
         err = ctypes.c_int(0)
         rc = lib.cmoe_moe_plan_noalloc(idx.data_ptr(), N * K, K, E, 0, E, per_k, cap, cap_rows,
                                        got["slot_row"].data_ptr(), got["row_slot"].data_ptr(),
                                        got["group_offsets"].data_ptr(), got["tile_group"].data_ptr(),
-                                       got["num_m_tiles"].data_ptr(), got["counts_kept"].data_ptr(), stream,
-                                       ctypes.byref(err))
+                                       got["num_m_tiles"].data_ptr(), got["counts_kept"].data_ptr(),
+                                       dropped.data_ptr(), stream, ctypes.byref(err))
         assert rc == CMOE_NOALLOC_OK and err.value == 0
         torch.cuda.synchronize()
+        assert int(dropped) == 0  # the row buffer was sized for the worst case
         for name in want:
             assert torch.equal(got[name], want[name]), f"call {call}: {name} differs"
         assert int(got["num_m_tiles"]) > 0
@@ -77,10 +79,15 @@ def test_noalloc_rejects_oversized_and_bad_arguments():
     t = torch.zeros(1024, device="cuda", dtype=torch.int32)
     p = t.data_ptr()
     err = ctypes.c_int(0)
-    rc = lib.cmoe_moe_plan_noalloc(p, n_slots, K, n_local, 0, n_local, 1, 4, 128 * 1024, p, p, p, p, p, p, None,
+    rc = lib.cmoe_moe_plan_noalloc(p, n_slots, K, n_local, 0, n_local, 1, 4, 128 * 1024, p, p, p, p, p, p, None, None,
                                    ctypes.byref(err))
     assert rc == CMOE_NOALLOC_TOO_LARGE
-    rc = lib.cmoe_moe_plan_noalloc(None, 16, 2, 4, 0, 4, 0, 0, 128, p, p, p, p, p, p, None, ctypes.byref(err))
+    rc = lib.cmoe_moe_plan_noalloc(None, 16, 2, 4, 0, 4, 0, 0, 128, p, p, p, p, p, p, None, None, ctypes.byref(err))
+    assert rc == CMOE_NOALLOC_BAD_ARGUMENT
+    # experts [3, 3 + 4) do not lie inside [0, 4); a negative capacity makes no sense either
+    rc = lib.cmoe_moe_plan_noalloc(p, 16, 2, 4, 3, 4, 0, 0, 128, p, p, p, p, p, p, None, None, ctypes.byref(err))
+    assert rc == CMOE_NOALLOC_BAD_ARGUMENT
+    rc = lib.cmoe_moe_plan_noalloc(p, 16, 2, 4, 0, 4, 1, -1, 128, p, p, p, p, p, p, None, None, ctypes.byref(err))
     assert rc == CMOE_NOALLOC_BAD_ARGUMENT
     torch.cuda.synchronize()
     assert int(t.abs().sum()) == 0  # nothing was launched

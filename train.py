@@ -166,14 +166,13 @@ def main(argv=None) -> int:
     harness.install_signal_handlers()
 
     start_step = 0
-    latest = harness.async_ckpt.latest_step()
-    if latest is not None:
-        try:
-            harness.async_ckpt.load(trainer.model, trainer.optimizer, latest, rank=rank)
+    try:
+        latest = harness.resume(trainer.model, trainer.optimizer, m.num_experts)
+        if latest is not None:
             start_step = latest + 1
             log.info("resumed from step %d", latest)
-        except Exception as exc:
-            log.warning("could not resume from step %s (%s); starting fresh", latest, exc)
+    except Exception as exc:
+        log.warning("could not resume (%s); starting fresh", exc)
     trainer.step_index = start_step
 
     # one data stream per data replica: tensor- and pipeline-parallel peers of a replica must see the same tokens
@@ -223,7 +222,14 @@ def main(argv=None) -> int:
             dead = harness.health_check()
             if dead:
                 log.warning("ranks %s stopped answering; recovering", dead)
-                new_topo = harness.recover(trainer.model, trainer.optimizer, m.num_experts)
+
+                def _rebuild(new_topology):
+                    # another expert-parallel degree means other expert tensors per rank: build the trainer anew
+                    nonlocal trainer
+                    trainer = Trainer(cfg, topology=new_topology)
+                    return trainer.model, trainer.optimizer
+
+                new_topo = harness.recover(trainer.model, trainer.optimizer, m.num_experts, rebuild=_rebuild)
                 trainer.topology = new_topo
 
     if t.max_steps > start_step:
