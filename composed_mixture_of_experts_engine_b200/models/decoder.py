@@ -85,7 +85,11 @@ class DecoderBlock(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         x = x + self.attn(self.attn_norm(x))
         h = self.norm(x)
-        if self.sequence_parallel:
+        if self.sequence_parallel and self.moe.fused_sequence_shard_path(h):
+            # peer-memory path: the layer takes the shard; the sequence gather is the row pull inside its first
+            # grouped GEMM, the reduce-scatter the row push of its second one
+            y = self.moe(h, sequence_shard=True)
+        elif self.sequence_parallel:
             group = tp_process_group(self.topology)
             full = C.all_gather(h, 1, group, reduce_scatter_grad=False)
             y = self.moe(full)  # replicated result (the layer all-reduces over TP)
@@ -232,8 +236,8 @@ class MoEDecoder(nn.Module):
         return [blk.moe for blk in self.blocks]
 
     def aux_losses(self) -> Tuple[torch.Tensor, torch.Tensor]:
-        aux = [l.router.last_aux_loss for l in self.moe_layers() if l.router.last_aux_loss is not None]
-        z = [l.router.last_z_loss for l in self.moe_layers() if l.router.last_z_loss is not None]
+        aux = [l.router.last_aux_loss * l.aux_scale for l in self.moe_layers() if l.router.last_aux_loss is not None]
+        z = [l.router.last_z_loss * l.aux_scale for l in self.moe_layers() if l.router.last_z_loss is not None]
         dev = next(self.parameters()).device
         zero = torch.zeros((), device=dev, dtype=torch.float32)
         n = max(self.num_layers_total, 1)

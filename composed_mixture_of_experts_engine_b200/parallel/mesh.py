@@ -34,6 +34,7 @@ __all__ = [
     "dp_process_group",
     "edp_process_group",
     "ddp_process_group",
+    "etp_process_group",
 ]
 
 _TP_GROUPS: Dict[Tuple[int, ...], "dist.ProcessGroup"] = {}
@@ -130,6 +131,11 @@ class ParallelTopology:
             if self.ep_from_dp:
                 return [self.rank_of(d, tp, pp) for d in range(self.dp_size) if d % self.ep_size == ep]
             return [self.rank_of(d, tp, pp, ep) for d in range(self.dp_size)]
+        if axis == "etp":  # expert-parallel x tensor-parallel block: ep-major, tp-minor (index = ep_rank * tp + tp_rank)
+            if self.ep_from_dp:
+                base = (dp // self.ep_size) * self.ep_size
+                return [self.rank_of(base + e, t, pp) for e in range(self.ep_size) for t in range(self.tp_size)]
+            return [self.rank_of(dp, t, pp, e) for e in range(self.ep_size) for t in range(self.tp_size)]
         if axis == "ddp":  # ranks that hold the same dense parameters and see different data
             if self.ep_from_dp:
                 return self.axis_ranks("dp")
@@ -234,14 +240,29 @@ def ddp_process_group(topology: ParallelTopology):
     return _axis_group(topology, "ddp", _DDP_GROUPS)
 
 
+_ETP_GROUPS: Dict[Tuple[int, ...], "dist.ProcessGroup"] = {}
+
+
+def etp_process_group(topology: ParallelTopology):
+    """The expert-parallel x tensor-parallel block of this rank: the ranks that together hold every (expert, FFN
+    slice) pair, over which the MoE layer exchanges token rows when sequence parallelism hands it sequence shards."""
+    return _axis_group(topology, "etp", _ETP_GROUPS)
+
+
 def _build_axis_groups(probe: ParallelTopology) -> AxisGroups:
     """Create every axis group of every rank, in an order that is the same on all ranks."""
     groups = AxisGroups()
     world = probe.world_size
-    for axis in ("dp", "tp", "pp", "ep", "edp", "ddp"):
+    for axis in ("dp", "tp", "pp", "ep", "edp", "ddp", "etp"):
         if axis == "ddp" and probe.ep_from_dp:  # the same ranks as "dp": share its communicator
             if "dp" in groups:
                 groups.add("ddp", groups.get_group("dp"), groups.ranks("dp"))
+            continue
+        if axis == "etp" and (probe.tp_size == 1 or probe.ep_size == 1):
+            # one of the two factors is trivial: the block is the other axis' group
+            other = "ep" if probe.tp_size == 1 else "tp"
+            if other in groups:
+                groups.add("etp", groups.get_group(other), groups.ranks(other))
             continue
         seen = set()
         for r in range(world):

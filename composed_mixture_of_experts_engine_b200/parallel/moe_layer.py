@@ -194,6 +194,7 @@ class DistributedMoELayer(nn.Module):
         self._last_n_slots = 0
         self._dropped_host: Optional[float] = 0.0
         self.force_library_path = False
+        self.aux_scale = 1.0  # factor on this layer's router loss terms (1/tp when the router sees sequence shards)
 
     # ---- telemetry (resolved lazily: reading these waits for the recorded events only) ----------
     def enable_timing(self, on: bool = True) -> None:
@@ -259,7 +260,51 @@ class DistributedMoELayer(nn.Module):
         return math.ceil(self.capacity_factor * n_tokens * self.top_k / self.num_experts)
 
     # ---- forward ----------------------------------------------------------------------------------
-    def forward(self, tokens: torch.Tensor) -> torch.Tensor:
+    def fused_sequence_shard_path(self, tokens: torch.Tensor) -> bool:
+        """True when the layer can take this rank's sequence shard directly under tensor + sequence parallelism:
+        CUDA bf16 tensors and peer memory over the expert-parallel x tensor-parallel block.  The gather of the
+        sequence and the reduce-scatter of the result then happen inside the grouped GEMM kernels
+        (``symm_peer.ep_moe_sequence_shard``) instead of as collectives around the layer."""
+        topo = self.topology
+        if topo.tp_size <= 1 or not dist.is_initialized() or self.force_library_path:
+            return False
+        if not (OF.on_device_path(tokens, self.w13, self.w2) and self._experts_are_views()):
+            return False
+        import os
+
+        if os.environ.get("CMOE_EP_TRANSPORT", "auto") == "nccl":
+            return False
+        from . import symm_peer
+
+        return symm_peer.available(topo, "etp")
+
+    def _forward_sequence_shard(self, tokens: torch.Tensor) -> torch.Tensor:
+        flat = tokens.reshape(-1, tokens.shape[-1])
+        topo = self.topology
+        # the router sees this rank's part of the sequence only: its gate gradient and its loss terms are partial
+        # sums over the tensor-parallel group (summed after the backward pass, like the norm weights' gradients)
+        self.router.gate_w.sequence_parallel_grad = True
+        self.aux_scale = 1.0 / topo.tp_size
+        idx, _w, _counts = self.router(flat)
+        gate_w = self.router.last_w32
+        N = flat.shape[0]
+        cap = self.capacity(N) if self.capacity_dropping else 0
+        self._last_n_slots = N * self.top_k * topo.tp_size
+        self._dropped_host = None if cap > 0 else 0.0
+        idx32 = self.router.last_idx32 if self.router.last_idx32 is not None else idx.to(torch.int32)
+        from . import symm_peer
+
+        expert_lo = self.local_expert_ids[0] if self.local_expert_ids else 0
+        y = symm_peer.ep_moe_sequence_shard(self, flat.contiguous(), gate_w.float().contiguous(),
+                                            idx32.to(torch.int32).contiguous(), cap, expert_lo)
+        return y.reshape(tokens.shape)
+
+    def forward(self, tokens: torch.Tensor, sequence_shard: bool = False) -> torch.Tensor:
+        """``sequence_shard=True``: ``tokens`` is this rank's shard of a sequence that is split over the
+        tensor-parallel group and the result is the same shard of the output (only where
+        :meth:`fused_sequence_shard_path` holds); otherwise every tensor-parallel rank passes the same tokens."""
+        if sequence_shard:
+            return self._forward_sequence_shard(tokens)
         if tokens.dim() == 3:
             B, S, H = tokens.shape
             flat = tokens.reshape(B * S, H)

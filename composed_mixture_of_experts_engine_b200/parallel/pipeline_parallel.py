@@ -48,6 +48,7 @@ class PipelineStage:
         self._multi_process = topology is not None and topology.pp_size > 1 and dist.is_initialized()
         self._pp_group = pp_process_group(topology) if self._multi_process else None
         self._activation_stash: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
+        self._sends_in_flight: List[Tuple[list, list]] = []
 
     # ---- position -----------------------------------------------------------------------------
     @property
@@ -74,20 +75,38 @@ class PipelineStage:
 
     # ---- transport ----------------------------------------------------------------------------
     def _exchange(self, send_prev=None, send_next=None, recv_prev=None, recv_next=None) -> None:
-        """Post all given sends / receives as one batch and wait for them."""
-        ops = []
+        """Post all given sends / receives as one batch.  A batch that receives something is waited for at once
+        (the caller needs the data next); a batch of sends only is left in flight and collected at the next
+        exchange, so the compute stream does not stall on a neighbour that has not posted its receive yet and the
+        transfer overlaps the compute that follows.  The sent tensors stay referenced until then."""
+        ops, keep = [], []
         if send_prev is not None:
-            ops.append(dist.P2POp(dist.isend, send_prev.contiguous(), self._prev_rank()))
+            t = send_prev.contiguous()
+            keep.append(t)
+            ops.append(dist.P2POp(dist.isend, t, self._prev_rank()))
         if recv_prev is not None:
             ops.append(dist.P2POp(dist.irecv, recv_prev, self._prev_rank()))
         if send_next is not None:
-            ops.append(dist.P2POp(dist.isend, send_next.contiguous(), self._next_rank()))
+            t = send_next.contiguous()
+            keep.append(t)
+            ops.append(dist.P2POp(dist.isend, t, self._next_rank()))
         if recv_next is not None:
             ops.append(dist.P2POp(dist.irecv, recv_next, self._next_rank()))
         if not ops:
             return
-        for req in dist.batch_isend_irecv(ops):
+        self._collect_sends()
+        reqs = dist.batch_isend_irecv(ops)
+        if recv_prev is None and recv_next is None:
+            self._sends_in_flight.append((reqs, keep))
+            return
+        for req in reqs:
             req.wait()
+
+    def _collect_sends(self) -> None:
+        pending, self._sends_in_flight = self._sends_in_flight, []
+        for reqs, _keep in pending:
+            for req in reqs:
+                req.wait()
 
     _HEADER_DTYPES = (torch.float32, torch.bfloat16, torch.float16, torch.float64, torch.int64, torch.int32)
     _HEADER_LEN = 12  # count, dtype code, rank, up to 9 extents
@@ -121,6 +140,7 @@ class PipelineStage:
             out = self.module(x) if self.module is not None else x
             if not self.is_last:
                 self._exchange(send_next=out.detach())
+                self._collect_sends()
             return out
         return self.module(micro_batch) if self.module is not None else micro_batch
 
@@ -177,6 +197,7 @@ class PipelineStage:
         if m == 0:
             if announce and self.is_first and not self.is_last:
                 self._send_header(0, (), torch.float32, device)
+            self._collect_sends()
             return [], []
         if not self.is_first:
             if activation_shape is None:
@@ -259,4 +280,5 @@ class PipelineStage:
                 self._exchange(recv_next=grad_buf)
             gin = bwd(i, grad_buf)
             self._exchange(send_prev=gin)
+        self._collect_sends()
         return outputs, losses

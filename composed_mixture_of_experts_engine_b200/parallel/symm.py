@@ -25,10 +25,10 @@ _DISABLED_REASON: Optional[str] = None
 
 
 def _axis_group(topo: ParallelTopology, axis: str):
-    from .mesh import ddp_process_group, edp_process_group
+    from .mesh import ddp_process_group, edp_process_group, etp_process_group
 
     return {"ep": ep_process_group, "tp": tp_process_group, "dp": dp_process_group,
-            "edp": edp_process_group, "ddp": ddp_process_group}[axis](topo)
+            "edp": edp_process_group, "ddp": ddp_process_group, "etp": etp_process_group}[axis](topo)
 
 
 def enabled_for(topo: Optional[ParallelTopology], axis: str) -> bool:

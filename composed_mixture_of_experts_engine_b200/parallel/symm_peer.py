@@ -50,8 +50,6 @@ _FAILED: Optional[str] = None
 def available(topology: Optional[ParallelTopology], axis: str) -> bool:
     if _FAILED is not None or not symm.enabled_for(topology, axis):
         return False
-    if topology.pp_size > 1:
-        return False  # several microbatches of one layer are in flight under 1F1B; per-layer buffers assume one
     return 1 < topology.axis_size(axis) <= 16
 
 
@@ -66,11 +64,15 @@ def _fused() -> bool:
 
 
 class _EPContext:
-    """Symmetric buffers, flag words and the barrier epoch of one expert-parallel group."""
+    """Symmetric buffers, flag words and the barrier epoch of one token-exchange group: the expert-parallel group
+    (``axis="ep"``), or the expert-parallel x tensor-parallel block (``axis="etp"``) when the layer is handed
+    sequence shards and every (expert, FFN slice) pair acts as an expert of its own."""
 
-    def __init__(self, topo: ParallelTopology):
+    def __init__(self, topo: ParallelTopology, axis: str = "ep"):
         self.topo = topo
-        self.group = symm.group_for(topo, "ep")
+        self.axis = axis
+        self.slices = topo.tp_size if axis == "etp" else 1  # FFN slices per expert inside this group
+        self.group = symm.group_for(topo, axis)
         self.rank, self.world = self.group.rank, self.group.world
         self.flags = self.group.flags
         self.flag_ptrs = self.flags.ptrs()
@@ -99,11 +101,14 @@ class _EPContext:
         return buf
 
     def expert_rank_table(self, num_experts: int) -> torch.Tensor:
+        """Group rank that owns each of the ``num_experts * slices`` exchange-level experts: expert ``g`` sliced
+        ``j`` carries the id ``j * num_experts + g`` and lives on group rank ``owner(g) * slices + j``."""
         t = self.expert_rank.get(num_experts)
         if t is None:
-            owner = []
-            for r in range(self.world):
-                owner += [r] * len(self.topo.experts_on_rank(num_experts, r))
+            by_expert = []
+            for r in range(self.topo.ep_size):
+                by_expert += [r] * len(self.topo.experts_on_rank(num_experts, r))
+            owner = [by_expert[g] * self.slices + j for j in range(self.slices) for g in range(num_experts)]
             t = torch.tensor(owner, dtype=torch.int32, device=self.topo.device)
             self.expert_rank[num_experts] = t
         return t
@@ -113,11 +118,11 @@ _CONTEXTS: Dict[tuple, _EPContext] = {}
 _LAYER_KEYS: Dict[int, int] = {}
 
 
-def _context(topo: ParallelTopology) -> _EPContext:
-    key = tuple(topo.axis_ranks("ep"))
+def _context(topo: ParallelTopology, axis: str = "ep") -> _EPContext:
+    key = (axis,) + tuple(topo.axis_ranks(axis))
     ctx = _CONTEXTS.get(key)
     if ctx is None:
-        ctx = _EPContext(topo)
+        ctx = _EPContext(topo, axis)
         _CONTEXTS[key] = ctx
     return ctx
 
@@ -137,8 +142,11 @@ def _ptrs(buf: symm.SymmBuffer) -> List[int]:
 
 class _EPMoEPeer(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, gate_w32, idx32, w13, w2, pc: _EPContext, lkey: int, expert_lo, num_experts, capacity,
+    def forward(ctx, x, gate_w32, idx32, w13, w2, pc: _EPContext, lkey, expert_lo, num_experts, capacity,
                 holder):
+        # ``num_experts`` / ``expert_lo`` / ``idx32`` are exchange-level: with FFN slices as experts of their own
+        # they count (expert, slice) pairs.  ``lkey`` = (layer, in-flight slot): the buffers that the backward
+        # reads again exist once per microbatch that a pipeline stage can hold between forward and backward
         ext = _ext.ext()
         T, H = x.shape
         K = idx32.shape[1]
@@ -163,7 +171,7 @@ class _EPMoEPeer(torch.autograd.Function):
                                 cap_rows=cap_rows, slot_row_out=srow.view(torch.int32, ep * T * K))
         xp = torch.empty(cap_rows, H, device=dev, dtype=torch.bfloat16)
         push = _push()
-        erank = pc.expert_rank_table(num_experts)
+        erank = pc.expert_rank_table(num_experts // pc.slices)
         y = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
         if push:
             ycs = pc.per_layer(lkey, "ycomb", T * K * H * 2)
@@ -206,7 +214,7 @@ class _EPMoEPeer(torch.autograd.Function):
         pc.barrier()
 
         srow = pc.per_layer(lkey, "slot_row", pc.world * T * K * 4)
-        erank = pc.expert_rank_table(ctx.num_experts)
+        erank = pc.expert_rank_table(ctx.num_experts // pc.slices)
         push = ctx.push
         slot_base = pc.rank * T * K
         d_gate = None
@@ -243,6 +251,16 @@ class _EPMoEPeer(torch.autograd.Function):
         return dx, d_gate, None, dw13, dw2, None, None, None, None, None, None
 
 
+def _in_flight_slot(layer) -> int:
+    """Which of the layer's buffer sets this forward uses.  Under a 1F1B pipeline a stage runs up to ``pp`` forward
+    passes of a layer before the first of their backward passes, so the tables and result rows that a backward pass
+    reads again exist ``pp`` times and are handed out round-robin (backward passes run in forward order)."""
+    n = max(1, layer.topology.pp_size)
+    k = getattr(layer, "_peer_forward_calls", 0)
+    layer._peer_forward_calls = k + 1
+    return k % n if torch.is_grad_enabled() else n  # evaluation passes keep out of the training slots
+
+
 def ep_moe(layer, flat: torch.Tensor, gate_w32: torch.Tensor, idx32: torch.Tensor, capacity: int, expert_lo: int
            ) -> torch.Tensor:
     global _FAILED
@@ -252,5 +270,36 @@ def ep_moe(layer, flat: torch.Tensor, gate_w32: torch.Tensor, idx32: torch.Tenso
         _FAILED = f"{type(exc).__name__}: {exc}"
         raise
     with layer._timer.phase("experts"):
-        return _EPMoEPeer.apply(flat, gate_w32, idx32, layer.w13, layer.w2, pc, _layer_key(layer), expert_lo,
-                                layer.num_experts, capacity, layer._last_plan_holder)
+        return _EPMoEPeer.apply(flat, gate_w32, idx32, layer.w13, layer.w2, pc,
+                                (_layer_key(layer), _in_flight_slot(layer)), expert_lo, layer.num_experts, capacity,
+                                layer._last_plan_holder)
+
+
+def ep_moe_sequence_shard(layer, shard: torch.Tensor, gate_w32: torch.Tensor, idx32: torch.Tensor, capacity: int,
+                          expert_lo: int) -> torch.Tensor:
+    """The layer under tensor + sequence parallelism, fed this rank's sequence shard ``shard`` [T_local, H] and its
+    routing (``idx32`` / ``gate_w32`` [T_local, K]); returns the finished output rows of the same shard.
+
+    Every (expert, FFN slice) pair is treated as an expert of its own: slice ``j`` of expert ``g`` gets the id
+    ``j * E + g`` and lives on rank (owner(g), j) of the expert-parallel x tensor-parallel block.  A token routed to
+    expert ``g`` is then routed to all ``tp`` slices of ``g`` with the same gate weight, and the weighted sum over
+    its ``tp * K`` result rows is at once the top-k combine and the sum over the FFN slices.  With that, the
+    sequence all-gather in front of the experts is the row pull inside the first grouped GEMM (each rank fetches the
+    rows it needs from whichever rank holds that part of the sequence), and the reduce-scatter behind them is the
+    row push of the second GEMM's epilogue followed by the local weighted sum: no separate collective, nothing
+    replicated, and the router runs on the shard only."""
+    global _FAILED
+    topo = layer.topology
+    try:
+        pc = _context(topo, "etp")
+    except Exception as exc:
+        _FAILED = f"{type(exc).__name__}: {exc}"
+        raise
+    tp, E = topo.tp_size, layer.num_experts
+    shift = torch.arange(tp, device=idx32.device, dtype=torch.int32).repeat_interleave(idx32.shape[1]) * E
+    idx_eff = (idx32.repeat(1, tp) + shift[None, :]).contiguous()
+    w_eff = gate_w32.repeat(1, tp)  # differentiable: the gradient of a gate weight sums over the slices
+    with layer._timer.phase("experts"):
+        return _EPMoEPeer.apply(shard, w_eff, idx_eff, layer.w13, layer.w2, pc,
+                                (_layer_key(layer), _in_flight_slot(layer)), topo.tp_rank * E + expert_lo, E * tp,
+                                capacity, layer._last_plan_holder)

@@ -503,6 +503,69 @@ def gpu_ep_layer(rank, world, transport):
     return out
 
 
+def gpu_moe_sequence_shard(rank, world, ep, tp):
+    """The MoE layer under tensor + sequence parallelism fed sequence shards (peer memory over the ep x tp block,
+    FFN slices routed as experts of their own) vs the unsliced layer with all experts on one GPU."""
+    import torch
+    import torch.distributed as dist
+
+    os.environ["CMOE_EP_TRANSPORT"] = "auto"
+    from composed_mixture_of_experts_engine_b200.ops.kernels import check_status
+    from composed_mixture_of_experts_engine_b200.parallel import DistributedMoELayer, build_topology
+    from composed_mixture_of_experts_engine_b200.parallel.mesh import tp_process_group
+
+    H, F, E, K, T = 256, 512, 8, 2, 1024  # T tokens per data replica (= per expert-parallel rank)
+    topo = build_topology(ep, ep, tp_size=tp, device_type="cuda", ep_from_dp=True)
+    dev = topo.device
+    torch.manual_seed(0)
+    full = DistributedMoELayer(H, F, E, K, dtype=torch.bfloat16).to(dev)
+    layer = DistributedMoELayer(H, F, E, K, topology=topo, dtype=torch.bfloat16).to(dev)
+    mine = topo.experts_on_this_rank(E)
+    e0, e1 = mine[0], mine[-1] + 1
+    fl, j = F // tp, topo.tp_rank
+    with torch.no_grad():
+        layer.router.gate_w.copy_(full.router.gate_w)
+        layer.w13[:, :fl].copy_(full.w13[e0:e1, j * fl:(j + 1) * fl])          # gate rows of this slice
+        layer.w13[:, fl:].copy_(full.w13[e0:e1, F + j * fl:F + (j + 1) * fl])  # up rows of this slice
+        layer.w2.copy_(full.w2[e0:e1, :, j * fl:(j + 1) * fl])
+    rel = lambda a, b: float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
+    out = {"fused": bool(layer.fused_sequence_shard_path(torch.empty(1, H, device=dev, dtype=torch.bfloat16)))}
+    T_l = T // tp
+    for it in range(2):  # twice: buffers, flags and in-flight slots are reused
+        xs, dys = [], []
+        for d in range(ep):  # every data replica's tokens, so that each rank can form the reference gradients
+            torch.manual_seed(100 + d + 10 * it)
+            xs.append(torch.randn(T, H, device=dev, dtype=torch.bfloat16))
+            dys.append(torch.randn(T, H, device=dev, dtype=torch.bfloat16))
+        d = topo.dp_rank
+        x = xs[d][j * T_l:(j + 1) * T_l].clone().requires_grad_(True)
+        dy = dys[d][j * T_l:(j + 1) * T_l]
+        for l in (layer, full):
+            l.zero_grad(set_to_none=True)
+        y = layer(x, sequence_shard=True)
+        y.backward(dy)
+        gate_grad = layer.router.gate_w.grad.float().clone()
+        dist.all_reduce(gate_grad, group=tp_process_group(topo))  # partial per sequence shard
+        x_all = torch.cat(xs).requires_grad_(True)
+        y_all = full(x_all)
+        y_all.backward(torch.cat(dys))
+        lo = d * T + j * T_l
+        out[f"y{it}"] = rel(y, y_all[lo:lo + T_l])
+        out[f"dx{it}"] = rel(x.grad, x_all.grad[lo:lo + T_l])
+        g13, g2 = full.w13.grad, full.w2.grad
+        want13 = torch.cat([g13[e0:e1, j * fl:(j + 1) * fl], g13[e0:e1, F + j * fl:F + (j + 1) * fl]], dim=1)
+        out[f"dw13_{it}"] = rel(layer.w13.grad, want13)
+        out[f"dw2_{it}"] = rel(layer.w2.grad, g2[e0:e1, :, j * fl:(j + 1) * fl])
+        # the reference's gate gradient covers all replicas' tokens; sum this replica's over the data replicas too
+        if ep > 1:
+            from composed_mixture_of_experts_engine_b200.parallel.mesh import ep_process_group
+
+            dist.all_reduce(gate_grad, group=ep_process_group(topo))
+        out[f"dgate{it}"] = rel(gate_grad, full.router.gate_w.grad)
+    check_status(dev)
+    return out
+
+
 def gpu_trainer(rank, world, transport, steps):
     """Trainer on `world` GPUs (dp = ep = world, sharded optimizer): finite decreasing loss, replicas in sync."""
     import torch

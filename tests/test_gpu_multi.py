@@ -76,6 +76,19 @@ def test_sequence_parallel_linears_on_peer_memory(transport):
             assert v < 4e-2, (r, k, v, out)
 
 
+def test_moe_layer_takes_sequence_shards_over_the_ep_x_tp_block():
+    """tp = 2 (and ep = 2 with four GPUs): every (expert, FFN slice) pair is an expert of its own in the exchange, so the
+    sequence gather and the reduce-scatter around the layer happen inside its grouped GEMM kernels."""
+    world = _world()
+    ep = world // 2
+    res = _spawn_gpu("gpu_moe_sequence_shard", world, ep, 2)
+    for r, out in res.items():
+        assert out.pop("fused")
+        for k, v in out.items():
+            tol = 6e-2 if k.startswith("dgate") else 3e-2
+            assert v < tol, (r, k, v, out)
+
+
 def test_trainer_pipeline_parallel_on_gpus():
     """Two pipeline stages over NCCL (1F1B, 4 microbatches), bf16 kernels and the fused optimizer on every stage; with
     four GPUs also tensor + sequence parallelism inside each stage."""
