@@ -47,13 +47,24 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--impl", choices=["ours", "reference", "library"], default="ours",
+                    help="ours: this repository's kernels; reference: the unmodified reference package; library: this "
+                         "repository's model with every hot op on NVIDIA / PyTorch library kernels (cuBLAS per expert, "
+                         "NCCL all-to-all, fused attention from the library, eager norms, torch.optim.AdamW)")
     ap.add_argument("--config", default=str(ROOT / "configs" / "olmoe_1b7b.yaml"))
     ap.add_argument("--micro-batch", type=int, default=MICRO_BATCH)
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
     ap.add_argument("--keep-mesh", action="store_true",
                     help="keep the configuration's own dp / ep / tp / pp mesh (its world size must equal the number "
                          "of ranks) instead of dp = ep = N; for configurations other than the headline one")
+    ap.add_argument("--mesh", default=None, metavar="DP,EP,TP,PP",
+                    help="with --keep-mesh: override the configuration's mesh (ep carved from dp), e.g. 1,1,2,2")
+    ap.add_argument("--layers", type=int, default=0, help="override the number of layers (a proxy run, not a headline)")
+    ap.add_argument("--ckpt-dir", default=None,
+                    help="take one asynchronous checkpoint (pinned snapshot + background write to this directory) "
+                         "inside the end-to-end timed region and report what it cost")
+    ap.add_argument("--ckpt-step", type=int, default=1, help="index of the timed step after which the checkpoint is taken")
+    ap.add_argument("--ckpt-model-only", action="store_true", help="checkpoint the bf16 weights only (no optimizer state)")
     ap.add_argument("--tiny", action="store_true",
                     help="self-test of the reference arm with toy dimensions (runs on CPU too); never a bench value")
     return ap.parse_args()
@@ -178,11 +189,24 @@ def run_ours(args) -> dict:
     from composed_mixture_of_experts_engine_b200.utils.config import MoEConfig
     from composed_mixture_of_experts_engine_b200.utils.mfu import exact_train_flops_per_token
 
+    library = args.impl == "library"
+    if library:
+        # every hot op on library kernels: the differentiable ops take their PyTorch paths, the exchanges NCCL
+        os.environ["CMOE_FORCE_LIBRARY"] = "1"
+        os.environ["CMOE_EP_TRANSPORT"] = os.environ["CMOE_DP_TRANSPORT"] = "nccl"
+        os.environ["CMOE_DISABLE_PEER_KERNELS"] = "1"
     rank, world = init_distributed("cuda")
     n = world
     cfg = MoEConfig.from_yaml(args.config)
     d = cfg.to_dict()
     accum = max(1, args.seqs_per_gpu // args.micro_batch)
+    if args.layers > 0:
+        d["model"]["num_layers"] = args.layers
+    if args.keep_mesh and args.mesh:
+        dp_, ep_, tp_, pp_ = (int(v) for v in args.mesh.split(","))
+        d["parallelism"].update(data_parallel=dp_, expert_parallel=ep_, tensor_parallel=tp_, pipeline_parallel=pp_,
+                                ep_from_dp=True)
+        cfg = MoEConfig.from_dict(d)
     if args.keep_mesh:
         if cfg.parallelism.world_size != n:
             raise SystemExit(f"--keep-mesh: {args.config} describes {cfg.parallelism.world_size} ranks, started {n}")
@@ -208,11 +232,18 @@ def run_ours(args) -> dict:
         return trainer.train_step(ids, tgt)
 
     losses = []
+    ckpt = None
+    if args.ckpt_dir:
+        from composed_mixture_of_experts_engine_b200.elastic.fault_monitor import AsyncCheckpointer, LocalNVMeAdapter
+
+        ckpt = AsyncCheckpointer(LocalNVMeAdapter(args.ckpt_dir), None, retention=1, workers=2)
 
     def e2e_step(i):
         ids, tgt = host[i % n_batches]
         loss = trainer.train_step(ids, tgt)  # H2D copy of the pinned batch happens inside
         losses.append(float(loss.item()))     # D2H read of the step result
+        if ckpt is not None and i == args.ckpt_step:
+            ckpt.save(trainer.model, None if args.ckpt_model_only else trainer.optimizer, 1000 + i, rank=rank)
 
     for i in range(args.warmup):
         dev_step(i)
@@ -227,6 +258,34 @@ def run_ours(args) -> dict:
     from composed_mixture_of_experts_engine_b200.ops.kernels import check_status
 
     check_status(dev)
+    # the same step with this package's own attention kernels instead of the library's (or the other way round when
+    # CMOE_ATTN_SM100=1 selected them for the main measurement): two untimed steps, then a short timed region
+    attn_alt = None
+    if not library and not args.keep_mesh:
+        main_own = os.environ.get("CMOE_ATTN_SM100", "0") == "1"
+        os.environ["CMOE_ATTN_SM100"] = "0" if main_own else "1"
+        try:
+            for i in range(2):
+                dev_step(i)
+            k_alt = max(2, min(args.steps, 4))
+            ms_alt = timed_region(dev_step, k_alt, dev)
+            attn_alt = {"attention": "library (cuDNN fused attention)" if main_own else
+                        "hand-written tcgen05 kernels (csrc/attention_fwd2.cu, csrc/attention.cu)",
+                        "value": trainer.tokens_per_step_per_rank * n / (ms_alt / k_alt / 1e3), "unit": "tokens/s",
+                        "steps": k_alt, "ms_per_step": ms_alt / k_alt}
+        finally:
+            os.environ["CMOE_ATTN_SM100"] = "1" if main_own else "0"
+        check_status(dev)
+    ckpt_info = None
+    if ckpt is not None:
+        t0 = time.perf_counter()
+        ckpt.shutdown(drain=True)  # outside the timed region: wait for the background write to finish
+        files = list(Path(args.ckpt_dir).rglob(f"rank={rank:06d}.pt"))
+        ckpt_info = {"async_ckpt_commit_ms": ckpt.last_commit_ms, "snapshot_d2h_ms": ckpt.last_d2h_ms,
+                     "background_write_ms": ckpt.last_write_ms, "drain_wait_after_timing_s": time.perf_counter() - t0,
+                     "bytes_this_rank": files[0].stat().st_size if files else 0,
+                     "what": "bf16 weights" if args.ckpt_model_only else "bf16 weights + fp32 master / moments shard",
+                     "error": repr(ckpt.last_error) if ckpt.last_error else None}
 
     tokens_step = trainer.tokens_per_step_global if args.keep_mesh else trainer.tokens_per_step_per_rank * n
     per_step_ms = ms_dev / args.steps
@@ -251,7 +310,7 @@ def run_ours(args) -> dict:
         "vs_baseline": None,
         "dtype": "bf16",
         "data": "synthetic uniform-random token ids; random-init weights N(0,0.02)",
-        "impl": "ours",
+        "impl": args.impl,
         "config": {
             "model": ("OLMoE-1B-7B-shaped (V50304 d2048 L16 h16 S4096 E64 F1024 top8, aux 0.01)"
                       if Path(args.config).name == "olmoe_1b7b.yaml" else
@@ -266,11 +325,16 @@ def run_ours(args) -> dict:
             "parallelism": (f"dp{n} x ep{n} (ep carved from dp), sharded optimizer state" if not args.keep_mesh else
                             f"dp{cfg.parallelism.data_parallel} x ep{cfg.parallelism.expert_parallel} x "
                             f"tp{cfg.parallelism.tensor_parallel} x pp{cfg.parallelism.pipeline_parallel}"),
-            "optimizer": "AdamW fp32 master + moments, global-norm clip 1.0",
+            "optimizer": ("torch.optim.AdamW on the bf16 parameters, clip_grad_norm_ 1.0" if library else
+                          "AdamW fp32 master + moments, global-norm clip 1.0"),
             "attention": ("hand-written tcgen05 kernels (CMOE_ATTN_SM100=1)"
-                          if os.environ.get("CMOE_ATTN_SM100", "0") == "1" else "library (cuDNN fused attention)"),
-            "dense_gemms": "hand-written two-SM tcgen05 GEMM (attention projections, LM head: forward, input and "
-                           "weight gradients)",
+                          if os.environ.get("CMOE_ATTN_SM100", "0") == "1" and not library
+                          else "library (cuDNN fused attention)"),
+            "dense_gemms": ("library (cuBLAS through F.linear)" if library else
+                            "hand-written two-SM tcgen05 GEMM (attention projections, LM head: forward, input and "
+                            "weight gradients)"),
+            "experts_and_exchange": ("library: cuBLAS per expert, NCCL all-to-all" if library else
+                                     "grouped tcgen05 GEMMs with the dispatch / combine transfers inside them"),
             "l2": "no explicit flush: every microbatch streams 13.8 GB of bf16 weights and >1 GB of activations "
                   "per layer, far larger than the 126 MB L2",
         },
@@ -284,6 +348,10 @@ def run_ours(args) -> dict:
         "clocks": clocks,
         "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30,
     }
+    if ckpt_info is not None:
+        out["checkpoint_in_timed_region"] = ckpt_info
+    if attn_alt is not None:
+        out["same_step_other_attention"] = attn_alt
     return out if rank == 0 else {}
 
 
@@ -437,7 +505,7 @@ def main():
     if not torch.cuda.is_available() and not (args.impl == "reference" and args.tiny):
         print(json.dumps({"impl": args.impl, "unavailable": "no CUDA device"}))
         return 0
-    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    out = run_reference(args) if args.impl == "reference" else run_ours(args)  # "library" shares run_ours
     rank = int(os.environ.get("RANK", "0"))
     if out and (rank == 0 or "unavailable" in out and rank == 0):
         print(json.dumps(out))

@@ -9,6 +9,12 @@ epilogues) it reports the device time of the layer, and next to it the time of t
 already local (no transfers): the difference is the exposed dispatch + combine cost per layer, the number the
 reference's design documents target at < 0.6-0.8 ms (docs/benchmarks.md:284-291) without measuring it.
 
+Roofline per transport: ``max(expert FLOPs of this rank / measured bf16 peak, NVLink bytes into this GPU / link
+rate)`` with the bytes counted from the row plan (rows whose token lives on another rank, once for the dispatch and
+once for the combine; twice that for forward + backward) and ``--link-gbs`` as the per-direction link rate (default
+770, the measured peer-copy rate of this pool; 900 nominal).  ``standalone`` times the two transfers as kernels of
+their own (``gather_rows_peer`` / ``combine_rows_peer`` on the same plan) against bytes / link rate.
+
 All times are CUDA-event times on the launching stream, median of ``--iters`` after ``--warmup`` runs, maximum over
 ranks; an L2-sized buffer is overwritten between iterations.  ``--zipf s`` skews the routing (expert popularity
 ~ 1 / rank^s) by shifting the inputs along the gate columns.
@@ -61,7 +67,8 @@ def main() -> int:
     ap.add_argument("--zipf", type=float, default=0.0)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--transports", default="nccl,peer,peer-push")
+    ap.add_argument("--transports", default="nccl,peer-push,peer")
+    ap.add_argument("--link-gbs", type=float, default=770.0)
     args = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -117,6 +124,67 @@ def main() -> int:
         check_status(dev)
         out["transports"][name] = {"fwd_ms": f, "fwd_bwd_ms": fb}
 
+    # ---- rooflines from the plan of the last forward --------------------------------------------------------
+    peak = 1590.0
+    pk = ROOT / "MEASURED_PEAKS.json"
+    if pk.exists():
+        peak = float(json.loads(pk.read_text()).get("bf16_tflops", peak))
+    plan = layer._last_plan_holder.get("plan") if world > 1 else None
+    if plan is not None:
+        n_rows = int(plan.num_m_tiles) * 128
+        rs = plan.row_slot[:n_rows]
+        kept = rs >= 0
+        remote = int((kept & ((rs // (T * K)) != rank)).sum())
+        real = int(kept.sum())
+        flops_fwd = 2.0 * real * 3 * H * F  # gate, up, down projections of the rows this rank serves
+        link = args.link_gbs * 1e9
+        x_bytes = remote * H * 2            # dispatch: token rows in;  combine: as many result rows out / in
+        out["plan"] = {"rows_served": real, "rows_from_other_ranks": remote, "dispatch_bytes_in": x_bytes,
+                       "combine_bytes": x_bytes, "expert_flops_fwd": flops_fwd, "bf16_peak_tflops": peak,
+                       "link_gb_per_s": args.link_gbs}
+        roof_f = max(flops_fwd / (peak * 1e12), 2 * x_bytes / link) * 1e3
+        roof_fb = max(3 * flops_fwd / (peak * 1e12), 4 * x_bytes / link) * 1e3
+        for red in ("roof_f", "roof_fb"):  # the slowest rank sets the layer time: take the largest roofline too
+            t = torch.tensor([roof_f if red == "roof_f" else roof_fb], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            if red == "roof_f":
+                roof_f = float(t.item())
+            else:
+                roof_fb = float(t.item())
+        out["roofline"] = {"fwd_ms": roof_f, "fwd_bwd_ms": roof_fb}
+        for name, v in out["transports"].items():
+            v["fwd_of_roofline"] = roof_f / v["fwd_ms"]
+            v["fwd_bwd_of_roofline"] = roof_fb / v["fwd_bwd_ms"]
+        # the two transfers as kernels of their own, on the same plan (pull transport: the result rows stay with
+        # the expert's rank and the token's rank pulls them)
+        if "peer" in out["transports"] and args.transports.split(",")[-1] == "peer":
+            from composed_mixture_of_experts_engine_b200.ops import _ext
+            from composed_mixture_of_experts_engine_b200.parallel import symm_peer
+
+            ext = _ext.ext()
+            pc = symm_peer._context(topo)
+            lkey = (symm_peer._layer_key(layer), (layer._peer_forward_calls - 1) % max(1, topo.pp_size))
+            xs = pc.shared("x", T * H * 2)
+            srow = pc.per_layer(lkey, "slot_row", world * T * K * 4)
+            yps = pc.per_layer(lkey, "yp", plan.cap_rows * H * 2)
+            xp = torch.empty(plan.cap_rows, H, device=dev, dtype=torch.bfloat16)
+            yv = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
+            idx32 = layer.router.last_idx32.contiguous()
+            w32 = layer.router.last_w32.detach().float().contiguous()
+            erank = pc.expert_rank_table(E)
+            d_ms = _median_ms(lambda: ext.gather_rows_peer(xs.ptrs(), T * K, K, plan.row_slot, None, xp,
+                                                           plan.num_m_tiles, H), args.iters, args.warmup, dev)
+            c_ms = _median_ms(lambda: ext.combine_rows_peer(yps.ptrs(), srow.ptrs(), idx32, erank, w32, yv, K,
+                                                            rank * T * K, H, None), args.iters, args.warmup, dev)
+            bt = torch.tensor([float(x_bytes)], device=dev, dtype=torch.float64)
+            dist.all_reduce(bt, op=dist.ReduceOp.MAX)
+            worst_bytes = float(bt.item())
+            out["standalone"] = {
+                "dispatch_ms": d_ms, "dispatch_of_nvlink_roofline": worst_bytes / link * 1e3 / d_ms,
+                "combine_ms": c_ms, "combine_of_nvlink_roofline": worst_bytes / link * 1e3 / c_ms,
+                "dispatch_gb_per_s_in": worst_bytes / 1e9 / d_ms * 1e3,
+                "combine_gb_per_s_in": worst_bytes / 1e9 / c_ms * 1e3}
+
     # the same amount of expert math on rows that are already here: a layer without expert parallelism that holds
     # this rank's share of the experts and sees as many (token, expert) rows as this rank processed above
     holder = layer._last_plan_holder
@@ -143,6 +211,13 @@ def main() -> int:
     for name, v in out["transports"].items():
         v["exposed_dispatch_combine_fwd_us"] = (v["fwd_ms"] - lf) * 1e3
         v["exposed_dispatch_combine_fwd_bwd_us"] = (v["fwd_bwd_ms"] - lfb) * 1e3
+    if "standalone" in out:
+        # how much of the transfers' stand-alone time the fused layer hides under the expert math
+        from composed_mixture_of_experts_engine_b200.telemetry.logger import overlap_ratio
+
+        comm = out["standalone"]["dispatch_ms"] + out["standalone"]["combine_ms"]
+        for name, v in out["transports"].items():
+            v["comm_compute_overlap_ratio_fwd"] = overlap_ratio(comm, lf, v["fwd_ms"])
     out["rows_dropped_for_buffer_space"] = int(overflow_counter(dev).item()) if world > 1 else 0
     out["rows_this_rank"] = rows
     if rank == 0:

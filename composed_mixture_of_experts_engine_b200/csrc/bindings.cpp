@@ -136,7 +136,7 @@ void gemm_pull(const Tensor& A, const Tensor& B, Tensor& D, int64_t epilogue, in
                const Tensor& num_m_tiles, int64_t max_m_tiles, const OptTensor& aux_in, const OptTensor& aux_out,
                const Tensor& row_slot, const std::vector<int64_t>& src_ptrs, int64_t slots_per_src, int64_t pull_K,
                const OptTensor& slot_scale, int64_t ld_src, Tensor& tile_ready, int64_t epoch, const OptTensor& status,
-               int64_t timeout_ns) {
+               int64_t timeout_ns, const OptTensor& stamps) {
   const c10::cuda::CUDAGuard guard(A.device());
   cmoe::GemmArgs g = gemm_args(A, B, D, cmoe::GEMM_GROUPED_M, epilogue, 0, N, K, false, b_mn, groups, b_group_rows,
                                split_n, tile_group, num_m_tiles, max_m_tiles, std::nullopt, 0, false, aux_in, aux_out,
@@ -152,6 +152,11 @@ void gemm_pull(const Tensor& A, const Tensor& B, Tensor& D, int64_t epilogue, in
   g.pull_ld_src = ld_src;
   g.tile_ready = reinterpret_cast<uint32_t*>(tile_ready.data_ptr<int>());
   g.pull_epoch = static_cast<uint32_t>(epoch);
+  if (stamps.has_value()) {
+    TORCH_CHECK(stamps->scalar_type() == at::kLong && stamps->numel() >= 4 && stamps->is_contiguous() &&
+                    stamps->is_cuda(), "stamps must be a CUDA int64 tensor of 4 elements");
+    g.pull_stamps = reinterpret_cast<unsigned long long*>(stamps->data_ptr<int64_t>());
+  }
   check_cuda(cmoe::launch_gemm(g, cur_stream()), "launch_gemm(pull)");
 }
 

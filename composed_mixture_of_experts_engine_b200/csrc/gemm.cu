@@ -87,6 +87,7 @@ struct KParams {
   int pull_cols;
   uint32_t* tile_ready;
   uint32_t pull_epoch;
+  unsigned long long* pull_stamps;
   // fused scatter: the slot of every output row gives its destination (rank, row)
   const int* scatter_row_slot;
   long long scatter_slots_per_rank;
@@ -379,6 +380,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
+      bool stamped = false;
       for (int t = blockIdx.x; t < n_total; t += gridDim.x) {
         const Tile ti = decode_tile(p, t, m_tiles, n_tiles);
         if (ti.skip || ti.k_blocks == 0) continue;
@@ -388,6 +390,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         for (int kb = 0; kb < ti.k_blocks; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, wc, ST_TIMEOUT_SMEM_FULL)) break;
           tc_fence_after();
+          if (p.pull_stamps != nullptr && !stamped) {
+            atomicMin(p.pull_stamps + 2, global_timer_ns());
+            stamped = true;
+          }
           const uint32_t a_addr = smem_u32(sA + stage * A_STAGE_BYTES);
           const uint32_t b_addr = smem_u32(sB + stage * B_STAGE_BYTES);
 #pragma unroll
@@ -407,11 +413,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
+      if (p.pull_stamps != nullptr && stamped) atomicMax(p.pull_stamps + 3, global_timer_ns());
     }
   } else if (warp >= 6) {
     // ------------------------------------------------------------------ row-pull warps (fused dispatch)
     if (p.pull_row_slot != nullptr) {
       const int pw = warp - 6;  // 0..3: each warp brings in 32 of the 128 rows of a tile
+      if (p.pull_stamps != nullptr && threadIdx.x == 6 * 32 && static_cast<int>(blockIdx.x) < m_tiles)
+        atomicMin(p.pull_stamps + 0, global_timer_ns());
       for (int mt = blockIdx.x; mt < m_tiles; mt += gridDim.x) {
         if (p.tile_group[mt] >= 0) {
           // Two rows at a time and up to eight 16-byte loads per lane and row in flight (16 KiB per warp): remote
@@ -473,6 +482,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.tile_ready + mt), "r"(p.pull_epoch) : "memory");
         }
       }
+      if (p.pull_stamps != nullptr && threadIdx.x == 6 * 32 && static_cast<int>(blockIdx.x) < m_tiles)
+        atomicMax(p.pull_stamps + 1, global_timer_ns());
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps
@@ -1082,6 +1093,7 @@ cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   kp.pull_cols = static_cast<int>(a.a_cols);
   kp.tile_ready = a.tile_ready;
   kp.pull_epoch = a.pull_epoch;
+  kp.pull_stamps = a.pull_stamps;
   if (a.pull_row_slot != nullptr &&
       (a.mode != GEMM_GROUPED_M || a.a_mn || a.tile_ready == nullptr || a.a_cols % 8 != 0))
     return cudaErrorInvalidValue;

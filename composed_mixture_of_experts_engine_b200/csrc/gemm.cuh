@@ -84,6 +84,11 @@ struct GemmArgs {
   long long pull_ld_src = 0;
   uint32_t* tile_ready = nullptr;
   uint32_t pull_epoch = 0;
+  // Optional device timestamps of a launch with the fused row pull (4 x uint64 of `%globaltimer` nanoseconds, the
+  // caller presets {max, 0, max, 0}): [0] first row pulled, [1] last tile of rows complete, [2] first MMA issued,
+  // [3] last accumulator committed; min / max over all CTAs.  Telemetry derives from them how much of the transfer
+  // ran under the tensor-core work.  nullptr: nothing is recorded.
+  unsigned long long* pull_stamps = nullptr;
 
   // Fused scatter (EPI_STORE, bf16, no accumulate).  When scatter_row_slot is set, output row r is not written to D
   // but to the buffer of rank  slot / scatter_slots_per_rank  in scatter_out, at row  slot % scatter_slots_per_rank

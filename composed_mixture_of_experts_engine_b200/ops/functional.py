@@ -19,9 +19,17 @@ from . import attention_sm100 as _attn_sm100
 from .kernels import EPI_SWIGLU_BWD, EPI_SWIGLU_FWD, GEMM_GROUPED_K, GEMM_GROUPED_M, MoEPlan
 
 
+def force_library() -> bool:
+    """``CMOE_FORCE_LIBRARY=1``: every differentiable op takes its PyTorch path even on a B200 (the library arm of
+    the benchmarks: cuBLAS / cuDNN / eager kernels through PyTorch, nothing of this package's device code)."""
+    import os
+
+    return os.environ.get("CMOE_FORCE_LIBRARY", "0") == "1"
+
+
 def on_device_path(*tensors: torch.Tensor) -> bool:
     """True when the sm_100a kernels handle these tensors (CUDA + bf16)."""
-    return all(t.is_cuda and t.dtype == torch.bfloat16 for t in tensors)
+    return all(t.is_cuda and t.dtype == torch.bfloat16 for t in tensors) and not force_library()
 
 
 # ------------------------------------------------------------------------------------------ RMSNorm

@@ -277,10 +277,12 @@ _pull_epoch: Dict[int, int] = {}
 def gemm_pull(A: torch.Tensor, B: torch.Tensor, D: torch.Tensor, plan: MoEPlan, *, epilogue: int, N: int, K: int,
               groups: int, b_group_rows: int, src_ptrs, slots_per_src: int, pull_K: int, ld_src: int,
               b_mn: bool = False, split_n: int = 0, aux_in: Optional[torch.Tensor] = None,
-              aux_out: Optional[torch.Tensor] = None, slot_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+              aux_out: Optional[torch.Tensor] = None, slot_scale: Optional[torch.Tensor] = None,
+              stamps: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Grouped GEMM whose A rows (``plan.row_slot`` -> token rows of the ranks in ``src_ptrs``) are brought in by
     extra warps of the same kernel, tile by tile (fused expert-parallel dispatch).  ``A`` is the destination
-    buffer of the pulled rows as well as the GEMM operand."""
+    buffer of the pulled rows as well as the GEMM operand.  ``stamps`` (int64[4], see :func:`new_pull_stamps`)
+    receives the device timestamps of first / last row pulled and first / last MMA."""
     idx = A.device.index or 0
     ready = _tile_ready.get(idx)
     if ready is None or ready.numel() < plan.max_m_tiles:
@@ -293,8 +295,28 @@ def gemm_pull(A: torch.Tensor, B: torch.Tensor, D: torch.Tensor, plan: MoEPlan, 
         _pull_epoch[idx] = 1
     _ext.ext().gemm_pull(A, B, D, epilogue, N, K, b_mn, groups, b_group_rows, split_n, plan.tile_group,
                          plan.num_m_tiles, plan.max_m_tiles, aux_in, aux_out, plan.row_slot, list(src_ptrs),
-                         slots_per_src, pull_K, slot_scale, ld_src, ready, _pull_epoch[idx], status_word(A.device), 0)
+                         slots_per_src, pull_K, slot_scale, ld_src, ready, _pull_epoch[idx], status_word(A.device), 0,
+                         stamps)
     return D
+
+
+_I64_MAX = (1 << 63) - 1
+
+
+def new_pull_stamps(device: torch.device) -> torch.Tensor:
+    """A timestamp record for :func:`gemm_pull`: {first pull, last pull, first MMA, last MMA} in nanoseconds of the
+    device's global timer, preset so that the kernel's atomic min / max leave the extremes over all CTAs."""
+    return torch.tensor([_I64_MAX, 0, _I64_MAX, 0], dtype=torch.int64, device=device)
+
+
+def pull_overlap_ratio(stamps: torch.Tensor) -> Optional[float]:
+    """Fraction of the row transfer's duration during which the tensor cores of the same launch were at work:
+    |[first pull, last pull] intersected with [first MMA, last MMA]| / |[first pull, last pull]|.  One device read.
+    ``None`` when the launch recorded nothing (no rows pulled)."""
+    p0, p1, m0, m1 = (int(v) for v in stamps.tolist())
+    if p0 == _I64_MAX or m0 == _I64_MAX or p1 <= p0:
+        return None
+    return max(0, min(p1, m1) - max(p0, m0)) / float(p1 - p0)
 
 
 def gemm_scatter(A: torch.Tensor, B: torch.Tensor, *, N: int, K: int, row_slot: torch.Tensor, slots_per_rank: int,

@@ -250,7 +250,9 @@ def build_optimizer(model: nn.Module, lr: float, weight_decay: float = 0.1, beta
                     max_grad_norm: float = 0.0, topology=None):
     """FusedAdamW for CUDA bf16 models, ``torch.optim.AdamW`` otherwise."""
     params = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
-    on_device = all(p.is_cuda and p.dtype == torch.bfloat16 for _, p in params)
+    from .functional import force_library
+
+    on_device = all(p.is_cuda and p.dtype == torch.bfloat16 for _, p in params) and not force_library()
     if not on_device:
         decay = [p for n, p in params if not _no_decay(n, p)]
         no_decay = [p for n, p in params if _no_decay(n, p)]

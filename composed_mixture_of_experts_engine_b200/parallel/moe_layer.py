@@ -199,6 +199,7 @@ class DistributedMoELayer(nn.Module):
     # ---- telemetry (resolved lazily: reading these waits for the recorded events only) ----------
     def enable_timing(self, on: bool = True) -> None:
         self._timer.enabled = on
+        self._last_plan_holder["want_stamps"] = bool(on)  # fused dispatch: record device timestamps of the launch
 
     def _resolve(self) -> dict:
         got = self._timer.resolve(wait=True)
@@ -220,6 +221,17 @@ class DistributedMoELayer(nn.Module):
 
     @property
     def last_overlap_ratio(self) -> float:
+        """How much of the dispatch transfer ran under expert compute.  On the fused peer-memory path this comes
+        from device timestamps inside the first grouped GEMM (first / last row pulled against first / last MMA of
+        the same launch); on the library path from the event times of the dispatch and expert phases, as the
+        reference does (pkg/distributed/moe_layer.py:340-341)."""
+        stamps = self._last_plan_holder.get("pull_stamps")
+        if stamps is not None:
+            from ..ops.kernels import pull_overlap_ratio
+
+            r = pull_overlap_ratio(stamps)
+            if r is not None:
+                return float(r)
         t = self._resolve()
         if "overlap_ratio" in t:
             return float(t["overlap_ratio"])

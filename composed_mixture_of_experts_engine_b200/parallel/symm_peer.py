@@ -182,6 +182,9 @@ class _EPMoEPeer(torch.autograd.Function):
         if _fused():
             # the dispatch runs inside the first grouped GEMM: rows stream in over NVLink tile by tile
             kw["pull"] = dict(src_ptrs=_ptrs(xs), slots_per_src=T * K, pull_K=K, ld_src=H)
+            if holder is not None and holder.get("want_stamps"):
+                holder["pull_stamps"] = kernels.new_pull_stamps(dev)  # read back when telemetry is emitted
+                kw["pull"]["stamps"] = holder["pull_stamps"]
         else:
             ext.gather_rows_peer(_ptrs(xs), T * K, K, plan.row_slot, None, xp, plan.num_m_tiles, H)
         hact, gu, _ = OF.grouped_swiglu_forward(xp, w13, w2, plan, **kw)
