@@ -237,6 +237,7 @@ def run_ours(args) -> dict:
         from composed_mixture_of_experts_engine_b200.elastic.fault_monitor import AsyncCheckpointer, LocalNVMeAdapter
 
         ckpt = AsyncCheckpointer(LocalNVMeAdapter(args.ckpt_dir), None, retention=1, workers=2)
+        ckpt.prepare(trainer.model, None if args.ckpt_model_only else trainer.optimizer)  # as train.py does at start-up
 
     def e2e_step(i):
         ids, tgt = host[i % n_batches]

@@ -6,6 +6,7 @@
 
 #include <cstdlib>
 
+#include <algorithm>
 #include <optional>
 #include <string>
 #include <vector>
@@ -309,16 +310,24 @@ void sumsq(const Tensor& x, Tensor& out) {
   TORCH_CHECK(x.is_contiguous() && out.scalar_type() == at::kFloat);
   const bool bf = x.scalar_type() == at::kBFloat16;
   TORCH_CHECK(bf || x.scalar_type() == at::kFloat);
-  check_cuda(cmoe::launch_sumsq(x.data_ptr(), bf, x.numel(), out.data_ptr<float>(), cur_stream()), "sumsq");
+  // per-block partial sums, added in block order by a second kernel (stream-ordered caching allocation)
+  Tensor partials = at::empty({std::max(1, cmoe::sumsq_partial_count(x.numel()))}, out.options());
+  check_cuda(cmoe::launch_sumsq(x.data_ptr(), bf, x.numel(), out.data_ptr<float>(), partials.data_ptr<float>(),
+                                cur_stream()),
+             "sumsq");
 }
 void cross_entropy(Tensor& logits, const Tensor& targets, Tensor& loss_sum, double grad_scale) {
   const c10::cuda::CUDAGuard guard(logits.device());
   TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && logits.scalar_type() == at::kBFloat16);
   TORCH_CHECK(targets.scalar_type() == at::kLong && targets.is_contiguous() && targets.numel() == logits.size(0));
+  // per-row losses, summed by a library reduction whose order is fixed: the loss value is reproducible bit for bit
+  Tensor row_loss = at::empty({logits.size(0)}, loss_sum.options());
   check_cuda(cmoe::launch_cross_entropy(logits.data_ptr(), reinterpret_cast<const long long*>(targets.data_ptr<int64_t>()),
-                                        loss_sum.data_ptr<float>(), logits.size(0), static_cast<int>(logits.size(1)),
-                                        logits.stride(0), static_cast<float>(grad_scale), cur_stream()),
+                                        loss_sum.data_ptr<float>(), row_loss.data_ptr<float>(), logits.size(0),
+                                        static_cast<int>(logits.size(1)), logits.stride(0),
+                                        static_cast<float>(grad_scale), cur_stream()),
              "cross_entropy");
+  loss_sum.add_(row_loss.sum());
 }
 
 // ------------------------------------------------------------------------------------------ MoE bookkeeping

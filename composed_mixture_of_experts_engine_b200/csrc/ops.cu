@@ -180,14 +180,24 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
   }
 }
 
-// dw[c] += sum_b partial[b, c]; grid (ceil(H / 128), row slices)
-__global__ void __launch_bounds__(128) colsum_add_kernel(const float* __restrict__ partial, float* __restrict__ dw,
-                                                         int n_rows, int H) {
+// Column sums of the per-CTA partial rows in a fixed order (the same inputs give the same bits, whichever CTA
+// finishes first).  Stage 1, grid (ceil(H / 128), slices): slice y adds the rows y, y + slices, ... in that order and
+// leaves the result in row y (only slice y ever touches those rows).  Stage 2, grid (ceil(H / 128)): dw[c] += the
+// `slices` stage-1 rows, again in order.
+__global__ void __launch_bounds__(128) colsum_stage1_kernel(float* __restrict__ partial, int n_rows, int H) {
   const int c = blockIdx.x * 128 + threadIdx.x;
   if (c >= H) return;
   float s = 0.f;
   for (int b = blockIdx.y; b < n_rows; b += gridDim.y) s += partial[static_cast<long long>(b) * H + c];
-  atomicAdd(dw + c, s);
+  partial[static_cast<long long>(blockIdx.y) * H + c] = s;
+}
+__global__ void __launch_bounds__(128) colsum_stage2_kernel(const float* __restrict__ partial, float* __restrict__ dw,
+                                                            int slices, int H) {
+  const int c = blockIdx.x * 128 + threadIdx.x;
+  if (c >= H) return;
+  float s = 0.f;
+  for (int y = 0; y < slices; ++y) s += partial[static_cast<long long>(y) * H + c];
+  dw[c] += s;
 }
 
 // ------------------------------------------------------------------------------------ RoPE
@@ -347,7 +357,8 @@ __global__ void adamw_kernel(const AdamWArgs a) {
   }
 }
 
-__global__ void __launch_bounds__(256) sumsq_kernel(const void* x, int is_bf16, long long n, float* out) {
+__global__ void __launch_bounds__(256) sumsq_kernel(const void* x, int is_bf16, long long n, float* out,
+                                                    float* __restrict__ partials) {
   __shared__ float red[8];
   float acc = 0.f;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -376,14 +387,30 @@ __global__ void __launch_bounds__(256) sumsq_kernel(const void* x, int is_bf16, 
     if (gi < n) acc += xf[gi] * xf[gi];
   }
   acc = block_sum<256>(acc, red);
-  if (threadIdx.x == 0) atomicAdd(out, acc);
+  if (threadIdx.x == 0) {
+    if (partials != nullptr)
+      partials[blockIdx.x] = acc;  // summed in block order by sumsq_final_kernel
+    else
+      atomicAdd(out, acc);
+  }
+}
+
+// out += sum of `n` per-block partial sums, always in the same order (one block, fixed tree)
+__global__ void __launch_bounds__(256) sumsq_final_kernel(const float* __restrict__ partials, int n,
+                                                          float* __restrict__ out) {
+  __shared__ float red[8];
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < n; i += 256) acc += partials[i];
+  acc = block_sum<256>(acc, red);
+  if (threadIdx.x == 0) *out += acc;
 }
 
 // ------------------------------------------------------------------------------------ cross-entropy
 constexpr int CE_THREADS = 512;
 __global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(__nv_bfloat16* __restrict__ logits,
                                                                    const long long* __restrict__ targets,
-                                                                   float* __restrict__ loss_sum, long long rows, int V,
+                                                                   float* __restrict__ loss_sum,
+                                                                   float* __restrict__ row_loss, long long rows, int V,
                                                                    long long ld, float grad_scale) {
   __shared__ float red[CE_THREADS / 32];
   __shared__ float s_max, s_sum;
@@ -432,7 +459,13 @@ __global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(__nv_bfloat16
   __syncthreads();
   const float lse = bm + logf(s_sum);
   const bool ignore = tgt < 0 || tgt >= V;
-  if (threadIdx.x == 0 && !ignore) atomicAdd(loss_sum, lse - __bfloat162float(lr[tgt]));
+  if (threadIdx.x == 0) {
+    const float l = ignore ? 0.f : lse - __bfloat162float(lr[tgt]);
+    if (row_loss != nullptr)
+      row_loss[row] = l;  // the caller sums the rows in a fixed order
+    else if (!ignore)
+      atomicAdd(loss_sum, l);
+  }
   __syncthreads();
   const float gs = ignore ? 0.f : grad_scale;
   for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
@@ -730,7 +763,8 @@ cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
   }
   if (dw_partial != nullptr) {
     const unsigned slices = grid < 16u ? grid : 16u;
-    colsum_add_kernel<<<dim3((H + 127) / 128, slices), 128, 0, stream>>>(dw_partial, dw, static_cast<int>(grid), H);
+    colsum_stage1_kernel<<<dim3((H + 127) / 128, slices), 128, 0, stream>>>(dw_partial, static_cast<int>(grid), H);
+    colsum_stage2_kernel<<<(H + 127) / 128, 128, 0, stream>>>(dw_partial, dw, static_cast<int>(slices), H);
   }
   return cudaGetLastError();
 }
@@ -768,18 +802,22 @@ cudaError_t launch_adamw(const AdamWArgs& a, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
-cudaError_t launch_sumsq(const void* x, int is_bf16, long long n, float* out, cudaStream_t stream) {
+int sumsq_partial_count(long long n) { return n <= 0 ? 0 : static_cast<int>(grid_for(n / 8 + 1, 256, 148 * 8)); }
+
+cudaError_t launch_sumsq(const void* x, int is_bf16, long long n, float* out, float* partials, cudaStream_t stream) {
   if (n <= 0) return cudaSuccess;
-  sumsq_kernel<<<grid_for(n / 8 + 1, 256, 148 * 8), 256, 0, stream>>>(x, is_bf16, n, out);
+  const unsigned grid = static_cast<unsigned>(sumsq_partial_count(n));
+  sumsq_kernel<<<grid, 256, 0, stream>>>(x, is_bf16, n, out, partials);
+  if (partials != nullptr) sumsq_final_kernel<<<1, 256, 0, stream>>>(partials, static_cast<int>(grid), out);
   return cudaGetLastError();
 }
 
-cudaError_t launch_cross_entropy(void* logits, const long long* targets, float* loss_sum, long long rows, int V,
-                                 long long ld, float grad_scale, cudaStream_t stream) {
+cudaError_t launch_cross_entropy(void* logits, const long long* targets, float* loss_sum, float* row_loss,
+                                 long long rows, int V, long long ld, float grad_scale, cudaStream_t stream) {
   if (rows <= 0) return cudaSuccess;
   if (ld % 8 != 0) return cudaErrorInvalidValue;
   cross_entropy_kernel<<<static_cast<unsigned>(rows), CE_THREADS, 0, stream>>>(
-      reinterpret_cast<__nv_bfloat16*>(logits), targets, loss_sum, rows, V, ld, grad_scale);
+      reinterpret_cast<__nv_bfloat16*>(logits), targets, loss_sum, row_loss, rows, V, ld, grad_scale);
   return cudaGetLastError();
 }
 

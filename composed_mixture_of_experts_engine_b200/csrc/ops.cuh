@@ -53,14 +53,19 @@ struct AdamWArgs {
   int zero_grad = 0;  // != 0: the gradient buffer is cleared after it has been read
 };
 cudaError_t launch_adamw(const AdamWArgs& a, cudaStream_t stream);
-// *out += sum(x^2) (out must be zeroed by the caller before the first call of a step)
-cudaError_t launch_sumsq(const void* x, int is_bf16, long long n, float* out, cudaStream_t stream);
+// *out += sum(x^2) (out must be zeroed by the caller before the first call of a step).  With `partials` (room for
+// sumsq_partial_count(n) floats) the per-block sums are added in a fixed order, so that equal inputs give equal bits
+// (the clipping factor, and with it the whole update, hangs on this number); nullptr: fp32 atomics.
+int sumsq_partial_count(long long n);
+cudaError_t launch_sumsq(const void* x, int is_bf16, long long n, float* out, float* partials, cudaStream_t stream);
 
 // ---- cross-entropy, forward and gradient in one pass ------------------------------------------
 // logits [rows, V] bf16 are overwritten with d(loss)/d(logits) = (softmax - onehot) * grad_scale;
-// *loss_sum += sum over rows of the per-row loss (fp32).  targets are int64; target < 0 is ignored.
-cudaError_t launch_cross_entropy(void* logits, const long long* targets, float* loss_sum, long long rows, int V,
-                                 long long ld, float grad_scale, cudaStream_t stream);
+// *loss_sum += sum over rows of the per-row loss (fp32), or, with `row_loss` [rows], the per-row losses are written
+// there for the caller to sum in a fixed order (*loss_sum is then left alone).  targets are int64; target < 0 is
+// ignored (its row loss is 0).
+cudaError_t launch_cross_entropy(void* logits, const long long* targets, float* loss_sum, float* row_loss,
+                                 long long rows, int V, long long ld, float grad_scale, cudaStream_t stream);
 
 // ---- MoE routing bookkeeping -------------------------------------------------------------------
 // Builds the expert-sorted, 128-row-padded row layout for `n_slots` (token, k) slots.

@@ -80,9 +80,11 @@ router_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tfull_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_last = const_cast<int*>(abort_flag) + 1;
-  float* s_prob = reinterpret_cast<float*>(s_last + 1);     // [256]
-  int* s_cnt = reinterpret_cast<int*>(s_prob + kRouterMaxExperts);  // [256]
-  float* s_z = reinterpret_cast<float*>(s_cnt + kRouterMaxExperts);
+  // per-tile sums as 64-bit fixed point (integer adds commute: the result does not depend on the order of the warps)
+  unsigned long long* s_prob = reinterpret_cast<unsigned long long*>(
+      (reinterpret_cast<uintptr_t>(s_last + 1) + 7) & ~uintptr_t(7));  // [256]
+  unsigned long long* s_z = s_prob + kRouterMaxExperts;
+  int* s_cnt = reinterpret_cast<int*>(s_z + 1);  // [256]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -167,10 +169,10 @@ router_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     const int E = p.E;
     const int nch = (E + 31) / 32;
     for (int e = et; e < kRouterMaxExperts; e += 128) {
-      s_prob[e] = 0.f;
+      s_prob[e] = 0ull;
       s_cnt[e] = 0;
     }
-    if (et == 0) *s_z = 0.f;
+    if (et == 0) *s_z = 0ull;
     asm volatile("bar.sync 1, 128;" ::: "memory");
 
     const bool ok = mbar_wait(tfull_bar, 0, wc, ST_TIMEOUT_TMEM_FULL);
@@ -219,7 +221,7 @@ router_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         for (int j = 0; j < 32; ++j)
           pv[j] = (row_ok && (c * 32 + j < E)) ? expf(__uint_as_float(r[j]) - lse) : 0.f;
         warp_transpose_reduce(pv, lane);
-        if (c * 32 + lane < E) atomicAdd(&s_prob[c * 32 + lane], pv[0]);
+        if (c * 32 + lane < E) atomicAdd(&s_prob[c * 32 + lane], __float2ull_rn(pv[0] * kRouterProbScale));
       }
       // pass 4: top-k by repeated arg-max over TMEM (already chosen experts are masked by bit sets)
       uint32_t sel[8];
@@ -273,16 +275,16 @@ router_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         }
       }
       const float z = warp_sum(row_ok ? lse * lse : 0.f);
-      if (lane == 0) atomicAdd(s_z, z);
+      if (lane == 0) atomicAdd(s_z, __float2ull_rn(z * kRouterZScale));
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
     // flush this tile's sums; the last CTA to finish turns them into the loss values
-    float* ws_prob = reinterpret_cast<float*>(p.workspace);
-    float* ws_z = ws_prob + E;
-    int* ws_cnt = reinterpret_cast<int*>(p.workspace) + E + 1;
-    unsigned int* ws_done = reinterpret_cast<unsigned int*>(p.workspace) + 2 * E + 1;
+    unsigned long long* ws_prob = reinterpret_cast<unsigned long long*>(p.workspace);
+    unsigned long long* ws_z = ws_prob + E;
+    int* ws_cnt = reinterpret_cast<int*>(ws_z + 1);
+    unsigned int* ws_done = reinterpret_cast<unsigned int*>(ws_cnt + E);
     for (int e = et; e < E; e += 128) {
-      if (s_prob[e] != 0.f) atomicAdd(&ws_prob[e], s_prob[e]);
+      if (s_prob[e] != 0ull) atomicAdd(&ws_prob[e], s_prob[e]);
       if (s_cnt[e] != 0) atomicAdd(&ws_cnt[e], s_cnt[e]);
     }
     if (et == 0) atomicAdd(ws_z, *s_z);
@@ -298,14 +300,14 @@ router_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       const float n_tok = static_cast<float>(p.n_tokens);
       float aux = 0.f, mxc = 0.f, sumc = 0.f;
       for (int e = lane; e < E; e += 32) {
-        const float pr = __ldcg(&ws_prob[e]);
+        const float pr = static_cast<float>(static_cast<double>(__ldcg(&ws_prob[e])) / kRouterProbScale);
         const int cn = __ldcg(&ws_cnt[e]);
         p.counts[e] = cn;
         p.mean_prob[e] = pr / n_tok;
         aux += (static_cast<float>(cn) / (n_tok * p.K)) * (pr / n_tok);
         mxc = fmaxf(mxc, static_cast<float>(cn));
         sumc += static_cast<float>(cn);
-        ws_prob[e] = 0.f;
+        ws_prob[e] = 0ull;
         ws_cnt[e] = 0;
       }
       aux = warp_sum(aux);
@@ -313,10 +315,10 @@ router_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       sumc = warp_sum(sumc);
       if (lane == 0) {
         p.stats[0] = aux * E;
-        p.stats[1] = __ldcg(ws_z) / n_tok;
+        p.stats[1] = static_cast<float>(static_cast<double>(__ldcg(ws_z)) / kRouterZScale) / n_tok;
         p.stats[2] = sumc > 0.f ? mxc / (sumc / E) : 1.f;
         p.stats[3] = sumc;
-        *ws_z = 0.f;
+        *ws_z = 0ull;
         *ws_done = 0u;
       }
     }
@@ -463,7 +465,7 @@ cudaError_t launch_router_fwd(const RouterFwdArgs& a, cudaStream_t stream) {
   p.status = a.status;
   p.timeout_ns = a.timeout_ns ? a.timeout_ns : kDefaultTimeoutNs;
 
-  const int smem = stages * stage_bytes + 1024 + 512 + 2 * kRouterMaxExperts * 4 + 64;
+  const int smem = stages * stage_bytes + 1024 + 512 + kRouterMaxExperts * (8 + 4) + 64;
   static int configured_smem = 0;
   if (smem > configured_smem) {
     e = cudaFuncSetAttribute(router_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

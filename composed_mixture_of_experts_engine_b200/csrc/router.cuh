@@ -7,10 +7,14 @@ namespace cmoe {
 
 constexpr int kRouterMaxExperts = 256;
 constexpr int kRouterMaxTopK = 8;
-// floats in the workspace: [0,E) sum of probabilities, [E] sum of lse^2; followed (as ints) by
-// [E+1, 2E+1) counts and [2E+1] the finished-CTA counter.  2*E+2 words in total, zero before the
-// first launch; the kernel leaves it zeroed again.
-inline size_t router_workspace_words(int num_experts) { return 2 * static_cast<size_t>(num_experts) + 2; }
+// Workspace layout (32-bit words, 8-byte aligned base): E + 1 unsigned 64-bit fixed-point accumulators (the sums of
+// the probabilities of each expert, scaled by 2^40, then the sum of lse^2 scaled by 2^24), followed by E int counts
+// and the finished-CTA counter.  The sums are integers so that the order in which the CTAs add to them cannot
+// change the result (same inputs, same bits).  3*E+4 words in total, zero before the first launch; the kernel
+// leaves it zeroed again.
+inline size_t router_workspace_words(int num_experts) { return 3 * static_cast<size_t>(num_experts) + 4; }
+constexpr float kRouterProbScale = 1099511627776.f;  // 2^40
+constexpr float kRouterZScale = 16777216.f;          // 2^24
 
 struct RouterFwdArgs {
   const void* X = nullptr;  // [n_tokens, H] bf16, leading dimension ldx

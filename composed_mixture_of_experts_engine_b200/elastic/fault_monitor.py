@@ -326,6 +326,35 @@ class _PinnedStager:
             self.guard()
         return host, (start, end), bufset
 
+    def reserve(self, obj: Any, sets: int = 1) -> int:
+        """Allocate ``sets`` idle sets of pinned buffers shaped like the CUDA tensors of ``obj`` now, so that the
+        first snapshots do not pay for ``cudaHostAlloc`` (about a second per 1.5 GB here) on the training thread.
+        Returns the number of bytes pinned."""
+        total = 0
+        if not torch.cuda.is_available():
+            return total
+        for _ in range(max(0, sets)):
+            bufset: Dict[str, torch.Tensor] = {}
+
+            def walk(o, path):
+                nonlocal total
+                if isinstance(o, torch.Tensor):
+                    if o.is_cuda:
+                        bufset[path] = torch.empty(o.shape, dtype=o.dtype, device="cpu", pin_memory=True)
+                        self.allocations += 1
+                        total += o.numel() * o.element_size()
+                elif isinstance(o, dict):
+                    for k, v in o.items():
+                        walk(v, f"{path}/{k}")
+                elif isinstance(o, (list, tuple)):
+                    for i, v in enumerate(o):
+                        walk(v, f"{path}/{i}")
+
+            walk(obj, "")
+            if bufset:
+                self.release(bufset)
+        return total
+
     def guard(self) -> None:
         """Make the current stream wait for the last snapshot's copy (no host wait)."""
         ev, self._pending = self._pending, None
@@ -386,6 +415,11 @@ class AsyncCheckpointer:
             meta.update(extra_meta)
         self._q.put(_CheckpointJob(step=step, payload=(snapshot, event, bufset), meta=meta))
         self.last_commit_ms = (time.perf_counter() - t0) * 1000.0
+
+    def prepare(self, model: torch.nn.Module, optimizer, sets: int = 1) -> int:
+        """Pin the host staging memory for ``sets`` snapshots of this model / optimizer ahead of the first save (call
+        it once after building them, outside the training loop).  Returns the bytes pinned."""
+        return self._stager.reserve(self._state(model, optimizer), sets)
 
     def _guard_from_optimizer(self, optimizer) -> bool:
         """True when ``optimizer`` will call the stager's guard before its next step (a pre-step hook, installed

@@ -330,6 +330,10 @@ class Trainer:
         for l in losses:
             total = total + l.detach().float()
         self.stage.module = self.model
+        # only the last stage saw the loss: hand it to the other stages so that every rank returns (and logs) it
+        from .parallel.mesh import pp_process_group
+
+        dist.broadcast(total, src=self.topology.axis_ranks("pp")[-1], group=pp_process_group(self.topology))
         return total
 
     def close(self) -> None:

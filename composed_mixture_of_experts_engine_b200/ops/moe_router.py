@@ -116,7 +116,7 @@ def _router_workspace(device: torch.device, E: int) -> torch.Tensor:
     key = (device.index or 0, E)
     ws = _workspaces.get(key)
     if ws is None:
-        ws = torch.zeros(2 * E + 2, dtype=torch.int32, device=device)
+        ws = torch.zeros(3 * E + 4, dtype=torch.int32, device=device)  # csrc/router.cuh: router_workspace_words
         _workspaces[key] = ws
     return ws
 

@@ -59,6 +59,11 @@ class _FlatGroup:
             self.flat_p = torch.zeros(self.numel, device=dev, dtype=torch.bfloat16)
             self.flat_g = torch.zeros(self.numel, device=dev, dtype=grad_dtype)
         self.decay = weight_decay_mask
+        # parameters that every tensor-parallel rank holds whole (norms, router gates, embeddings under sequence
+        # parallelism): their squared gradient norm must count once, not once per tensor-parallel rank
+        tp = topology.tp_size if topology is not None else 1
+        self.tp_size = tp
+        self.replicated = [tp > 1 and not getattr(p, "tensor_parallel_shard", False) for p in params]
         for p, off in zip(params, offs):
             n = p.numel()
             self.flat_p[off:off + n].copy_(p.data.reshape(-1))
@@ -79,19 +84,19 @@ class _FlatGroup:
         self._segments = self._build_segments()
         self.grad_scale = 1.0  # extra factor on this group's gradients (1/ep for expert weights, see build_optimizer)
 
-    def _build_segments(self) -> List[Tuple[int, int, bool]]:
-        """(start, end, decay) runs inside this rank's shard, in shard-local coordinates."""
-        segs: List[Tuple[int, int, bool]] = []
+    def _build_segments(self) -> List[Tuple[int, int, bool, bool]]:
+        """(start, end, decay, replicated over tp) runs inside this rank's shard, in shard-local coordinates."""
+        segs: List[Tuple[int, int, bool, bool]] = []
         lo, hi = self.shard_lo, self.shard_lo + self.shard_numel
         bounds = self.offsets + [self.numel]
-        for i, d in enumerate(self.decay):
+        for i, (d, r) in enumerate(zip(self.decay, self.replicated)):
             a, b = max(bounds[i], lo), min(bounds[i + 1], hi)
             if a >= b:
                 continue
-            if segs and segs[-1][2] == d and segs[-1][1] == a - lo:
-                segs[-1] = (segs[-1][0], b - lo, d)
+            if segs and segs[-1][2] == d and segs[-1][3] == r and segs[-1][1] == a - lo:
+                segs[-1] = (segs[-1][0], b - lo, d, r)
             else:
-                segs.append((a - lo, b - lo, d))
+                segs.append((a - lo, b - lo, d, r))
         return segs
 
     def reassign_grads(self) -> None:
@@ -217,9 +222,17 @@ class FusedAdamW:
             gs = self._reduce_grads(g)
             shards.append(gs)
             if self.max_grad_norm > 0:
-                tmp.zero_()
-                ext.sumsq(gs, tmp)
-                self.sumsq.add_(tmp, alpha=g.grad_scale ** 2)
+                if g.tp_size > 1 and any(g.replicated):
+                    # every tensor-parallel rank adds its shard to the world-wide sum: what all of them hold whole
+                    # enters with weight 1/tp so that it counts once (as the library path's clipping does)
+                    for a, b, _decay, rep in g._segments:
+                        tmp.zero_()
+                        ext.sumsq(gs[a:b], tmp)
+                        self.sumsq.add_(tmp, alpha=g.grad_scale ** 2 / (g.tp_size if rep else 1))
+                else:
+                    tmp.zero_()
+                    ext.sumsq(gs, tmp)
+                    self.sumsq.add_(tmp, alpha=g.grad_scale ** 2)
         if self.max_grad_norm > 0:
             for pg in self._norm_groups:
                 if pg is not None:
@@ -229,7 +242,7 @@ class FusedAdamW:
         for g, gs in zip(self.groups, shards):
             sharded = g.shard_world > 1
             p16_base = g.flat_p[g.shard_lo:g.shard_lo + g.shard_numel]
-            for a, b, decay in g._segments:
+            for a, b, decay, _rep in g._segments:
                 ext.adamw(g.master[a:b], p16_base[a:b], g.m[a:b], g.v[a:b], gs[a:b], self.lr, b1, b2, self.eps,
                           self.weight_decay if decay else 0.0, self.step_count, g.grad_scale, self.max_grad_norm,
                           self.sumsq if self.max_grad_norm > 0 else None, not sharded)

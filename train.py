@@ -164,6 +164,10 @@ def main(argv=None) -> int:
                       health_interval_s=cfg.elastic.health_check_interval_s,
                       drop_grace_s=cfg.elastic.drop_grace_period_s, min_nodes=cfg.elastic.min_nodes), topo)
     harness.install_signal_handlers()
+    if trainer.device.type == "cuda" and t.ckpt_interval > 0:
+        # pin the host staging buffers of the asynchronous checkpoints now, not inside the first save
+        pinned = harness.async_ckpt.prepare(trainer.model, trainer.optimizer)
+        log.info("pinned %.1f GB of host memory for checkpoint snapshots", pinned / 1e9)
 
     start_step = 0
     try:
