@@ -145,7 +145,7 @@ void gemm_pull(const Tensor& A, const Tensor& B, Tensor& D, int64_t epilogue, in
   TORCH_CHECK(!src_ptrs.empty() && src_ptrs.size() <= static_cast<size_t>(cmoe::kMaxPeers), "peer table size");
   for (size_t i = 0; i < src_ptrs.size(); ++i) g.pull_src.ptr[i] = reinterpret_cast<void*>(src_ptrs[i]);
   TORCH_CHECK(row_slot.scalar_type() == at::kInt && row_slot.numel() >= A.size(0));
-  TORCH_CHECK(tile_ready.scalar_type() == at::kInt && tile_ready.numel() >= max_m_tiles);
+  TORCH_CHECK(tile_ready.scalar_type() == at::kInt && tile_ready.numel() >= max_m_tiles * cmoe::kPullFlagsPerTile);
   g.pull_row_slot = row_slot.data_ptr<int>();
   g.pull_slots_per_src = slots_per_src;
   g.pull_K = static_cast<int>(pull_K);

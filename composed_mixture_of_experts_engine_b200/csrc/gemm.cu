@@ -39,6 +39,7 @@ constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int CHUNK_BYTES = 64 * BK * 2;  // one 64 x 64 bf16 box (MN-major operands) = 8 KiB
 constexpr int GEMM_THREADS = 192;
 constexpr int GEMM_THREADS_PULL = 320;  // + four row-pull warps (fused expert-parallel dispatch)
+constexpr int PULL_SUBS = 4;            // the pull warps fill a 128-row tile in quarters, each with its own ready flag
 constexpr int TMEM_COLS = 2 * BN;  // 512: two accumulators
 constexpr int GROUP_M_SWIZZLE = 8;
 // epilogue staging: two buffers of 128 rows x 128 bytes (32 fp32 or 64 bf16 columns) in the 128-byte swizzle, from
@@ -337,7 +338,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
         if (p.pull_row_slot != nullptr) {
           // the rows of this tile are written by the pull warps of some CTA of this launch
-          flag_wait_ge(p.tile_ready + ti.m0 / BM, p.pull_epoch, wc);
+          for (int q = 0; q < PULL_SUBS; ++q) flag_wait_ge(p.tile_ready + (ti.m0 / BM) * PULL_SUBS + q, p.pull_epoch, wc);
           asm volatile("fence.proxy.async.global;" ::: "memory");  // generic-proxy writes -> TMA reads
         }
         for (int kb = 0; kb < ti.k_blocks; ++kb) {
@@ -418,15 +419,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   } else if (warp >= 6) {
     // ------------------------------------------------------------------ row-pull warps (fused dispatch)
     if (p.pull_row_slot != nullptr) {
-      const int pw = warp - 6;  // 0..3: each warp brings in 32 of the 128 rows of a tile
-      if (p.pull_stamps != nullptr && threadIdx.x == 6 * 32 && static_cast<int>(blockIdx.x) < m_tiles)
+      const int pw = warp - 6;  // 0..3: each warp brings in a quarter of the rows of a work item
+      if (p.pull_stamps != nullptr && threadIdx.x == 6 * 32 && static_cast<int>(blockIdx.x) < m_tiles * PULL_SUBS)
         atomicMin(p.pull_stamps + 0, global_timer_ns());
-      for (int mt = blockIdx.x; mt < m_tiles; mt += gridDim.x) {
+      // Work items are quarter tiles (32 rows, 8 per warp) handed out in tile order: all CTAs first work on the
+      // earliest tiles, so the rows that the first wave of MMA tiles needs are complete after one or two rounds
+      // of loads instead of after a whole 128-row tile per CTA (one CTA moves ~16 GB/s at NVLink latency)
+      for (int item = blockIdx.x; item < m_tiles * PULL_SUBS; item += gridDim.x) {
+        const int mt = item / PULL_SUBS, sub = item % PULL_SUBS;
         if (p.tile_group[mt] >= 0) {
           // Two rows at a time and up to eight 16-byte loads per lane and row in flight (16 KiB per warp): remote
           // loads over NVLink take microseconds, so the transfer rate is set by the bytes in flight
-          for (int i = 0; i < 32; i += 2) {
-            const long long r0 = static_cast<long long>(mt) * BM + pw * 32 + i;
+          for (int i = 0; i < 32 / PULL_SUBS; i += 2) {
+            const long long r0 = static_cast<long long>(mt) * BM + sub * 32 + pw * (32 / PULL_SUBS) + i;
             int slot[2];
             const __nv_bfloat16* src[2];
             float sc[2];
@@ -479,10 +484,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         asm volatile("fence.proxy.async.global;" ::: "memory");
         asm volatile("bar.sync 2, 128;" ::: "memory");
         if (threadIdx.x == 6 * 32) {
-          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.tile_ready + mt), "r"(p.pull_epoch) : "memory");
+          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.tile_ready + mt * PULL_SUBS + sub),
+                       "r"(p.pull_epoch)
+                       : "memory");
         }
       }
-      if (p.pull_stamps != nullptr && threadIdx.x == 6 * 32 && static_cast<int>(blockIdx.x) < m_tiles)
+      if (p.pull_stamps != nullptr && threadIdx.x == 6 * 32 && static_cast<int>(blockIdx.x) < m_tiles * PULL_SUBS)
         atomicMax(p.pull_stamps + 1, global_timer_ns());
     }
   } else {

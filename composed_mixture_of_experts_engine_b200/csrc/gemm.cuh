@@ -73,9 +73,9 @@ struct GemmArgs {
   // the rows of A themselves before the tiles that need them run: row r of A is the token row
   // (slot % pull_slots_per_src) / pull_K of rank slot / pull_slots_per_src (slot = pull_row_slot[r]), read with
   // plain loads from that rank's buffer in pull_src (peer memory over NVLink, or local), times pull_slot_scale[slot]
-  // if given; padding rows are zero filled.  tile_ready[m] (uint32, this GPU's memory) is set to pull_epoch when
-  // 128-row tile m is complete, and the TMA producer of every tile waits (bounded) for it.  The transfer of later
-  // tiles overlaps the MMAs of earlier ones.
+  // if given; padding rows are zero filled.  tile_ready[4 m + q] (uint32, this GPU's memory, kPullFlagsPerTile words
+  // per tile) is set to pull_epoch when quarter q of 128-row tile m is complete, and the TMA producer of every
+  // tile waits (bounded) for its four flags.  The transfer of later tiles overlaps the MMAs of earlier ones.
   const int* pull_row_slot = nullptr;
   PeerTable pull_src = {};
   long long pull_slots_per_src = 0;
@@ -112,6 +112,7 @@ cudaError_t launch_gemm(const GemmArgs& args, cudaStream_t stream);
 // Two-SM variant (clusters of two CTAs, `tcgen05.mma.cta_group::2`, 256 x 256 tiles) for dense GEMMs and grouped-K
 // weight-gradient GEMMs with plain results; `gemm_2cta_supported` says whether a launch description qualifies.
 bool gemm_2cta_supported(const GemmArgs& args);
+constexpr int kPullFlagsPerTile = 4;  // words of GemmArgs::tile_ready per 128-row tile
 cudaError_t launch_gemm_2cta(const GemmArgs& args, cudaStream_t stream);
 
 }  // namespace cmoe

@@ -285,8 +285,8 @@ def gemm_pull(A: torch.Tensor, B: torch.Tensor, D: torch.Tensor, plan: MoEPlan, 
     receives the device timestamps of first / last row pulled and first / last MMA."""
     idx = A.device.index or 0
     ready = _tile_ready.get(idx)
-    if ready is None or ready.numel() < plan.max_m_tiles:
-        ready = torch.zeros(max(plan.max_m_tiles, 16384), device=A.device, dtype=torch.int32)
+    if ready is None or ready.numel() < 4 * plan.max_m_tiles:  # four flags per 128-row tile (csrc/gemm.cuh)
+        ready = torch.zeros(max(4 * plan.max_m_tiles, 65536), device=A.device, dtype=torch.int32)
         _tile_ready[idx] = ready
         _pull_epoch[idx] = 0
     _pull_epoch[idx] = (_pull_epoch[idx] + 1) % (1 << 30)

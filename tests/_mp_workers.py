@@ -495,6 +495,16 @@ def gpu_ep_layer(rank, world, transport):
         out[f"dx{it}"] = rel(x.grad, x2.grad)
         out[f"dw13_{it}"] = rel(layer.w13.grad, g13[mine[0]:mine[-1] + 1])
         out[f"dgate{it}"] = rel(layer.router.gate_w.grad, full.router.gate_w.grad)
+        if it == 1:
+            # the same inputs once more: bit-identical results (no sum in the exchange or in the expert GEMMs depends
+            # on the order in which peers or CTAs arrive), so any difference is a race
+            keep = [t.detach().clone() for t in (y, x.grad, layer.w13.grad, layer.w2.grad, layer.router.gate_w.grad)]
+            layer.zero_grad(set_to_none=True)
+            x3 = x.detach().clone().requires_grad_(True)
+            y3 = layer(x3)
+            y3.backward(dy)
+            again = (y3, x3.grad, layer.w13.grad, layer.w2.grad, layer.router.gate_w.grad)
+            out["replay"] = max(float((a.float() - b.float()).abs().max()) for a, b in zip(keep, again))
     check_status(dev)
     if transport.endswith("-debug"):  # nothing (this rank or a peer) wrote outside a symmetric buffer
         from composed_mixture_of_experts_engine_b200.parallel import symm

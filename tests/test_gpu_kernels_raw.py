@@ -210,7 +210,7 @@ def test_router_fwd_bwd(ext, status, N, H, E, K):
     counts = torch.empty(E, device="cuda", dtype=torch.int32)
     mean_prob = torch.empty(E, device="cuda", dtype=torch.float32)
     stats = torch.zeros(4, device="cuda", dtype=torch.float32)
-    ws = torch.zeros(2 * E + 2, device="cuda", dtype=torch.int32)
+    ws = torch.zeros(3 * E + 4, device="cuda", dtype=torch.int32)  # csrc/router.cuh: router_workspace_words
     for _ in range(2):  # twice: the workspace must come back clean
         ext.router_fwd(x, w, K, logits, idx, tw, lse, counts, mean_prob, stats, ws, status, 0)
     torch.cuda.synchronize()

@@ -55,6 +55,7 @@ def _world():
 def test_ep_layer_matches_single_gpu(transport):
     res = _spawn_gpu("gpu_ep_layer", _world(), transport)
     for r, out in res.items():
+        assert out.pop("replay") == 0.0, (r, "the same inputs twice gave different bits")
         for k, v in out.items():
             tol = 6e-2 if k.startswith("dgate") else 3e-2
             assert v < tol, (r, k, v, out)
