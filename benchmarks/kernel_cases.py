@@ -7,7 +7,8 @@ launches with CUDA events (an L2-sized buffer is overwritten between launches) a
 achieved bandwidth / throughput and the fraction of the measured peaks (MEASURED_PEAKS.json).  The same command
 line under ``ncu -k regex:<kernel> -c 1`` captures one launch of the case.
 
-Cases: adamw, rmsnorm, router (config-2 shape: T16384 d4096 E64 top2), gemm_dense, dense_shapes, grouped_fwd1, grouped_fwd2,
+Cases: adamw, rmsnorm, router / router_bwd (config-2 shape: T16384 d4096 E64 top2), gemm_dense, dense_shapes,
+grouped_fwd1, grouped_fwd1_pull (fused dispatch through a local one-entry peer table), grouped_fwd2,
 grouped_dgrad, grouped_wgrad, gather, combine.
 """
 
@@ -105,6 +106,29 @@ def main():
         ms = time_launches(lambda: fused_router_forward(x, w, K), max(args.iters, 20))
         nbytes = N * H * 2 + H * E * 2 + N * E * 4 + N * K * 8 + N * 4
         out.update(ms=ms, gbs=nbytes / ms / 1e6, frac_of_hbm=nbytes / ms / 1e6 / hbm, tokens_per_s=N / ms * 1e3)
+    elif args.case == "router_bwd":
+        # analytic d(logits) kernel + the two tcgen05 GEMMs of the router backward (config-2 shape)
+        N, H, E, K = 16384 // (2 if args.small else 1), 4096, 64, 2
+        x = torch.randn(N, H, device=dev, dtype=bf)
+        w = (torch.randn(H, E, device=dev) * 0.02).to(bf)
+        from composed_mixture_of_experts_engine_b200.ops.moe_router import fused_router_forward
+
+        o = fused_router_forward(x, w, K)
+        gw = torch.randn(N, K, device=dev)
+        ga = torch.tensor([0.01], device=dev)
+        gz = torch.tensor([0.001], device=dev)
+        gl16 = torch.empty(N, E, device=dev, dtype=bf)
+
+        def bwd():
+            ext.router_bwd(o.logits, o.lse, o.idx32, gw, o.counts, ga, gz, gl16, None)
+            kernels.linear_nt(gl16, w)      # grad_tokens = gl @ gate_w^T
+            kernels.linear_tn(x, gl16)      # grad_gate_w = tokens^T @ gl
+
+        ms = time_launches(bwd, max(args.iters, 20))
+        only = time_launches(lambda: ext.router_bwd(o.logits, o.lse, o.idx32, gw, o.counts, ga, gz, gl16, None),
+                             max(args.iters, 20))
+        nbytes = N * E * 4 + N * E * 2 + 2 * N * H * 2 + H * E * 4  # logits in, gl out; tokens in, grad_tokens out
+        out.update(ms=ms, dlogits_kernel_ms=only, gbs=nbytes / ms / 1e6, frac_of_hbm=nbytes / ms / 1e6 / hbm)
     elif args.case == "gemm_dense":
         M = N = K = 8192 // (2 if args.small else 1)
         A = torch.randn(M, K, device=dev, dtype=bf)
@@ -152,6 +176,20 @@ def main():
         if args.case == "grouped_fwd1":
             fn = lambda: kernels.gemm(X, W13.view(-1, H), Hact, mode=GEMM_GROUPED_M, epilogue=EPI_SWIGLU_FWD, N=F, K=H,
                                       b_group_rows=2 * F, split_n=F, aux_out=GU, **common)
+            fl = 2 * R * 2 * F * H
+        elif args.case == "grouped_fwd1_pull":
+            # the same GEMM with the fused dispatch: four extra warps per CTA fill X from a token buffer through a
+            # one-entry "peer" table that points at this GPU's own memory (what the pull warps cost the tensor pipe)
+            Tn, Kk = R // 8, 8
+            idx = torch.stack([torch.randperm(E, device=dev)[:Kk] for _ in range(Tn)]).to(torch.int32)
+            plan = kernels.moe_plan(idx, E)
+            tok = torch.randn(Tn, H, device=dev, dtype=bf)
+            Xp = torch.empty(plan.cap_rows, H, device=dev, dtype=bf)
+            Hp = torch.empty(plan.cap_rows, F, device=dev, dtype=bf)
+            GUp = torch.empty(plan.cap_rows, 2 * F, device=dev, dtype=bf)
+            fn = lambda: kernels.gemm_pull(Xp, W13.view(-1, H), Hp, plan, epilogue=EPI_SWIGLU_FWD, N=F, K=H, groups=E,
+                                           b_group_rows=2 * F, split_n=F, aux_out=GUp, src_ptrs=[tok.data_ptr()],
+                                           slots_per_src=Tn * Kk, pull_K=Kk, ld_src=H)
             fl = 2 * R * 2 * F * H
         elif args.case == "grouped_fwd2":
             fn = lambda: kernels.gemm(Hact, W2.view(-1, F), Y, mode=GEMM_GROUPED_M, N=H, K=F, b_group_rows=H, **common)

@@ -12,6 +12,17 @@ weights, so the first losses differ only by the expert mix (5.68 against 5.70 he
 (200 steps: 2.28 against 2.42, largest gap 0.22); identical curves cannot be expected.
 Reference recipe: cross entropy on fp32 logits, AdamW(betas=(0.9, 0.95)), global-norm clip 1.0
 (train.py:207-212,297-323 of the reference).
+
+    python benchmarks/loss_parity.py --device cuda --steps 200
+    torchrun --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 benchmarks/loss_parity.py --device cuda \
+        [--transport nccl]
+
+``--device cuda`` compares this package with itself: the attention decoder trained by the public ``Trainer`` in bf16
+on the sm_100a kernels (fused optimizer with fp32 master weights; on several GPUs dp = ep = N with the peer-memory
+or the NCCL transport) against the same decoder in fp32 on the PyTorch path on CPU (stock AdamW), from equal
+weights on equal batches (the CPU run sees the union of all ranks' batches, which is what data parallelism
+averages over).  Here the two sides compute the same function, so the curves must agree to bf16 rounding; the line
+reports the largest loss gap and the largest relative gap of the gradient norms.
 """
 
 from __future__ import annotations
@@ -99,12 +110,105 @@ def _train(model, batches, lr: float):
     return losses
 
 
+def _self_parity(a) -> None:
+    """bf16 CUDA trainer (this package's kernels) against the fp32 CPU path of the same decoder."""
+    import os
+
+    if str(ROOT) not in sys.path:
+        sys.path.insert(0, str(ROOT))
+    if a.transport != "auto":
+        os.environ["CMOE_EP_TRANSPORT"] = os.environ["CMOE_DP_TRANSPORT"] = a.transport
+    import torch.distributed as dist
+
+    from composed_mixture_of_experts_engine_b200.engine import Trainer, init_distributed
+    from composed_mixture_of_experts_engine_b200.utils.config import MoEConfig
+
+    rank, world = init_distributed("cuda")
+
+    def cfg(dtype, dp):
+        return MoEConfig.from_dict({
+            "model": dict(arch="moe_decoder", hidden_dim=256, num_layers=2, num_heads=4, num_experts=8, top_k=2,
+                          ffn_dim=256, vocab_size=2048, sequence_length=256, dtype=dtype, aux_loss_coeff=0.01,
+                          init_std=0.02),
+            "training": dict(micro_batch_size=a.batch, gradient_accumulation_steps=1, global_batch_size=a.batch * dp,
+                             max_steps=10 * a.steps, warmup_steps=0, learning_rate=a.lr, grad_clip=1.0, seed=3),
+            "parallelism": dict(data_parallel=dp, expert_parallel=dp, ep_from_dp=True)})
+
+    gpu = Trainer(cfg("bfloat16", world))
+    V, S = 2048, 256
+    pools = []
+    for r in range(world):  # every rank's pool of batches, seen repeatedly so that the loss falls within the run
+        gen = torch.Generator().manual_seed(100 + r)
+        pools.append([(torch.randint(0, V, (a.batch, S), generator=gen), torch.randint(0, V, (a.batch, S), generator=gen))
+                      for _ in range(4)])
+    # the fp32 twin on CPU (rank 0 only): all experts in one process, the union of the ranks' batches per step
+    cpu = None
+    full_state = None
+    if world > 1:
+        # gather the expert shards so that rank 0 can assemble the whole model
+        parts = [None] * world
+        dist.all_gather_object(parts, {k: v.float().cpu() for k, v in gpu.model.state_dict().items()})
+        full_state = {}
+        for k in parts[0]:
+            if k.rsplit(".", 1)[-1] in ("w13", "w2"):
+                full_state[k] = torch.cat([p[k] for p in parts], dim=0)
+            else:
+                full_state[k] = parts[0][k]
+    else:
+        full_state = {k: v.float().cpu() for k, v in gpu.model.state_dict().items()}
+    if rank == 0:
+        from composed_mixture_of_experts_engine_b200.parallel import ParallelTopology
+
+        c = cfg("float32", 1)
+        d = c.to_dict()
+        d["training"].update(micro_batch_size=a.batch * world, global_batch_size=a.batch * world)
+        cpu = Trainer(MoEConfig.from_dict(d), device_type="cpu", topology=ParallelTopology(1, 0, 1, 1))
+        cpu.model.load_state_dict(full_state)
+        torch.set_num_threads(max(1, min(16, os.cpu_count() or 1)))
+    l_gpu, l_cpu, n_gpu, n_cpu = [], [], [], []
+    for i in range(a.steps):
+        ids, tgt = pools[rank][i % 4]
+        loss = gpu.train_step(ids, tgt).detach().clone()
+        if world > 1:
+            dist.all_reduce(loss)
+            loss /= world
+        l_gpu.append(float(loss))
+        n_gpu.append(gpu.optimizer.grad_norm())
+        if cpu is not None:
+            ids_all = torch.cat([pools[r][i % 4][0] for r in range(world)])
+            tgt_all = torch.cat([pools[r][i % 4][1] for r in range(world)])
+            l_cpu.append(float(cpu.train_step(ids_all, tgt_all)))
+            n_cpu.append(cpu.last_grad_norm)
+        if world > 1:
+            dist.barrier()  # the other ranks do not start the next device step while rank 0 is still on its CPU step
+    if rank == 0:
+        diffs = [abs(x - y) for x, y in zip(l_gpu, l_cpu)]
+        rel_norm = [abs(x - y) / max(y, 1e-12) for x, y in zip(n_gpu, n_cpu)]
+        print(json.dumps({
+            "mode": "bf16 CUDA kernels vs fp32 CPU path of the same decoder", "n_gpus": world,
+            "transport": ("peer memory" if a.transport == "auto" else a.transport) if world > 1 else "none",
+            "steps": a.steps, "first_loss": [l_gpu[0], l_cpu[0]], "last_loss": [l_gpu[-1], l_cpu[-1]],
+            "max_abs_loss_gap": max(diffs), "mean_abs_loss_gap": sum(diffs) / len(diffs),
+            "max_rel_grad_norm_gap": max(rel_norm), "mean_rel_grad_norm_gap": sum(rel_norm) / len(rel_norm),
+            "grad_norm_first_last": [[n_gpu[0], n_cpu[0]], [n_gpu[-1], n_cpu[-1]]]}))
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--batch", type=int, default=4)
     ap.add_argument("--lr", type=float, default=3e-4)
+    ap.add_argument("--device", choices=["cpu", "cuda"], default="cpu",
+                    help="cpu: against the unmodified reference in fp32; cuda: the bf16 kernels against this package's "
+                         "own fp32 CPU path")
+    ap.add_argument("--transport", choices=["auto", "nccl"], default="auto", help="--device cuda on several GPUs")
     a = ap.parse_args()
+    if a.device == "cuda":
+        _self_parity(a)
+        return
     if not (REF / "pkg").is_dir():
         print(json.dumps({"unavailable": "baseline/_ref is not installed"}))
         return

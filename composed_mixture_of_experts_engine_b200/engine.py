@@ -149,6 +149,7 @@ class Trainer:
             self.stage = PipelineStage(topology.pp_rank, topology.pp_size, self.model, topology)
         self.last_aux: Optional[torch.Tensor] = None
         self.last_z: Optional[torch.Tensor] = None
+        self.last_grad_norm: float = 0.0  # library path: global gradient norm of the last step (before clipping)
 
     def _sync_tensor_parallel_replicas(self) -> None:
         """Tensor-parallel ranks draw their weight slices from different random streams; everything that is NOT
@@ -287,6 +288,7 @@ class Trainer:
                 dist.all_reduce(total, group=pp_process_group(topo))
         else:
             total = sum(sq.values())
+        self.last_grad_norm = float(total.sqrt())
         coef = float(max_norm / (total.sqrt() + 1e-6))
         if coef < 1.0:
             for p in self.model.parameters():

@@ -198,6 +198,41 @@ def trainer_steps(rank, world, config_path, steps):
             "local_experts": tr.model.blocks[0].moe.local_expert_ids}
 
 
+def train_main_tp(rank, world, tmp_dir):
+    """``train.py`` itself on `world` gloo ranks with tensor parallelism and sequence parallelism OFF: the
+    tensor-parallel peers of one data replica must be fed the same tokens (the row-parallel all-reduce sums partial
+    products of ONE activation), which shows as identical logged losses on all of them."""
+    import json
+
+    import yaml
+
+    import train as train_main_module
+
+    cfg = {
+        "model": dict(arch="moe_decoder", hidden_dim=32, num_layers=2, num_heads=2, num_experts=4, top_k=2,
+                      ffn_dim=64, vocab_size=128, sequence_length=16, dtype="float32", aux_loss_coeff=0.01,
+                      init_std=0.02),
+        "training": dict(micro_batch_size=2, gradient_accumulation_steps=1, global_batch_size=2, max_steps=4,
+                         warmup_steps=0, learning_rate=1e-3, log_interval=1, ckpt_interval=0, seed=0),
+        "parallelism": dict(data_parallel=1, expert_parallel=1, tensor_parallel=world, pipeline_parallel=1,
+                            ep_from_dp=True, sequence_parallel=False),
+        "checkpoint": dict(local_dir=f"{tmp_dir}/ck{rank}", remote_uri=f"file://{tmp_dir}/remote{rank}"),
+        "telemetry": dict(log_dir=f"{tmp_dir}/logs", tensorboard_dir=f"{tmp_dir}/tb",
+                          json_path=f"{tmp_dir}/logs/step.jsonl"),
+    }
+    path = f"{tmp_dir}/tp{rank}.yaml"
+    with open(path, "w") as f:
+        yaml.safe_dump(cfg, f)
+    # train.main() initialises (and at the end destroys) the process group itself
+    import torch.distributed as dist
+
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    rc = train_main_module.main(["--config", path, "--cpu", "--no-wandb"])
+    rows = [json.loads(l) for l in open(f"{tmp_dir}/logs/step.rank{rank}.jsonl") if l.strip().startswith("{")]
+    return {"rc": rc, "losses": [r["loss"] for r in rows if "loss" in r]}
+
+
 def moe_layer_tp(rank, world):
     """MoE layer with the experts sliced on the FFN width over tp=world ranks vs the unsliced layer: output, token
     gradient, router gate gradient (needs the all-reduce of the partial gate-weight gradients) and weight slices."""

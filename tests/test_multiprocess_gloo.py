@@ -173,6 +173,13 @@ def test_fused_optimizer_flat_shards_are_re_sliced_by_parameter_name(tmp_path):
         assert after[r]["worst"] == 0.0
 
 
+def test_train_py_feeds_tensor_parallel_peers_the_same_tokens(tmp_path):
+    res = _spawn("train_main_tp", 2, str(tmp_path), timeout=600)
+    assert res[0]["rc"] == 0 and res[1]["rc"] == 0
+    assert len(res[0]["losses"]) >= 3
+    assert res[0]["losses"] == res[1]["losses"]
+
+
 def test_moe_layer_tensor_parallel_matches_unsliced():
     res = _spawn("moe_layer_tp", 2)
     for r, out in res.items():
