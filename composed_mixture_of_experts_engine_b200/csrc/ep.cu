@@ -114,7 +114,9 @@ __global__ void __launch_bounds__(256) combine_rows_peer_kernel(const PeerTable 
       my_row = reinterpret_cast<const int*>(slot_row.ptr[my_owner])[slot_base + t * K + lane];
       my_w = w ? w[t * K + lane] : 1.f;
     }
-    for (int c = lane * 8; c < H; c += 256) {
+    for (int cb = 0; cb < H; cb += 256) {  // the same trip count on every lane: the shuffles below need all 32
+      const int c = cb + lane * 8;
+      const bool act = c < H;
       float acc[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
@@ -122,7 +124,7 @@ __global__ void __launch_bounds__(256) combine_rows_peer_kernel(const PeerTable 
         const int owner = __shfl_sync(0xffffffffu, my_owner, k);
         const int row = __shfl_sync(0xffffffffu, my_row, k);
         const float wk = __shfl_sync(0xffffffffu, my_w, k);
-        if (row < 0) continue;
+        if (row < 0 || !act) continue;
         float f[8];
         // rows pushed here by the owners' GEMM epilogues sit at [t*K + k]; otherwise pull from the owner
         const __nv_bfloat16* src = local_rows ? local_rows + (t * K + k) * ld_rows
@@ -132,7 +134,7 @@ __global__ void __launch_bounds__(256) combine_rows_peer_kernel(const PeerTable 
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] += wk * f[j];
       }
-      st8(y + t * ld_y + c, acc);
+      if (act) st8(y + t * ld_y + c, acc);
     }
   }
 }

@@ -28,14 +28,39 @@ def attention_reference(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> to
     return out.permute(0, 2, 1, 3).to(q.dtype).contiguous()
 
 
+_NATIVE_GQA = {"cuda": None}  # None: not probed yet; True / False: whether a fused kernel takes grouped K / V
+
+
+def sdpa_grouped(qt: torch.Tensor, kt: torch.Tensor, vt: torch.Tensor) -> torch.Tensor:
+    """Causal ``scaled_dot_product_attention`` on [B, heads, S, hd] tensors whose K / V carry fewer heads than Q.
+
+    On CUDA the fused library kernels read the shared K / V heads in place (``enable_gqa=True``) instead of from
+    copies repeated ``nh / nkv`` times.  Whether the installed PyTorch has a fused kernel for that is found out on
+    the first call (restricted to the fused backends, so that a silent fall-back to the unfused math kernel cannot
+    happen); if not, K / V are repeated as before."""
+    nh, nkv = qt.shape[1], kt.shape[1]
+    if nkv == nh:
+        return F.scaled_dot_product_attention(qt, kt, vt, is_causal=True)
+    if qt.is_cuda and _NATIVE_GQA["cuda"] is not False:
+        try:
+            from torch.nn.attention import SDPBackend, sdpa_kernel
+
+            with sdpa_kernel([SDPBackend.CUDNN_ATTENTION, SDPBackend.FLASH_ATTENTION]):
+                out = F.scaled_dot_product_attention(qt, kt, vt, is_causal=True, enable_gqa=True)
+            _NATIVE_GQA["cuda"] = True
+            return out
+        except Exception:
+            if _NATIVE_GQA["cuda"] is True:
+                raise
+            _NATIVE_GQA["cuda"] = False
+    rep = nh // nkv
+    return F.scaled_dot_product_attention(qt, kt.repeat_interleave(rep, dim=1), vt.repeat_interleave(rep, dim=1),
+                                          is_causal=True)
+
+
 def _sdpa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
-    nh, nkv = q.shape[2], k.shape[2]
     qt, kt, vt = (t.permute(0, 2, 1, 3) for t in (q, k, v))
-    if nkv != nh:
-        kt = kt.repeat_interleave(nh // nkv, dim=1)
-        vt = vt.repeat_interleave(nh // nkv, dim=1)
-    out = F.scaled_dot_product_attention(qt, kt, vt, is_causal=True)
-    return out.permute(0, 2, 1, 3).contiguous()
+    return sdpa_grouped(qt, kt, vt).permute(0, 2, 1, 3).contiguous()
 
 
 def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:

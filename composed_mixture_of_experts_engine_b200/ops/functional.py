@@ -200,11 +200,9 @@ class _RopeAttentionFn(torch.autograd.Function):
             q = t[:, :, :nh].permute(0, 2, 1, 3).requires_grad_()
             k = t[:, :, nh: nh + nkv].permute(0, 2, 1, 3).requires_grad_()
             v = t[:, :, nh + nkv:].permute(0, 2, 1, 3).requires_grad_()
-            kk, vv = k, v
-            if nkv != nh:
-                kk = k.repeat_interleave(nh // nkv, dim=1)
-                vv = v.repeat_interleave(nh // nkv, dim=1)
-            out = F.scaled_dot_product_attention(q, kk, vv, is_causal=True)
+            from .attention import sdpa_grouped
+
+            out = sdpa_grouped(q, k, v)  # grouped K / V are read in place where the library has a fused kernel for it
         ctx.inner = (q, k, v, out)
         ctx.save_for_backward(cos, sin)
         ctx.dims = (B, S, heads, hd, nh, nkv)

@@ -36,6 +36,11 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip_gpu)
         if "multigpu" in item.keywords and n_dev < 2:
             item.add_marker(skip_multi)
+    # Collection order of the GPU suites: the attention kernels (the largest hand-written kernels) run after every
+    # other suite, and the allocation-free entry point, which shares one device array between calls, runs last; a
+    # run that stops at the first failure has then already run everything else.
+    late = {"test_gpu_attention.py": 1, "test_zz_no_alloc.py": 2}
+    items.sort(key=lambda it: late.get(Path(str(it.fspath)).name, 0))  # stable: the rest keeps its order
 
 
 def find_free_port() -> int:

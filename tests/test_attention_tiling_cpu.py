@@ -5,7 +5,7 @@ rescaled by ``alpha`` of the *previous* tile when that tile's partial product is
 i is read back while tile i+1 is in its softmax).  The backward walks the query tiles at or below a key tile's
 diagonal and forms P from the saved log-sum-exp, dS = P (dP - delta) scale, and the three gradient products.
 These tests pin that arithmetic independently of the GPU; the kernels themselves are tested in
-tests/test_zy_gpu_attention.py.
+tests/test_gpu_attention.py.
 """
 
 from __future__ import annotations
