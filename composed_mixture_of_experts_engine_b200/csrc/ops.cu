@@ -629,97 +629,58 @@ __global__ void __launch_bounds__(PLAN_WARPS * 32) moe_plan_assign_kernel(const 
 }
 
 // ------------------------------------------------------------------------------------ gather / combine
-__global__ void __launch_bounds__(256) gather_rows_kernel(const __nv_bfloat16* __restrict__ src,
-                                                          const int* __restrict__ row_slot, int slot_div,
-                                                          const float* __restrict__ slot_scale,
-                                                          __nv_bfloat16* __restrict__ out, long long cap_rows,
-                                                          const int* __restrict__ num_m_tiles, int H, long long ld_src,
-                                                          long long ld_out) {
-  // one warp per output row; up to eight 16-byte loads per lane are issued before the first store, and the slot
-  // of the warp's next row is fetched while the current row is in flight
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ row_slot,
+                                   int slot_div, const float* __restrict__ slot_scale,
+                                   __nv_bfloat16* __restrict__ out, long long cap_rows,
+                                   const int* __restrict__ num_m_tiles, int H, long long ld_src, long long ld_out) {
   const long long n_rows = num_m_tiles ? min(static_cast<long long>(*num_m_tiles) * 128, cap_rows) : cap_rows;
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
-  const long long stride = static_cast<long long>(gridDim.x) * warps_per_block;
-  long long r = blockIdx.x * static_cast<long long>(warps_per_block) + (threadIdx.x >> 5);
-  int slot = r < n_rows ? row_slot[r] : -1;
-  for (; r < n_rows; r += stride) {
-    const int next_slot = (r + stride < n_rows) ? row_slot[r + stride] : -1;
+  for (long long r = blockIdx.x * static_cast<long long>(warps_per_block) + (threadIdx.x >> 5); r < n_rows;
+       r += static_cast<long long>(gridDim.x) * warps_per_block) {
+    const int slot = row_slot[r];
     __nv_bfloat16* o = out + r * ld_out;
     if (slot < 0) {
       for (int c = lane * 8; c < H; c += 256) *reinterpret_cast<uint4*>(o + c) = make_uint4(0u, 0u, 0u, 0u);
     } else {
       const __nv_bfloat16* s = src + static_cast<long long>(slot / slot_div) * ld_src;
-      const float sc = slot_scale ? slot_scale[slot] : 1.f;
-      for (int c0 = lane * 8; c0 < H; c0 += 2048) {
-        uint4 v[8];
+      if (slot_scale == nullptr) {
+        for (int c = lane * 8; c < H; c += 256) *reinterpret_cast<uint4*>(o + c) = *reinterpret_cast<const uint4*>(s + c);
+      } else {
+        const float sc = slot_scale[slot];
+        for (int c = lane * 8; c < H; c += 256) {
+          float f[8];
+          load8(s + c, f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          if (c0 + j * 256 < H) v[j] = *reinterpret_cast<const uint4*>(s + c0 + j * 256);  // a token row is read top-k times: keep it cached
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          if (c0 + j * 256 < H) {
-            if (slot_scale != nullptr) {
-              const float2 a = unpack_bf16x2(v[j].x), b2 = unpack_bf16x2(v[j].y), c2 = unpack_bf16x2(v[j].z),
-                           d = unpack_bf16x2(v[j].w);
-              v[j].x = pack_bf16x2(a.x * sc, a.y * sc);
-              v[j].y = pack_bf16x2(b2.x * sc, b2.y * sc);
-              v[j].z = pack_bf16x2(c2.x * sc, c2.y * sc);
-              v[j].w = pack_bf16x2(d.x * sc, d.y * sc);
-            }
-            *reinterpret_cast<uint4*>(o + c0 + j * 256) = v[j];
-          }
+          for (int j = 0; j < 8; ++j) f[j] *= sc;
+          store8(o + c, f);
         }
       }
     }
-    slot = next_slot;
   }
 }
 
-__global__ void __launch_bounds__(256) combine_rows_kernel(const __nv_bfloat16* __restrict__ rows,
-                                                           const int* __restrict__ slot_row,
-                                                           const float* __restrict__ w, __nv_bfloat16* __restrict__ y,
-                                                           long long n_tokens, int K, int H, long long ld_rows,
-                                                           long long ld_y) {
-  // one warp per token: lanes 0..K-1 look up the K (row, weight) pairs once, then for every 512-byte column block
-  // the loads of up to eight rows are issued before the first one is used (K x 16 bytes in flight per lane)
+__global__ void combine_rows_kernel(const __nv_bfloat16* __restrict__ rows, const int* __restrict__ slot_row,
+                                    const float* __restrict__ w, __nv_bfloat16* __restrict__ y, long long n_tokens,
+                                    int K, int H, long long ld_rows, long long ld_y) {
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   for (long long t = blockIdx.x * static_cast<long long>(warps_per_block) + (threadIdx.x >> 5); t < n_tokens;
        t += static_cast<long long>(gridDim.x) * warps_per_block) {
-    int my_row = -1;
-    float my_w = 0.f;
-    if (lane < K) {
-      my_row = slot_row[t * K + lane];
-      my_w = w ? w[t * K + lane] : 1.f;
-    }
-    for (int cb = 0; cb < H; cb += 256) {  // the same trip count on every lane: the shuffles below need all 32
-      const int c = cb + lane * 8;
-      const bool act = c < H;
+    for (int c = lane * 8; c < H; c += 256) {
       float acc[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-      for (int k0 = 0; k0 < K; k0 += 8) {
-        uint4 v[8];
-        float wk[8];
+      for (int k = 0; k < K; ++k) {
+        const int r = slot_row[t * K + k];
+        if (r < 0) continue;
+        const float wk = w ? w[t * K + k] : 1.f;
+        float f[8];
+        load8(rows + static_cast<long long>(r) * ld_rows + c, f);
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const int row = __shfl_sync(0xffffffffu, my_row, (k0 + q) & 31);
-          wk[q] = __shfl_sync(0xffffffffu, my_w, (k0 + q) & 31);
-          if (k0 + q >= K || row < 0) wk[q] = 0.f;
-          v[q] = make_uint4(0u, 0u, 0u, 0u);
-          if (act && k0 + q < K && row >= 0)
-            v[q] = __ldcs(reinterpret_cast<const uint4*>(rows + static_cast<long long>(row) * ld_rows + c));
-        }
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const float2 a = unpack_bf16x2(v[q].x), b2 = unpack_bf16x2(v[q].y), c2 = unpack_bf16x2(v[q].z),
-                       d = unpack_bf16x2(v[q].w);
-          acc[0] += wk[q] * a.x; acc[1] += wk[q] * a.y; acc[2] += wk[q] * b2.x; acc[3] += wk[q] * b2.y;
-          acc[4] += wk[q] * c2.x; acc[5] += wk[q] * c2.y; acc[6] += wk[q] * d.x; acc[7] += wk[q] * d.y;
-        }
+        for (int j = 0; j < 8; ++j) acc[j] += wk * f[j];
       }
-      if (act) store8(y + t * ld_y + c, acc);
+      store8(y + t * ld_y + c, acc);
     }
   }
 }
@@ -893,7 +854,7 @@ cudaError_t launch_gather_rows(const void* src, const int* row_slot, int slot_di
 
 cudaError_t launch_combine_rows(const void* rows, const int* slot_row, const float* w, void* y, long long n_tokens,
                                 int K, int H, long long ld_rows, long long ld_y, cudaStream_t stream) {
-  if (H % 8 != 0 || n_tokens <= 0 || K <= 0 || K > 32) return cudaErrorInvalidValue;  // one lane per (token, k) pair
+  if (H % 8 != 0 || n_tokens <= 0) return cudaErrorInvalidValue;
   combine_rows_kernel<<<grid_for(n_tokens, 8, 148 * 8), 256, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(rows), slot_row, w, reinterpret_cast<__nv_bfloat16*>(y), n_tokens, K, H,
       ld_rows, ld_y);
