@@ -218,6 +218,21 @@ def main() -> int:
         comm = out["standalone"]["dispatch_ms"] + out["standalone"]["combine_ms"]
         for name, v in out["transports"].items():
             v["comm_compute_overlap_ratio_fwd"] = overlap_ratio(comm, lf, v["fwd_ms"])
+    if world > 1 and "peer-push" in out["transports"]:
+        # device timestamps of the fused GEMM1 (first / last row pulled, first / last MMA) of one more forward pass
+        os.environ["CMOE_EP_TRANSPORT"], os.environ["CMOE_EP_PUSH"] = "auto", "1"
+        layer.enable_timing(True)
+        for _ in range(3):
+            fwd()
+        torch.cuda.synchronize()
+        stamps = layer._last_plan_holder.get("pull_stamps")
+        if stamps is not None:
+            p0, p1, m0, m1 = (int(v) for v in stamps.tolist())
+            out["fused_gemm1_timeline_us"] = {"pull_first_to_last": (p1 - p0) / 1e3, "mma_first_to_last": (m1 - m0) / 1e3,
+                                              "first_mma_after_first_pull": (m0 - p0) / 1e3,
+                                              "last_mma_after_last_pull": (m1 - p1) / 1e3,
+                                              "overlap_ratio": layer.last_overlap_ratio}
+        layer.enable_timing(False)
     out["rows_dropped_for_buffer_space"] = int(overflow_counter(dev).item()) if world > 1 else 0
     out["rows_this_rank"] = rows
     if rank == 0:

@@ -145,6 +145,33 @@ __device__ __forceinline__ bool flag_wait_ge(const uint32_t* flag, uint32_t targ
   return true;
 }
 
+// The same bounded wait on a flag that a CTA of this GPU writes (gpu-scope acquire: cheaper than the system-scope
+// one that flags written by peers need).
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool flag_wait_ge_gpu(const uint32_t* flag, uint32_t target, const WaitCtx& w,
+                                                 int code = ST_TIMEOUT_PEER_FLAG) {
+  if ((int32_t)(ld_acquire_gpu(flag) - target) >= 0) return true;
+  if (w.abort_flag && *w.abort_flag) return false;
+  const unsigned long long t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while ((int32_t)(ld_acquire_gpu(flag) - target) < 0) {
+    __nanosleep(64);
+    if (((++spins) & 31u) == 0u) {
+      if (w.abort_flag && *w.abort_flag) return false;
+      if (global_timer_ns() - t0 > w.timeout_ns) {
+        if (w.abort_flag) *w.abort_flag = 1;
+        if (w.status) atomicCAS(w.status, 0, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
 // ----------------------------------------------------------------------------
 // TMA (tiled bulk tensor copies, this GPU's memory only; no cluster broadcast)
 // ----------------------------------------------------------------------------

@@ -326,46 +326,54 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    // One elected lane issues the loads.  With the fused row pull the whole warp walks the tiles: lanes 0..3 each
+    // poll one of the tile's four quarter flags at the same time (one L2 round trip per tile instead of four in a
+    // row, which the four buffered stages hide), then lane 0 goes on alone.
+    const bool pulling = p.pull_row_slot != nullptr;
+    if (lane == 0 || pulling) {
       int stage = 0;
       uint32_t phase = 0;
       for (int t = blockIdx.x; t < n_total; t += gridDim.x) {
         const Tile ti = decode_tile(p, t, m_tiles, n_tiles);
         if (ti.skip || ti.k_blocks == 0) continue;
-        if (p.ready_flags != nullptr) {
+        if (lane == 0 && p.ready_flags != nullptr) {
           const uint32_t* f = p.ready_flags + (long long)ti.group * p.ready_stride;
           for (int s = 0; s < p.ready_count; ++s) flag_wait_ge(f + s, p.ready_target, wc);
         }
-        if (p.pull_row_slot != nullptr) {
-          // the rows of this tile are written by the pull warps of some CTA of this launch
-          for (int q = 0; q < PULL_SUBS; ++q) flag_wait_ge(p.tile_ready + (ti.m0 / BM) * PULL_SUBS + q, p.pull_epoch, wc);
-          asm volatile("fence.proxy.async.global;" ::: "memory");  // generic-proxy writes -> TMA reads
+        if (pulling) {
+          // the rows of this tile are written by the pull warps of some CTAs of this launch
+          if (lane < PULL_SUBS) flag_wait_ge_gpu(p.tile_ready + (ti.m0 / BM) * PULL_SUBS + lane, p.pull_epoch, wc);
+          __syncwarp();
+          if (lane == 0) asm volatile("fence.proxy.async.global;" ::: "memory");  // generic-proxy writes -> TMA reads
         }
-        for (int kb = 0; kb < ti.k_blocks; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, wc, ST_TIMEOUT_SMEM_EMPTY)) break;
-          mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
-          uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
-          uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
-          const int k = kb * BK;
-          if (p.a_mn) {
-            tma_load_2d(a_dst, &tmA, &full_bar[stage], ti.a_mn0, ti.a_k0 + k);
-            tma_load_2d(a_dst + CHUNK_BYTES, &tmA, &full_bar[stage], ti.a_mn0 + 64, ti.a_k0 + k);
-          } else {
-            tma_load_2d(a_dst, &tmA, &full_bar[stage], ti.a_k0 + k, ti.a_mn0);
-          }
-          if (p.b_mn) {
+        if (lane == 0) {
+          for (int kb = 0; kb < ti.k_blocks; ++kb) {
+            if (!mbar_wait(&empty_bar[stage], phase ^ 1u, wc, ST_TIMEOUT_SMEM_EMPTY)) break;
+            mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
+            uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
+            uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
+            const int k = kb * BK;
+            if (p.a_mn) {
+              tma_load_2d(a_dst, &tmA, &full_bar[stage], ti.a_mn0, ti.a_k0 + k);
+              tma_load_2d(a_dst + CHUNK_BYTES, &tmA, &full_bar[stage], ti.a_mn0 + 64, ti.a_k0 + k);
+            } else {
+              tma_load_2d(a_dst, &tmA, &full_bar[stage], ti.a_k0 + k, ti.a_mn0);
+            }
+            if (p.b_mn) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              tma_load_2d(b_dst + j * CHUNK_BYTES, &tmB, &full_bar[stage], ti.b_n0 + 64 * j, ti.b_k0 + k);
-          } else {
-            tma_load_2d(b_dst, &tmB, &full_bar[stage], ti.b_k0 + k, ti.b_n0);
-            tma_load_2d(b_dst + 128 * BK * 2, &tmB, &full_bar[stage], ti.b_k0 + k, ti.b_n1);
-          }
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1u;
+              for (int j = 0; j < 4; ++j)
+                tma_load_2d(b_dst + j * CHUNK_BYTES, &tmB, &full_bar[stage], ti.b_n0 + 64 * j, ti.b_k0 + k);
+            } else {
+              tma_load_2d(b_dst, &tmB, &full_bar[stage], ti.b_k0 + k, ti.b_n0);
+              tma_load_2d(b_dst + 128 * BK * 2, &tmB, &full_bar[stage], ti.b_k0 + k, ti.b_n1);
+            }
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
           }
         }
+        if (pulling) __syncwarp();
         if (*abort_flag) break;
       }
     }
