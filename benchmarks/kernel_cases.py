@@ -68,6 +68,9 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--small", action="store_true", help="quarter-size inputs (for multi-pass profiler captures)")
     ap.add_argument("--rows", type=int, default=65536, help="expert-sorted rows of the grouped cases")
+    ap.add_argument("--experts", type=int, default=64, help="experts of the grouped cases")
+    ap.add_argument("--hidden", type=int, default=2048, help="model width of the grouped cases")
+    ap.add_argument("--ffn", type=int, default=1024, help="FFN width per expert of the grouped cases")
     args = ap.parse_args()
     ext = _ext.ext()
     hbm, tflops_peak, how = peaks()
@@ -163,7 +166,7 @@ def main():
             del x, w, dy, y, dx, dw, dw16
         out.update(cases=rows_out)
     elif args.case.startswith("grouped_") or args.case in ("gather", "combine"):
-        E, H, F = 64, 2048, 1024
+        E, H, F = args.experts, args.hidden, args.ffn
         R = args.rows // shrink
         tg, nt, go, tiles = uniform_plan(R, E)
         X = torch.randn(R, H, device=dev, dtype=bf)

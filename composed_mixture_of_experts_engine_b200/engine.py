@@ -224,7 +224,7 @@ class Trainer:
                 loss.backward()
                 total = total + loss.detach().float()
         if self.topology.tp_size > 1 and self.cfg.parallelism.sequence_parallel:
-            finalize_sequence_parallel_grads(self.model, self.topology)
+            finalize_sequence_parallel_grads(self.model, self.topology, optimizer=self.optimizer)
         if self.optimizer is not None:
             if isinstance(self.optimizer, FusedAdamW):
                 self.optimizer.step(lr)

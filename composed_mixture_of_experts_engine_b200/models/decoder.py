@@ -81,6 +81,10 @@ class DecoderBlock(nn.Module):
         if sp:
             for p in list(self.attn_norm.parameters()) + list(self.norm.parameters()):
                 p.sequence_parallel_grad = True  # partial per TP rank: summed over the TP group after backward
+            if self.moe.fused_sequence_shard_path(self.moe.w13):
+                # the layer will take sequence shards: its router then sees a shard only (known now, so that the
+                # optimizer can group the gate with the other partially summed parameters)
+                self.moe.router.gate_w.sequence_parallel_grad = True
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         x = x + self.attn(self.attn_norm(x))
@@ -253,15 +257,20 @@ class MoEDecoder(nn.Module):
                 "other": total - embed - router - experts - attn}
 
 
-def finalize_sequence_parallel_grads(model: nn.Module, topology: ParallelTopology) -> None:
-    """Sum over the TP group the gradients of parameters that saw only this rank's sequence shard."""
+def finalize_sequence_parallel_grads(model: nn.Module, topology: ParallelTopology, optimizer=None) -> None:
+    """Sum over the TP group the gradients of parameters that saw only this rank's sequence shard.  The fused
+    optimizer keeps those gradients at the front of one flat buffer and sums them with one collective; whatever it
+    does not cover (another optimizer, a parameter flagged after the optimizer was built) is summed one by one."""
     import torch.distributed as dist
 
     if topology.tp_size == 1 or not dist.is_initialized():
         return
     group = tp_process_group(topology)
+    done = set()
+    if optimizer is not None and hasattr(optimizer, "allreduce_sequence_parallel_grads"):
+        done = optimizer.allreduce_sequence_parallel_grads(group)
     for p in model.parameters():
-        if not getattr(p, "sequence_parallel_grad", False):
+        if not getattr(p, "sequence_parallel_grad", False) or id(p) in done:
             continue
         main = getattr(p, "main_grad", None)
         if main is not None:  # fused optimizer: kernel-accumulated and autograd parts meet in the fp32 buffer

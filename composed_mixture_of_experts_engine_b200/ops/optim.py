@@ -64,6 +64,15 @@ class _FlatGroup:
         tp = topology.tp_size if topology is not None else 1
         self.tp_size = tp
         self.replicated = [tp > 1 and not getattr(p, "tensor_parallel_shard", False) for p in params]
+        # leading run of parameters whose gradients are partial sums over the tensor-parallel group (they saw a
+        # sequence shard): build_optimizer puts them first, so one all-reduce over flat_g[:sp_prefix] sums them all
+        self.sp_prefix = 0
+        self.sp_prefix_ids = set()
+        for p, off in zip(params, offs):
+            if not getattr(p, "sequence_parallel_grad", False):
+                break
+            self.sp_prefix = off + _align(p.numel(), 8)
+            self.sp_prefix_ids.add(id(p))
         for p, off in zip(params, offs):
             n = p.numel()
             self.flat_p[off:off + n].copy_(p.data.reshape(-1))
@@ -250,6 +259,18 @@ class FusedAdamW:
                 g.flat_g.zero_()
                 self._publish_params(g)
 
+    def allreduce_sequence_parallel_grads(self, group) -> set:
+        """Sum over the tensor-parallel ``group`` the gradients of the parameters that saw only this rank's sequence
+        shard, in one collective per flat group (they sit at the front of the fp32 gradient buffer).  Returns the ids
+        of the parameters that were covered; anything flagged later is left to the caller."""
+        done: set = set()
+        for g in self.groups:
+            if g.sp_prefix > 0 and g.flat_g.dtype == torch.float32:
+                g.reassign_grads()  # fold what autograd left in p.grad into the buffer first
+                dist.all_reduce(g.flat_g[:g.sp_prefix], group=group)
+                done |= g.sp_prefix_ids
+        return done
+
     def grad_norm(self) -> float:
         """Global gradient norm of the last step (one device read)."""
         return float(self.last_grad_norm_sq.sqrt()) if self.last_grad_norm_sq is not None else 0.0
@@ -282,6 +303,8 @@ def build_optimizer(model: nn.Module, lr: float, weight_decay: float = 0.1, beta
         dp_group = ddp_process_group(topology)  # None when the group has one rank
         expert_dp_group = edp_process_group(topology)
     groups: List[_FlatGroup] = []
+    # parameters whose gradients need the tensor-parallel sum go first (stable: the rest keeps its order)
+    dense.sort(key=lambda np_: 0 if getattr(np_[1], "sequence_parallel_grad", False) else 1)
     if dense:
         # fp32 gradient buffer: the weight-gradient GEMMs of the projections and of the LM head add into it with
         # TMA reduce-add across microbatches; vector parameters' autograd gradients are added at step time
