@@ -190,10 +190,19 @@ def main():
             Xp = torch.empty(plan.cap_rows, H, device=dev, dtype=bf)
             Hp = torch.empty(plan.cap_rows, F, device=dev, dtype=bf)
             GUp = torch.empty(plan.cap_rows, 2 * F, device=dev, dtype=bf)
-            fn = lambda: kernels.gemm_pull(Xp, W13.view(-1, H), Hp, plan, epilogue=EPI_SWIGLU_FWD, N=F, K=H, groups=E,
-                                           b_group_rows=2 * F, split_n=F, aux_out=GUp, src_ptrs=[tok.data_ptr()],
-                                           slots_per_src=Tn * Kk, pull_K=Kk, ld_src=H)
+            fn = lambda st=None: kernels.gemm_pull(Xp, W13.view(-1, H), Hp, plan, epilogue=EPI_SWIGLU_FWD, N=F, K=H,
+                                                   groups=E, b_group_rows=2 * F, split_n=F, aux_out=GUp,
+                                                   src_ptrs=[tok.data_ptr()], slots_per_src=Tn * Kk, pull_K=Kk,
+                                                   ld_src=H, stamps=st)
             fl = 2 * R * 2 * F * H
+            # device timeline of one launch: first / last row pulled against first / last MMA
+            st = kernels.new_pull_stamps(torch.device("cuda", 0))
+            fn()
+            fn(st)
+            torch.cuda.synchronize()
+            p0, p1, m0, m1 = (int(v) for v in st.tolist())
+            out.update(timeline_us={"pull_first_to_last": (p1 - p0) / 1e3, "mma_first_to_last": (m1 - m0) / 1e3,
+                                    "first_mma_after_first_pull": (m0 - p0) / 1e3})
         elif args.case == "grouped_fwd2":
             fn = lambda: kernels.gemm(Hact, W2.view(-1, F), Y, mode=GEMM_GROUPED_M, N=H, K=F, b_group_rows=H, **common)
             fl = 2 * R * F * H

@@ -105,9 +105,18 @@ void push_shard(const std::vector<int64_t>& params, int64_t rank, int64_t shard_
         "push_shard");
 }
 
+
+
+void set_peer_status_word(Tensor& status) {
+  const c10::cuda::CUDAGuard guard(status.device());
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() >= 1);
+  check(cmoe::set_peer_status_word(status.data_ptr<int>()), "set_peer_status_word");
+}
+
 }  // namespace
 
 void register_ep(pybind11::module_& m) {
+  m.def("set_peer_status_word", &set_peer_status_word);
   m.def("peer_barrier", &peer_barrier);
   m.def("peer_allgather", &peer_allgather);
   m.def("gather_rows_peer", &gather_rows_peer);

@@ -25,6 +25,7 @@ enum StatusCode : int {
   ST_TIMEOUT_TMEM_EMPTY = 4,   // MMA warp waited for an accumulator that was never drained
   ST_TIMEOUT_PEER_FLAG = 5,    // waited for a flag that a peer GPU (or another CTA) never wrote
   ST_BAD_ARGUMENT = 6,
+  ST_BAD_INDEX = 7,             // a row plan or routing table named a rank / row outside the buffers: access skipped
 };
 
 constexpr unsigned long long kDefaultTimeoutNs = 4000000000ull;  // 4 s

@@ -14,6 +14,16 @@ namespace cmoe {
 
 namespace {
 
+// Where the kernels of this file record that a table pointed outside the peer buffers (set once per process with
+// set_peer_status_word; the kernels skip the access and go on, the host finds the code at its next status check).
+static __device__ int* g_peer_status = nullptr;
+
+__device__ __forceinline__ bool peer_ok(const PeerTable& t, int rank) {
+  if (static_cast<unsigned>(rank) < static_cast<unsigned>(kMaxPeers) && t.ptr[rank] != nullptr) return true;
+  if (g_peer_status != nullptr) atomicCAS(g_peer_status, 0, ST_BAD_INDEX);
+  return false;
+}
+
 __device__ __forceinline__ void ld8(const __nv_bfloat16* p, float (&f)[8]) {
   const uint4 x = *reinterpret_cast<const uint4*>(p);
   const float2 a = unpack_bf16x2(x.x), b = unpack_bf16x2(x.y), c = unpack_bf16x2(x.z), d = unpack_bf16x2(x.w);
@@ -68,6 +78,10 @@ __global__ void __launch_bounds__(256) gather_rows_peer_kernel(const PeerTable s
       continue;
     }
     const int rank = static_cast<int>(slot / slots_per_src);
+    if (!peer_ok(src, rank)) {  // a slot that names no source buffer: recorded, the row is left zero
+      for (int c = lane * 8; c < H; c += 256) *reinterpret_cast<uint4*>(o + c) = make_uint4(0u, 0u, 0u, 0u);
+      continue;
+    }
     const long long tok = (slot - rank * slots_per_src) / K;
     const __nv_bfloat16* s = reinterpret_cast<const __nv_bfloat16*>(src.ptr[rank]) + tok * ld_src;
     const float sc = slot_scale ? slot_scale[slot] : 1.f;
@@ -111,7 +125,8 @@ __global__ void __launch_bounds__(256) combine_rows_peer_kernel(const PeerTable 
     if (lane < K) {
       const int e = idx[t * K + lane];
       my_owner = expert_rank[e];
-      my_row = reinterpret_cast<const int*>(slot_row.ptr[my_owner])[slot_base + t * K + lane];
+      if (peer_ok(slot_row, my_owner) && (local_rows != nullptr || peer_ok(rows, my_owner)))
+        my_row = reinterpret_cast<const int*>(slot_row.ptr[my_owner])[slot_base + t * K + lane];
       my_w = w ? w[t * K + lane] : 1.f;
     }
     for (int cb = 0; cb < H; cb += 256) {  // the same trip count on every lane: the shuffles below need all 32
@@ -152,7 +167,9 @@ __global__ void __launch_bounds__(256) combine_bwd_w_peer_kernel(const PeerTable
   for (long long s = blockIdx.x * static_cast<long long>(warps) + (threadIdx.x >> 5); s < n_slots;
        s += static_cast<long long>(gridDim.x) * warps) {
     const int owner = expert_rank[idx[s]];
-    const int row = reinterpret_cast<const int*>(slot_row.ptr[owner])[slot_base + s];
+    const int row = (peer_ok(slot_row, owner) && (local_rows != nullptr || peer_ok(rows, owner)))
+                        ? reinterpret_cast<const int*>(slot_row.ptr[owner])[slot_base + s]
+                        : -1;
     float acc = 0.f;
     if (row >= 0) {
       const __nv_bfloat16* a = local_rows ? local_rows + s * ld_rows
@@ -253,6 +270,10 @@ inline unsigned blocks_for(long long items, int per_block, int max_blocks) {
 }
 
 }  // namespace
+
+cudaError_t set_peer_status_word(int* status) {
+  return cudaMemcpyToSymbol(g_peer_status, &status, sizeof(status));
+}
 
 cudaError_t launch_peer_barrier(const PeerTable& flags, int rank, int world, uint32_t epoch, int* status,
                                 unsigned long long timeout_ns, cudaStream_t stream) {

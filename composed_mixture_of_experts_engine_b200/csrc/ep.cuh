@@ -13,6 +13,10 @@ struct PeerTable {
   void* ptr[kMaxPeers];
 };
 
+// Device int where the row kernels below record ST_BAD_INDEX when a row plan or routing table names a rank that has
+// no buffer in the peer table (the access is skipped).  Set once per process; nullptr switches the record off.
+cudaError_t set_peer_status_word(int* status);
+
 // Group barrier over 32-bit flag words in symmetric memory.  Rank `rank` writes `epoch` into word [rank] of
 // every peer's flag array, then waits (bounded by timeout_ns) until all `world` words of its own array are
 // >= epoch.  A wait that runs out records ST_TIMEOUT_PEER_FLAG in *status and the kernel returns normally.

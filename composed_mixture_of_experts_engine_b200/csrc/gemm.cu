@@ -450,9 +450,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               sc[q] = 1.f;
               if (slot[q] >= 0) {
                 const int src_rank = static_cast<int>(slot[q] / p.pull_slots_per_src);
-                const long long tok = (slot[q] - src_rank * p.pull_slots_per_src) / p.pull_K;
-                src[q] = reinterpret_cast<const __nv_bfloat16*>(p.pull_src.ptr[src_rank]) + tok * p.pull_ld_src;
-                if (p.pull_slot_scale) sc[q] = p.pull_slot_scale[slot[q]];
+                if (static_cast<unsigned>(src_rank) >= static_cast<unsigned>(kMaxPeers) ||
+                    p.pull_src.ptr[src_rank] == nullptr) {
+                  // the plan names a rank without a buffer: record it and leave the row zero instead of faulting
+                  if (p.status != nullptr) atomicCAS(p.status, 0, ST_BAD_INDEX);
+                } else {
+                  const long long tok = (slot[q] - src_rank * p.pull_slots_per_src) / p.pull_K;
+                  src[q] = reinterpret_cast<const __nv_bfloat16*>(p.pull_src.ptr[src_rank]) + tok * p.pull_ld_src;
+                  if (p.pull_slot_scale) sc[q] = p.pull_slot_scale[slot[q]];
+                }
               }
             }
             for (int c0 = lane * 8; c0 < p.pull_cols; c0 += 2048) {
@@ -563,7 +569,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               const int slot = p.scatter_row_slot[rr];
               if (slot >= 0) {
                 const int dr = static_cast<int>(slot / p.scatter_slots_per_rank);
-                dest[i] = make_int2(dr, static_cast<int>(slot - dr * p.scatter_slots_per_rank));
+                if (static_cast<unsigned>(dr) < static_cast<unsigned>(kMaxPeers) && p.scatter_out.ptr[dr] != nullptr)
+                  dest[i] = make_int2(dr, static_cast<int>(slot - dr * p.scatter_slots_per_rank));
+                else if (p.status != nullptr)
+                  atomicCAS(p.status, 0, ST_BAD_INDEX);  // no such destination: recorded, the row is not stored
               }
             }
           }

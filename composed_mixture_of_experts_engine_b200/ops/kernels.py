@@ -24,6 +24,7 @@ STATUS_NAMES = {
     4: "timeout: accumulator never drained",
     5: "timeout: peer flag never written",
     6: "bad argument",
+    7: "a row plan or routing table named a rank or row outside the buffers (the access was skipped)",
 }
 
 
@@ -41,6 +42,7 @@ def status_word(device: torch.device) -> torch.Tensor:
     if t is None:
         t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
         _status[idx] = t
+        _ext.ext().set_peer_status_word(t)  # the peer row kernels record bad indices in the same word
     return t
 
 

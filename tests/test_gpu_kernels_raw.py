@@ -520,6 +520,30 @@ def test_gemm_with_fused_scatter_matches_gemm_then_scatter(ext, status):
     assert torch.equal(torch.cat(outs), want)
 
 
+def test_row_kernels_skip_and_report_a_slot_that_names_no_buffer(ext):
+    """A corrupted row plan (a slot that points at a rank the peer table has no buffer for) must not turn into a
+    stray access: the row kernels leave such rows zero, record the bad index in the status word and carry on."""
+    from composed_mixture_of_experts_engine_b200.ops import kernels
+
+    dev = torch.device("cuda", 0)
+    kernels.check_status(dev)  # start from a clean word
+    T, H = 256, 128
+    src = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    slots = torch.arange(128, device="cuda", dtype=torch.int32)
+    slots[5] = 3 * T + 7      # rank 3 of a one-entry table
+    slots[9] = 40 * T + 1     # beyond the table altogether
+    out = torch.full((128, H), 5.0, device="cuda", dtype=torch.bfloat16)
+    tiles = torch.tensor([1], device="cuda", dtype=torch.int32)
+    ext.gather_rows_peer([src.data_ptr()], T, 1, slots, None, out, tiles, H)
+    torch.cuda.synchronize()
+    good = [i for i in range(128) if i not in (5, 9)]
+    assert torch.equal(out[good], src[good])
+    assert float(out[5].abs().max()) == 0.0 and float(out[9].abs().max()) == 0.0
+    with pytest.raises(kernels.KernelTimeoutError, match="outside the buffers"):
+        kernels.check_status(dev)
+    kernels.check_status(dev)  # the word was cleared by the failed check
+
+
 def test_bounded_wait_reports_a_status_instead_of_hanging(ext):
     """A barrier whose second participant never arrives: the wait runs out after a few milliseconds, the kernel
     returns normally with status 5 (peer flag never written) and the context stays usable."""
