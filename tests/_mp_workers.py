@@ -659,7 +659,18 @@ def gpu_trainer_hybrid(rank, world, dp, ep, tp, pp, steps):
     ids, tgt = tr.synthetic_batch(torch.Generator().manual_seed(tr.topology.dp_rank))
     losses = [float(tr.train_step(ids, tgt)) for _ in range(steps)]
     check_status(tr.device)
-    return {"losses": losses, "last": tr.topology.is_last_pp_stage(), "n_blocks": len(tr.model.blocks)}
+    # parameters that every tensor-parallel rank holds whole must stay bit-identical on all of them: their gradients
+    # are partial sums per sequence shard, summed over the group before the update
+    blk = tr.model.blocks[0]
+    whole = {"norm": blk.norm.weight, "attn_norm": blk.attn_norm.weight, "gate": blk.moe.router.gate_w}
+    if tr.model.embed is not None:
+        whole["embed"] = tr.model.embed.weight
+    if tr.model.lm_head is not None:
+        whole["lm_head"] = tr.model.lm_head.weight
+    return {"losses": losses, "last": tr.topology.is_last_pp_stage(), "n_blocks": len(tr.model.blocks),
+            "tp_rank": tr.topology.tp_rank, "pp_rank": tr.topology.pp_rank,
+            "whole": {k: v.detach().double().flatten()[:256].tolist() for k, v in whole.items()},
+            "fused_sp_moe": bool(getattr(blk.moe.router.gate_w, "sequence_parallel_grad", False))}
 
 
 def gpu_tp_sp(rank, world, transport="auto"):

@@ -90,6 +90,20 @@ def test_moe_layer_takes_sequence_shards_over_the_ep_x_tp_block():
             assert v < tol, (r, k, v, out)
 
 
+def test_trainer_tensor_sequence_parallel_on_gpus():
+    """tp = 2 with sequence parallelism (no pipeline): the MoE blocks take sequence shards over peer memory, the
+    attention projections gather / reduce-scatter inside their GEMMs.  The loss falls, and every parameter that both
+    ranks hold whole (norms, router gate, embedding, LM head) is bit-identical on both after training, which it can
+    only be if the partial gradients of the two sequence shards were summed before each update."""
+    res = _spawn_gpu("gpu_trainer_hybrid", 2, 1, 1, 2, 1, 8)
+    a, b = res[0], res[1]
+    assert a["fused_sp_moe"] and b["fused_sp_moe"]
+    assert all(math.isfinite(l) for l in a["losses"]) and a["losses"][-1] < a["losses"][0]
+    assert a["losses"] == b["losses"]
+    for name in a["whole"]:
+        assert a["whole"][name] == b["whole"][name], name
+
+
 def test_trainer_pipeline_parallel_on_gpus():
     """Two pipeline stages over NCCL (1F1B, 4 microbatches), bf16 kernels and the fused optimizer on every stage; with
     four GPUs also tensor + sequence parallelism inside each stage."""
