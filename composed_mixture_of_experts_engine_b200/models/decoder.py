@@ -245,7 +245,15 @@ class MoEDecoder(nn.Module):
         dev = next(self.parameters()).device
         zero = torch.zeros((), device=dev, dtype=torch.float32)
         n = max(self.num_layers_total, 1)
-        return (torch.stack(aux).sum() / n if aux else zero), (torch.stack(z).sum() / n if z else zero)
+        a = torch.stack(aux).sum() / n if aux else zero
+        zl = torch.stack(z).sum() / n if z else zero
+        if any(l.aux_scale != 1.0 for l in self.moe_layers()):
+            # the routers saw sequence shards: each rank holds its shard's share of the two terms.  Sum them over the
+            # tensor-parallel group so that every rank reports the same value; the backward of this sum is the
+            # identity, so each rank still back-propagates its own share only
+            both = C.all_reduce(torch.stack([a, zl]), tp_process_group(self.topology))
+            a, zl = both[0], both[1]
+        return a, zl
 
     def count_parameters(self) -> Dict[str, int]:
         total = sum(p.numel() for p in self.parameters())
