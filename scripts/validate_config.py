@@ -23,20 +23,44 @@ def main(argv=None) -> int:
         print("usage: validate_config.py <file-or-dir> ...", file=sys.stderr)
         return 2
     colour = sys.stdout.isatty()
+
+    def tag(ok: bool) -> str:
+        word = "OK" if ok else "FAIL"
+        return f"{GREEN if ok else RED}{word}{RESET}" if colour else word
+
     files = []
     for a in argv:
         p = Path(a)
-        files += sorted(p.glob("*.yaml")) if p.is_dir() else [p]
+        if p.is_dir():
+            found = sorted(list(p.glob("*.yaml")) + list(p.glob("*.yml")))
+            if not found:
+                print(f"[WARN] no *.yaml / *.yml files in {p}")
+            files += found
+        elif p.is_file():
+            files.append(p)
+        else:
+            print(f"[{tag(False)}] {p}: no such file or directory")
+            return 1
+    if not files:
+        print("nothing to validate")
+        return 1
     failed = 0
     for f in files:
         try:
             cfg = MoEConfig.from_yaml(f)
-            tag = f"{GREEN}OK{RESET}" if colour else "OK"
-            print(f"[{tag}] {f}  (world_size={cfg.parallelism.world_size}, arch={cfg.model.arch})")
-        except (ConfigValidationError, FileNotFoundError) as exc:
+            m, par = cfg.model, cfg.parallelism
+            print(f"[{tag(True)}] {f}  H={m.hidden_dim} E={m.num_experts} K={m.top_k} world_size={par.world_size} "
+                  f"dtype={m.dtype} arch={m.arch}")
+        except ConfigValidationError as exc:
             failed += 1
-            tag = f"{RED}FAIL{RESET}" if colour else "FAIL"
-            print(f"[{tag}] {f}\n{exc}")
+            print(f"[{tag(False)}] {f}")
+            for line in str(exc).splitlines():
+                print(f"       {line}")
+        except Exception as exc:  # unreadable file, YAML syntax error, ...: a failure of that file, not of the run
+            failed += 1
+            print(f"[{tag(False)}] {f}: {type(exc).__name__}: {exc}")
+    ok = len(files) - failed
+    print(f"{ok} of {len(files)} config(s) valid" + (f", {failed} failed" if failed else ""))
     return 1 if failed else 0
 
 

@@ -227,7 +227,17 @@ def train_main_tp(rank, world, tmp_dir):
     import torch.distributed as dist
 
     if dist.is_initialized():
+        # a fresh rendezvous port agreed on over the old group: re-using the old port races with rank 0 closing
+        # the store that the other ranks may still be connected to
+        box = [None]
+        if rank == 0:
+            from tests.conftest import find_free_port
+
+            box[0] = find_free_port()
+        dist.broadcast_object_list(box, src=0)
+        dist.barrier()
         dist.destroy_process_group()
+        os.environ["MASTER_PORT"] = str(box[0])
     rc = train_main_module.main(["--config", path, "--cpu", "--no-wandb"])
     rows = [json.loads(l) for l in open(f"{tmp_dir}/logs/step.rank{rank}.jsonl") if l.strip().startswith("{")]
     return {"rc": rc, "losses": [r["loss"] for r in rows if "loss" in r]}
