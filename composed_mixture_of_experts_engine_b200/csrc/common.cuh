@@ -187,6 +187,15 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* t
       : "memory");
 }
 
+// Asks the TMA unit to bring the box at (x, y) into L2 without a destination in shared memory: a later load of the
+// same box then pays L2 latency instead of DRAM latency.  No completion is tracked; same alignment rule for x.
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* tmap, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(
+                   reinterpret_cast<uint64_t>(tmap)),
+               "r"(x), "r"(y)
+               : "memory");
+}
+
 // Tiled TMA stores (shared -> global) of a [1, rows, cols] box of a rank-3 tensor map, tracked by bulk async-groups.
 // x = innermost coordinate (elements): x * sizeof(element) must be a multiple of 16 bytes; no coordinate may be negative.
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* tmap, const void* smem_src, int x, int y, int z) {

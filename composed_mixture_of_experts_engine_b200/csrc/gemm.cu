@@ -96,6 +96,7 @@ struct KParams {
   long long scatter_ld;
   int out_mode;    // OutMode (EPI_STORE only)
   int fwd_staged;  // SwiGLU forward: h (tmD) and gate|up (tmE) leave through the staging area and TMA stores
+  int bwd_staged;  // SwiGLU backward: dGate|dUp (tmE) leave through the piece's own staging buffer and TMA stores
 };
 
 struct Tile {
@@ -230,13 +231,10 @@ __device__ __forceinline__ void prefetch_f32_chunk(const float* row_ptr, int col
   }
 }
 
-// SwiGLU backward for 32 columns of one row: dH (fp32 bits in r) with the saved gate / up values (bf16 in cg / cu)
-// -> dGate at D[row, col..] and dUp at D[row, N + col..].  Eight columns at a time, straight from the packed
-// inputs to the packed outputs; columns past N hold garbage and are not stored.
-__device__ __forceinline__ void swiglu_bwd_chunk(const uint32_t (&r)[32], const uint4 (&cg)[4], const uint4 (&cu)[4],
-                                                 int col, int N, void* Dg, long long ldd, long long row) {
-  __nv_bfloat16* dgp = reinterpret_cast<__nv_bfloat16*>(Dg) + row * ldd + col;
-  __nv_bfloat16* dup = dgp + N;
+// SwiGLU backward for 32 columns of one row: dH (fp32 bits in r) with the saved gate / up values (bf16, packed in
+// cg / cu) -> dGate / dUp (bf16, packed) written over cg / cu.  Eight columns at a time, straight from the packed
+// inputs to the packed outputs.
+__device__ __forceinline__ void swiglu_bwd_math(const uint32_t (&r)[32], uint4 (&cg)[4], uint4 (&cu)[4]) {
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const uint32_t gw[4] = {cg[j].x, cg[j].y, cg[j].z, cg[j].w};
@@ -254,9 +252,23 @@ __device__ __forceinline__ void swiglu_bwd_chunk(const uint32_t (&r)[32], const 
       og[q] = pack_bf16x2(dg0, dg1);
       ou[q] = pack_bf16x2(dh0 * (g.x * s0), dh1 * (g.y * s1));
     }
+    cg[j] = make_uint4(og[0], og[1], og[2], og[3]);
+    cu[j] = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+  }
+}
+
+// ... and its results stored from registers: dGate at D[row, col..], dUp at D[row, N + col..]; columns past N hold
+// garbage and are not stored.
+__device__ __forceinline__ void swiglu_bwd_chunk(const uint32_t (&r)[32], uint4 (&cg)[4], uint4 (&cu)[4], int col,
+                                                 int N, void* Dg, long long ldd, long long row) {
+  swiglu_bwd_math(r, cg, cu);
+  __nv_bfloat16* dgp = reinterpret_cast<__nv_bfloat16*>(Dg) + row * ldd + col;
+  __nv_bfloat16* dup = dgp + N;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
     if (col + j * 8 < N) {  // N is a multiple of 8
-      *reinterpret_cast<uint4*>(dgp + j * 8) = make_uint4(og[0], og[1], og[2], og[3]);
-      *reinterpret_cast<uint4*>(dup + j * 8) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+      *reinterpret_cast<uint4*>(dgp + j * 8) = cg[j];
+      *reinterpret_cast<uint4*>(dup + j * 8) = cu[j];
     }
   }
 }
@@ -540,13 +552,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       // before the wait for its accumulator
       auto gu_issue = [&](uint32_t ctr, int col) {
         const uint32_t b = ctr & 1u;
-        if (!mbar_wait(&gempty_bar[b], ((ctr >> 1) & 1u) ^ 1u, wc, ST_TIMEOUT_SMEM_EMPTY)) return;
+        // direct stores: the buffer is free once all 128 threads have read it.  Staged stores: the caller has
+        // waited for the TMA store that last read it.
+        if (!p.bwd_staged && !mbar_wait(&gempty_bar[b], ((ctr >> 1) & 1u) ^ 1u, wc, ST_TIMEOUT_SMEM_EMPTY)) return;
         uint8_t* dst = stg + b * STAGING_BUF_BYTES;
         mbar_arrive_expect_tx(&gfull_bar[b], STAGING_BUF_BYTES);
         tma_load_2d(dst, &tmD, &gfull_bar[b], col, ti.m0);
         tma_load_2d(dst + STAGING_BUF_BYTES / 2, &tmD, &gfull_bar[b], p.N + col, ti.m0);
       };
-      if (EPI == EPI_SWIGLU_BWD && threadIdx.x == EPI_FIRST_THREAD) gu_issue(stage_ctr, ti.n0);
+      if (EPI == EPI_SWIGLU_BWD && threadIdx.x == EPI_FIRST_THREAD) {
+        // staged: this piece's buffer was last read by the store issued two pieces ago
+        if (p.bwd_staged) bulk_wait_group_read<1>();
+        gu_issue(stage_ctr, ti.n0);
+      }
       const bool ok = mbar_wait(&tfull_bar[acc], acc_phase, wc, ST_TIMEOUT_TMEM_FULL);
       tc_fence_after();
       const uint32_t t_acc = tmem_base + acc * BN + lane_base;
@@ -809,9 +827,74 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
         }
       }
-      if (EPI == EPI_SWIGLU_BWD) {
-        // acc = dH; D = [dGate | dUp] with row stride ldd (>= 2N).  Runs whether or not the accumulator wait succeeded, so that every requested piece is also consumed
+      if (EPI == EPI_SWIGLU_BWD && p.bwd_staged) {
+        // acc = dH; [dGate | dUp] = f(dH, gate, up).  Every thread reads its own row of the gate / up piece from the
+        // staging buffer, writes its results over it, and the piece leaves through two TMA stores (each thread's
+        // direct 16-byte stores at a row stride were the largest single cost of this epilogue).  One named barrier
+        // per piece, carrying the OR of "a wait failed / abort seen" so that all 128 threads leave together.
         const int gsw = (row_in_tile >> 1) & 3;  // 64-byte swizzle: 16-byte chunk j of row r sits at j ^ ((r / 2) % 4)
+        bool any_bad = false;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col = ti.n0 + c * 32;
+          if (col >= p.N) break;
+          const uint32_t b = stage_ctr & 1u;
+          if (threadIdx.x == EPI_FIRST_THREAD && c + 1 < BN / 32 && col + 32 < p.N) {
+            bulk_wait_group_read<0>();  // the store of the previous piece has read the other buffer
+            gu_issue(stage_ctr + 1, col + 32);
+          }
+          const bool got = mbar_wait(&gfull_bar[b], (stage_ctr >> 1) & 1u, wc, ST_TIMEOUT_SMEM_FULL);
+          uint32_t r[32];
+          if (ok) {
+            tmem_ld_32x32b_x32(t_acc + c * 32, r);
+            tmem_ld_wait();
+          }
+          uint4 cg[4], cu[4];
+          uint8_t* grow = stg + b * STAGING_BUF_BYTES + row_in_tile * 64;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            cg[j] = *reinterpret_cast<const uint4*>(grow + ((j ^ gsw) << 4));
+            cu[j] = *reinterpret_cast<const uint4*>(grow + STAGING_BUF_BYTES / 2 + ((j ^ gsw) << 4));
+          }
+          if (ok && got) {
+            swiglu_bwd_math(r, cg, cu);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              *reinterpret_cast<uint4*>(grow + ((j ^ gsw) << 4)) = cg[j];
+              *reinterpret_cast<uint4*>(grow + STAGING_BUF_BYTES / 2 + ((j ^ gsw) << 4)) = cu[j];
+            }
+          }
+          fence_proxy_async_smem();
+          {
+            const int bad = (!ok || !got || *abort_flag) ? 1 : 0;
+            int any;
+            asm volatile(
+                "{\n\t.reg .pred q, r;\n\tsetp.ne.s32 q, %1, 0;\n\tbar.red.or.pred r, 1, 128, q;\n\t"
+                "selp.s32 %0, 1, 0, r;\n\t}"
+                : "=r"(any)
+                : "r"(bad)
+                : "memory");
+            any_bad = any != 0;
+          }
+          if (any_bad) break;  // uniform over the 128 epilogue threads
+          if (threadIdx.x == EPI_FIRST_THREAD) {
+            tma_store_3d(&tmE, stg + b * STAGING_BUF_BYTES, col, 0, ti.m0);                          // dGate
+            tma_store_3d(&tmE, stg + b * STAGING_BUF_BYTES + STAGING_BUF_BYTES / 2, col, 1, ti.m0);  // dUp
+            bulk_commit_group();
+          }
+          ++stage_ctr;
+        }
+        tc_fence_before();
+        mbar_arrive(&tempty_bar[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+        if (any_bad) break;
+        continue;
+      }
+      if (EPI == EPI_SWIGLU_BWD) {
+        // direct stores.  acc = dH; D = [dGate | dUp] with row stride ldd (>= 2N).  Runs whether or not the
+        // accumulator wait succeeded, so that every requested piece is also consumed
+        const int gsw = (row_in_tile >> 1) & 3;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           const int col = ti.n0 + c * 32;
@@ -844,7 +927,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
     // shared memory and the kernel's results must outlive the TMA stores still in flight
     if (threadIdx.x == EPI_FIRST_THREAD &&
-        (p.out_mode == OUT_TMA_STORE || p.out_mode == OUT_TMA_REDUCE || (EPI == EPI_SWIGLU_FWD && p.fwd_staged)))
+        (p.out_mode == OUT_TMA_STORE || p.out_mode == OUT_TMA_REDUCE || (EPI == EPI_SWIGLU_FWD && p.fwd_staged) ||
+         (EPI == EPI_SWIGLU_BWD && p.bwd_staged)))
       bulk_wait_group<0>();
   }
 
@@ -1148,6 +1232,7 @@ cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   }
   CUtensorMap tmE = tmA;  // placeholder unless the SwiGLU forward stages its gate|up output
   kp.fwd_staged = 0;
+  kp.bwd_staged = 0;
   if (a.epilogue == EPI_SWIGLU_FWD && !direct_epilogue_forced() && a.mode != GEMM_GROUPED_K) {
     // h [rows, N] and the optional gate|up copy [rows, 2N] (as [2 halves, rows, N]) leave through TMA stores
     const long long d_rows = a.mode == GEMM_GROUPED_M ? a.a_rows : a.M;
@@ -1166,6 +1251,11 @@ cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream) {
     const long long aux_rows = a.mode == GEMM_GROUPED_M ? a.a_rows : a.M;
     e = make_tmap(&tmD, a.aux_in, aux_rows, 2LL * a.N, a.ld_aux_in, BM, 32);
     if (e != cudaSuccess) return e;
+    // [dGate | dUp] leaves through TMA stores of the same 128 x 32 pieces (as [rows, 2 halves, N], clipped at N)
+    if (!direct_epilogue_forced() && !a.d_fp32 && !a.accumulate && a.mode != GEMM_GROUPED_K &&
+        (reinterpret_cast<uintptr_t>(a.D) & 15u) == 0 && (a.ldd * 2) % 16 == 0 && a.ldd >= 2LL * a.N &&
+        make_tmap_halves(&tmE, a.D, aux_rows, a.N, a.ldd) == cudaSuccess)
+      kp.bwd_staged = 1;
   }
   kp.ready_flags = a.ready_flags;
   kp.ready_stride = a.ready_stride;
