@@ -88,6 +88,17 @@ def main():
                            args.iters)
         nbytes = n * (8 + 8 + 8 + 8 + 2)
         out.update(ms=ms, gbs=nbytes / ms / 1e6, frac_of_hbm=nbytes / ms / 1e6 / hbm, elements=n)
+    elif args.case == "hbm":
+        # what the memory system gives a pure write, a pure read and a copy of 1 GiB (ATen kernels: reference rates
+        # for the row kernels, whose traffic is mostly one-directional)
+        n = 1 << 29
+        x = torch.empty(n, device=dev, dtype=bf)
+        y = torch.empty(n, device=dev, dtype=bf)
+        w_ms = time_launches(lambda: x.fill_(1.0), args.iters)
+        r_ms = time_launches(lambda: x.sum(dtype=torch.float32), args.iters)
+        c_ms = time_launches(lambda: y.copy_(x), args.iters)
+        gb = n * 2 / 1e6
+        out.update(write_gbs=gb / w_ms, read_gbs=gb / r_ms, copy_gbs=2 * gb / c_ms)
     elif args.case == "rmsnorm":
         rows, H = 32768 // shrink, 2048
         x = torch.randn(rows, H, device=dev, dtype=bf)

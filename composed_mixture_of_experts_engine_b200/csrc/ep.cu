@@ -6,6 +6,7 @@
 // pkg/distributed/expert_parallel.py:104-218) and C10 (FSDP2 reduce-scatter / all-gather,
 // pkg/distributed/data_parallel.py:91-97).  Every remote access is a plain ld/st on a peer-mapped address;
 // there is no TMA on peer memory and no wait without a bound anywhere in this file.
+#include <cstdlib>
 #include "ep.cuh"
 
 #include "common.cuh"
@@ -150,6 +151,64 @@ __global__ void __launch_bounds__(256) combine_rows_peer_kernel(const PeerTable 
         for (int j = 0; j < 8; ++j) acc[j] += wk * f[j];
       }
       if (act) st8(y + t * ld_y + c, acc);
+    }
+  }
+}
+
+// Same sum for a compile-time K: the K source rows of a token are resolved once (lane k looks pair k up, the warp
+// shares the results by shuffle) and the loads of all K rows of a column block are issued before the first use, so
+// a lane keeps K x 16 bytes in flight instead of 16.  The order of the additions is that of the kernel above.
+template <int KK>
+__global__ void __launch_bounds__(256) combine_rows_peer_k_kernel(const PeerTable rows, const PeerTable slot_row,
+                                                                  const int* __restrict__ idx,
+                                                                  const int* __restrict__ expert_rank,
+                                                                  const float* __restrict__ w,
+                                                                  __nv_bfloat16* __restrict__ y, long long n_tokens,
+                                                                  int H, long long slot_base, long long ld_rows,
+                                                                  long long ld_y,
+                                                                  const __nv_bfloat16* __restrict__ local_rows) {
+  const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+  for (long long t = blockIdx.x * static_cast<long long>(warps) + (threadIdx.x >> 5); t < n_tokens;
+       t += static_cast<long long>(gridDim.x) * warps) {
+    const __nv_bfloat16* my_src = nullptr;
+    float my_w = 0.f;
+    if (lane < KK) {
+      const int e = idx[t * KK + lane];
+      const int owner = expert_rank[e];
+      if (peer_ok(slot_row, owner) && (local_rows != nullptr || peer_ok(rows, owner))) {
+        const int row = reinterpret_cast<const int*>(slot_row.ptr[owner])[slot_base + t * KK + lane];
+        if (row >= 0)
+          my_src = local_rows ? local_rows + (t * KK + lane) * ld_rows
+                              : reinterpret_cast<const __nv_bfloat16*>(rows.ptr[owner]) +
+                                    static_cast<long long>(row) * ld_rows;
+      }
+      my_w = w ? w[t * KK + lane] : 1.f;
+    }
+    const __nv_bfloat16* src[KK];
+    float wk[KK];
+#pragma unroll
+    for (int k = 0; k < KK; ++k) {
+      src[k] = reinterpret_cast<const __nv_bfloat16*>(
+          __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_src), k));
+      wk[k] = __shfl_sync(0xffffffffu, my_w, k);
+    }
+    for (int c = lane * 8; c < H; c += 256) {
+      uint4 v[KK];
+#pragma unroll
+      for (int k = 0; k < KK; ++k)
+        v[k] = src[k] != nullptr ? *reinterpret_cast<const uint4*>(src[k] + c) : make_uint4(0u, 0u, 0u, 0u);
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+      for (int k = 0; k < KK; ++k) {
+        if (src[k] == nullptr) continue;  // a dropped slot adds nothing
+        const float2 a = unpack_bf16x2(v[k].x), b = unpack_bf16x2(v[k].y), cc = unpack_bf16x2(v[k].z),
+                     d = unpack_bf16x2(v[k].w);
+        acc[0] += wk[k] * a.x; acc[1] += wk[k] * a.y; acc[2] += wk[k] * b.x; acc[3] += wk[k] * b.y;
+        acc[4] += wk[k] * cc.x; acc[5] += wk[k] * cc.y; acc[6] += wk[k] * d.x; acc[7] += wk[k] * d.y;
+      }
+      st8(y + t * ld_y + c, acc);
     }
   }
 }
@@ -306,6 +365,30 @@ cudaError_t launch_combine_rows_peer(const PeerTable& rows, const PeerTable& slo
                                      long long slot_base, long long ld_rows, long long ld_y, const void* local_rows,
                                      cudaStream_t stream) {
   if (H % 8 != 0 || n_tokens <= 0 || K <= 0 || K > 32) return cudaErrorInvalidValue;
+  static const bool generic_only = [] {
+    const char* v = std::getenv("CMOE_COMBINE_GENERIC");  // A/B switch: the kernel with a run-time K for every K
+    return v != nullptr && v[0] != '\0' && v[0] != '0';
+  }();
+  if (!generic_only) {
+    const unsigned grid = blocks_for(n_tokens, 8, 148 * 8);
+    auto yb = reinterpret_cast<__nv_bfloat16*>(y);
+    auto lr = reinterpret_cast<const __nv_bfloat16*>(local_rows);
+#define CMOE_COMBINE_PEER_CASE(KK)                                                                                  \
+  case KK:                                                                                                          \
+    combine_rows_peer_k_kernel<KK><<<grid, 256, 0, stream>>>(rows, slot_row, idx, expert_rank, w, yb, n_tokens, H,  \
+                                                             slot_base, ld_rows, ld_y, lr);                         \
+    return cudaGetLastError();
+    switch (K) {
+      CMOE_COMBINE_PEER_CASE(2)
+      CMOE_COMBINE_PEER_CASE(4)
+      CMOE_COMBINE_PEER_CASE(6)
+      CMOE_COMBINE_PEER_CASE(8)
+      CMOE_COMBINE_PEER_CASE(12)
+      CMOE_COMBINE_PEER_CASE(16)
+      default: break;
+    }
+#undef CMOE_COMBINE_PEER_CASE
+  }
   combine_rows_peer_kernel<<<blocks_for(n_tokens, 8, 148 * 8), 256, 0, stream>>>(
       rows, slot_row, idx, expert_rank, w, reinterpret_cast<__nv_bfloat16*>(y), n_tokens, K, H, slot_base, ld_rows,
       ld_y, reinterpret_cast<const __nv_bfloat16*>(local_rows));

@@ -8,6 +8,8 @@
 // capacity dropping (moe_layer.py:64-155).  RoPE has no counterpart there.
 #include "ops.cuh"
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace cmoe {
@@ -685,6 +687,52 @@ __global__ void combine_rows_kernel(const __nv_bfloat16* __restrict__ rows, cons
   }
 }
 
+// Same sum for a compile-time K: the K (row, weight) pairs of a token are looked up once (lane k loads pair k, the
+// warp shares them by shuffle) and the loads of all K rows of a column block are issued before the first use, so a
+// lane keeps K x 16 bytes in flight instead of 16.  The order of the additions is that of the kernel above.
+template <int KK>
+__global__ void combine_rows_k_kernel(const __nv_bfloat16* __restrict__ rows, const int* __restrict__ slot_row,
+                                      const float* __restrict__ w, __nv_bfloat16* __restrict__ y, long long n_tokens,
+                                      int H, long long ld_rows, long long ld_y) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (long long t = blockIdx.x * static_cast<long long>(warps_per_block) + (threadIdx.x >> 5); t < n_tokens;
+       t += static_cast<long long>(gridDim.x) * warps_per_block) {
+    int my_r = -1;
+    float my_w = 0.f;
+    if (lane < KK) {
+      my_r = slot_row[t * KK + lane];
+      my_w = w ? w[t * KK + lane] : 1.f;
+    }
+    const __nv_bfloat16* src[KK];
+    float wk[KK];
+#pragma unroll
+    for (int k = 0; k < KK; ++k) {
+      const int r = __shfl_sync(0xffffffffu, my_r, k);
+      wk[k] = __shfl_sync(0xffffffffu, my_w, k);
+      src[k] = r >= 0 ? rows + static_cast<long long>(r) * ld_rows : nullptr;
+    }
+    for (int c = lane * 8; c < H; c += 256) {
+      uint4 v[KK];
+#pragma unroll
+      for (int k = 0; k < KK; ++k)
+        v[k] = src[k] != nullptr ? *reinterpret_cast<const uint4*>(src[k] + c) : make_uint4(0u, 0u, 0u, 0u);
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+      for (int k = 0; k < KK; ++k) {
+        if (src[k] == nullptr) continue;  // a dropped slot adds nothing (and no signed zero)
+        const float2 a = unpack_bf16x2(v[k].x), b = unpack_bf16x2(v[k].y), cc = unpack_bf16x2(v[k].z),
+                     d = unpack_bf16x2(v[k].w);
+        acc[0] += wk[k] * a.x; acc[1] += wk[k] * a.y; acc[2] += wk[k] * b.x; acc[3] += wk[k] * b.y;
+        acc[4] += wk[k] * cc.x; acc[5] += wk[k] * cc.y; acc[6] += wk[k] * d.x; acc[7] += wk[k] * d.y;
+      }
+      store8(y + t * ld_y + c, acc);
+    }
+  }
+}
+
 __global__ void combine_bwd_w_kernel(const __nv_bfloat16* __restrict__ rows, const int* __restrict__ slot_row,
                                      const __nv_bfloat16* __restrict__ dy, float* __restrict__ dw, long long n_tokens,
                                      int K, int H, long long ld_rows, long long ld_dy) {
@@ -855,6 +903,22 @@ cudaError_t launch_gather_rows(const void* src, const int* row_slot, int slot_di
 cudaError_t launch_combine_rows(const void* rows, const int* slot_row, const float* w, void* y, long long n_tokens,
                                 int K, int H, long long ld_rows, long long ld_y, cudaStream_t stream) {
   if (H % 8 != 0 || n_tokens <= 0) return cudaErrorInvalidValue;
+  static const bool generic_only = [] {
+    const char* v = std::getenv("CMOE_COMBINE_GENERIC");  // A/B switch: the kernel with a run-time K for every K
+    return v != nullptr && v[0] != '\0' && v[0] != '0';
+  }();
+  if (!generic_only && (K == 8 || K == 6 || K == 4 || K == 2)) {
+    const unsigned grid = grid_for(n_tokens, 8, 148 * 8);
+    auto rb = reinterpret_cast<const __nv_bfloat16*>(rows);
+    auto yb = reinterpret_cast<__nv_bfloat16*>(y);
+    switch (K) {
+      case 8: combine_rows_k_kernel<8><<<grid, 256, 0, stream>>>(rb, slot_row, w, yb, n_tokens, H, ld_rows, ld_y); break;
+      case 6: combine_rows_k_kernel<6><<<grid, 256, 0, stream>>>(rb, slot_row, w, yb, n_tokens, H, ld_rows, ld_y); break;
+      case 4: combine_rows_k_kernel<4><<<grid, 256, 0, stream>>>(rb, slot_row, w, yb, n_tokens, H, ld_rows, ld_y); break;
+      default: combine_rows_k_kernel<2><<<grid, 256, 0, stream>>>(rb, slot_row, w, yb, n_tokens, H, ld_rows, ld_y); break;
+    }
+    return cudaGetLastError();
+  }
   combine_rows_kernel<<<grid_for(n_tokens, 8, 148 * 8), 256, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(rows), slot_row, w, reinterpret_cast<__nv_bfloat16*>(y), n_tokens, K, H,
       ld_rows, ld_y);
