@@ -88,6 +88,21 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_fwd_kernel(const __nv_bflo
   }
 }
 
+// rows of x / dy that a CTA of the backward kernel keeps in flight (shared-memory ring)
+__host__ __device__ constexpr int rn_bwd_stages(int vec) { return vec <= 2 ? 4 : 2; }
+__host__ __device__ constexpr int rn_bwd_smem(int vec) { return rn_bwd_stages(vec) * 2 * vec * RN_THREADS * 16; }
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
+               "l"(gsrc)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 template <int VEC>
 __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
                                                                  const __nv_bfloat16* __restrict__ x,
@@ -97,6 +112,8 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
                                                                  float* __restrict__ dw_partial, long long rows,
                                                                  int H) {
   __shared__ float red[RN_THREADS / 32];
+  extern __shared__ uint4 rn_ring[];  // [stages][x | dy][VEC][RN_THREADS]: every thread's own 16-byte pieces
+  constexpr int S = rn_bwd_stages(VEC);
   float wv[VEC][8], dwacc[VEC][8];
 #pragma unroll
   for (int i = 0; i < VEC; ++i) {
@@ -108,21 +125,27 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
     }
     if (c < H) load8(w + c, wv[i]);
   }
-  // the raw 16-byte pieces of the next row are requested before the block-wide reduction of the current one, so a
-  // CTA always has two rows in flight
-  uint4 nx[VEC], nd[VEC];
-  auto fetch = [&](long long row) {
+  // The rows of x and dy stream through a ring of S rows in shared memory, filled by per-thread asynchronous copies
+  // (`cp.async`, 16 bytes each, past L1): a CTA keeps S rows of loads in flight without holding them in registers,
+  // and every thread reads back only the pieces it copied itself, so the ring needs no barrier.  One commit group per
+  // row (an empty one past the end), so that "all but the newest S - 1 groups" is always the row about to be used.
+  auto slot = [&](int s, int which, int i) { return rn_ring + ((s * 2 + which) * VEC + i) * RN_THREADS + threadIdx.x; };
+  auto issue = [&](long long row, int s) {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       const int c = (i * RN_THREADS + threadIdx.x) * 8;
       if (row < rows && c < H) {
-        nx[i] = __ldcs(reinterpret_cast<const uint4*>(x + row * H + c));
-        nd[i] = __ldcs(reinterpret_cast<const uint4*>(dy + row * H + c));
+        cp_async_16(slot(s, 0, i), x + row * H + c);
+        cp_async_16(slot(s, 1, i), dy + row * H + c);
       }
     }
+    cp_async_commit();
   };
-  fetch(blockIdx.x);
+#pragma unroll
+  for (int s = 0; s < S; ++s) issue(blockIdx.x + static_cast<long long>(s) * gridDim.x, s);
+  int s = 0;
   for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    cp_async_wait<S - 1>();
     const float r = rstd[row];
     float xh[VEC][8], g[VEC][8];
     float dot = 0.f;
@@ -130,8 +153,9 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
     for (int i = 0; i < VEC; ++i) {
       const int c = (i * RN_THREADS + threadIdx.x) * 8;
       if (c < H) {
-        const uint32_t xw[4] = {nx[i].x, nx[i].y, nx[i].z, nx[i].w};
-        const uint32_t dw4[4] = {nd[i].x, nd[i].y, nd[i].z, nd[i].w};
+        const uint4 nx = *slot(s, 0, i), nd = *slot(s, 1, i);
+        const uint32_t xw[4] = {nx.x, nx.y, nx.z, nx.w};
+        const uint32_t dw4[4] = {nd.x, nd.y, nd.z, nd.w};
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const float2 xv = unpack_bf16x2(xw[q]), dv = unpack_bf16x2(dw4[q]);
@@ -145,7 +169,9 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
         }
       }
     }
-    fetch(row + gridDim.x);
+    // the slot's values are in registers (the arithmetic above used them): refill it with the row S steps ahead
+    issue(row + static_cast<long long>(S) * gridDim.x, s);
+    s = (s + 1 == S) ? 0 : s + 1;
     dot = block_sum<RN_THREADS>(dot, red) / H;
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
@@ -190,7 +216,8 @@ __global__ void __launch_bounds__(128) colsum_stage1_kernel(float* __restrict__ 
   const int c = blockIdx.x * 128 + threadIdx.x;
   if (c >= H) return;
   float s = 0.f;
-  for (int b = blockIdx.y; b < n_rows; b += gridDim.y) s += partial[static_cast<long long>(b) * H + c];
+#pragma unroll 8
+  for (int b = blockIdx.y; b < n_rows; b += gridDim.y) s += partial[static_cast<long long>(b) * H + c];  // loads ahead, adds in order
   partial[static_cast<long long>(blockIdx.y) * H + c] = s;
 }
 __global__ void __launch_bounds__(128) colsum_stage2_kernel(const float* __restrict__ partial, float* __restrict__ dw,
@@ -198,6 +225,7 @@ __global__ void __launch_bounds__(128) colsum_stage2_kernel(const float* __restr
   const int c = blockIdx.x * 128 + threadIdx.x;
   if (c >= H) return;
   float s = 0.f;
+#pragma unroll 8
   for (int y = 0; y < slices; ++y) s += partial[static_cast<long long>(y) * H + c];
   dw[c] += s;
 }
@@ -791,7 +819,7 @@ cudaError_t launch_rmsnorm_fwd(const void* x, const void* w, void* y, float* rst
 }
 
 long long rmsnorm_bwd_partial_rows(long long rows, int num_sms) {
-  return grid_for(rows, 1, (num_sms > 0 ? num_sms : 148) * 8);
+  return grid_for(rows, 1, (num_sms > 0 ? num_sms : 148) * 4);  // one wave of persistent CTAs
 }
 
 cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw,
@@ -803,11 +831,17 @@ cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
   auto xb = reinterpret_cast<const __nv_bfloat16*>(x);
   auto wb = reinterpret_cast<const __nv_bfloat16*>(w);
   auto dxb = reinterpret_cast<__nv_bfloat16*>(dx);
+  static bool configured = false;
+  if (!configured) {  // the largest ring (H up to 8192) is above the default 48 KiB of dynamic shared memory
+    cudaError_t e = cudaFuncSetAttribute(rmsnorm_bwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, rn_bwd_smem(8));
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
   switch (rn_vec_for(H)) {
-    case 1: rmsnorm_bwd_kernel<1><<<grid, RN_THREADS, 0, stream>>>(dyb, xb, wb, rstd, dxb, dw, dw_partial, rows, H); break;
-    case 2: rmsnorm_bwd_kernel<2><<<grid, RN_THREADS, 0, stream>>>(dyb, xb, wb, rstd, dxb, dw, dw_partial, rows, H); break;
-    case 4: rmsnorm_bwd_kernel<4><<<grid, RN_THREADS, 0, stream>>>(dyb, xb, wb, rstd, dxb, dw, dw_partial, rows, H); break;
-    default: rmsnorm_bwd_kernel<8><<<grid, RN_THREADS, 0, stream>>>(dyb, xb, wb, rstd, dxb, dw, dw_partial, rows, H); break;
+    case 1: rmsnorm_bwd_kernel<1><<<grid, RN_THREADS, rn_bwd_smem(1), stream>>>(dyb, xb, wb, rstd, dxb, dw, dw_partial, rows, H); break;
+    case 2: rmsnorm_bwd_kernel<2><<<grid, RN_THREADS, rn_bwd_smem(2), stream>>>(dyb, xb, wb, rstd, dxb, dw, dw_partial, rows, H); break;
+    case 4: rmsnorm_bwd_kernel<4><<<grid, RN_THREADS, rn_bwd_smem(4), stream>>>(dyb, xb, wb, rstd, dxb, dw, dw_partial, rows, H); break;
+    default: rmsnorm_bwd_kernel<8><<<grid, RN_THREADS, rn_bwd_smem(8), stream>>>(dyb, xb, wb, rstd, dxb, dw, dw_partial, rows, H); break;
   }
   if (dw_partial != nullptr) {
     const unsigned slices = grid < 16u ? grid : 16u;
