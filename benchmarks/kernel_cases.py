@@ -71,6 +71,8 @@ def main():
     ap.add_argument("--experts", type=int, default=64, help="experts of the grouped cases")
     ap.add_argument("--hidden", type=int, default=2048, help="model width of the grouped cases")
     ap.add_argument("--ffn", type=int, default=1024, help="FFN width per expert of the grouped cases")
+    ap.add_argument("--router-hidden", type=int, default=4096, help="model width of the router cases")
+    ap.add_argument("--topk", type=int, default=2, help="experts per token of the router cases")
     args = ap.parse_args()
     ext = _ext.ext()
     hbm, tflops_peak, how = peaks()
@@ -112,7 +114,7 @@ def main():
         out.update(fwd_ms=f, fwd_gbs=2 * nb / f / 1e6, fwd_frac=2 * nb / f / 1e6 / hbm, bwd_ms=b,
                    bwd_gbs=3 * nb / b / 1e6, bwd_frac=3 * nb / b / 1e6 / hbm)
     elif args.case == "router":
-        N, H, E, K = 16384 // (2 if args.small else 1), 4096, 64, 2
+        N, H, E, K = 16384 // (2 if args.small else 1), args.router_hidden, 64, args.topk
         x = torch.randn(N, H, device=dev, dtype=bf)
         w = (torch.randn(H, E, device=dev) * 0.02).to(bf)
         from composed_mixture_of_experts_engine_b200.ops.moe_router import fused_router_forward
@@ -121,8 +123,8 @@ def main():
         nbytes = N * H * 2 + H * E * 2 + N * E * 4 + N * K * 8 + N * 4
         out.update(ms=ms, gbs=nbytes / ms / 1e6, frac_of_hbm=nbytes / ms / 1e6 / hbm, tokens_per_s=N / ms * 1e3)
     elif args.case == "router_bwd":
-        # analytic d(logits) kernel + the two tcgen05 GEMMs of the router backward (config-2 shape)
-        N, H, E, K = 16384 // (2 if args.small else 1), 4096, 64, 2
+        # analytic d(logits) kernel + the two tcgen05 GEMMs of the router backward (config-2 shape by default)
+        N, H, E, K = 16384 // (2 if args.small else 1), args.router_hidden, 64, args.topk
         x = torch.randn(N, H, device=dev, dtype=bf)
         w = (torch.randn(H, E, device=dev) * 0.02).to(bf)
         from composed_mixture_of_experts_engine_b200.ops.moe_router import fused_router_forward

@@ -10,7 +10,7 @@ peer-memory kernels); the fused sm_100a paths replace them where they apply.
 
 from __future__ import annotations
 
-from typing import List, Optional
+from typing import List
 
 import torch
 import torch.distributed as dist

@@ -36,7 +36,6 @@ import os
 from typing import Dict, List, Optional
 
 import torch
-import torch.distributed as dist
 
 from ..ops import _ext
 from ..ops import functional as OF

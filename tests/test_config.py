@@ -1,7 +1,6 @@
 """Config tree: YAML files load, validators fire, env overrides coerce, YAML round trip, legacy shim.
 Mirrors the coverage of the reference's tests/test_config.py."""
 
-import os
 import warnings
 from pathlib import Path
 

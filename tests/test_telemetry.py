@@ -1,7 +1,6 @@
 """Telemetry envelope, sinks and thread safety (reference: tests/test_telemetry.py)."""
 
 import json
-import sys
 import threading
 import types
 
