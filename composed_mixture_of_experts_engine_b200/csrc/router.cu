@@ -85,6 +85,8 @@ router_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       (reinterpret_cast<uintptr_t>(s_last + 1) + 7) & ~uintptr_t(7));  // [256]
   unsigned long long* s_z = s_prob + kRouterMaxExperts;
   int* s_cnt = reinterpret_cast<int*>(s_z + 1);  // [256]
+  int* s_topi = s_cnt + kRouterMaxExperts;                      // [kRouterMaxTopK][128] chosen experts, one column per row
+  float* s_topp = reinterpret_cast<float*>(s_topi + kRouterMaxTopK * 128);  // [kRouterMaxTopK][128] their probabilities
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -223,55 +225,52 @@ router_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         warp_transpose_reduce(pv, lane);
         if (c * 32 + lane < E) atomicAdd(&s_prob[c * 32 + lane], __float2ull_rn(pv[0] * kRouterProbScale));
       }
-      // pass 4: top-k by repeated arg-max over TMEM (already chosen experts are masked by bit sets)
+      // pass 4: top-k by repeated arg-max over TMEM (already chosen experts are masked by bit sets).  The loops
+      // over k and over the 32-expert chunks stay rolled: this code runs once per CTA, so every instruction is a
+      // cold fetch, and eight unrolled copies of the compare block cost more in instruction fetches than they
+      // save in loop overhead.  The K results wait in shared memory (one column per thread) for the renormalisation.
       uint32_t sel[8];
 #pragma unroll
       for (int c = 0; c < 8; ++c) sel[c] = 0u;
-      float pk[kRouterMaxTopK];
-      int ik[kRouterMaxTopK];
       float psum = 0.f;
+#pragma unroll 1
+      for (int kk = 0; kk < p.K; ++kk) {
+        float best = -INFINITY;
+        int bi = -1;
+#pragma unroll 1
+        for (int c = 0; c < nch; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_row + c * 32, r);
+          tmem_ld_wait();
+          uint32_t m = 0u;
 #pragma unroll
-      for (int kk = 0; kk < kRouterMaxTopK; ++kk) {
-        pk[kk] = 0.f;
-        ik[kk] = 0;
-        if (kk < p.K) {
-          float best = -INFINITY;
-          int bi = -1;
+          for (int q = 0; q < 8; ++q) m = (q == c) ? sel[q] : m;
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            if (c < nch) {
-              uint32_t r[32];
-              tmem_ld_32x32b_x32(t_row + c * 32, r);
-              tmem_ld_wait();
-              const uint32_t m = sel[c];
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const float v = __uint_as_float(r[j]);
-                const bool cand = (c * 32 + j < E) && (((m >> j) & 1u) == 0u);
-                if (cand && (bi < 0 || v > best)) {
-                  best = v;
-                  bi = c * 32 + j;
-                }
-              }
+          for (int j = 0; j < 32; ++j) {
+            const float v = __uint_as_float(r[j]);
+            const bool cand = (c * 32 + j < E) && (((m >> j) & 1u) == 0u);
+            if (cand && (bi < 0 || v > best)) {
+              best = v;
+              bi = c * 32 + j;
             }
           }
-#pragma unroll
-          for (int c = 0; c < 8; ++c)
-            if (c == (bi >> 5)) sel[c] |= 1u << (bi & 31);
-          ik[kk] = bi;
-          pk[kk] = expf(best - lse);
-          psum += pk[kk];
         }
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          if (c == (bi >> 5)) sel[c] |= 1u << (bi & 31);
+        const float pk = expf(best - lse);
+        psum += pk;
+        s_topi[kk * 128 + et] = bi;
+        s_topp[kk * 128 + et] = pk;
       }
       if (row_ok) {
         const float inv = 1.f / psum;
-#pragma unroll
-        for (int kk = 0; kk < kRouterMaxTopK; ++kk) {
-          if (kk < p.K) {
-            p.topk_idx[row * p.K + kk] = ik[kk];
-            p.topk_w[row * p.K + kk] = pk[kk] * inv;
-            atomicAdd(&s_cnt[ik[kk]], 1);
-          }
+#pragma unroll 1
+        for (int kk = 0; kk < p.K; ++kk) {
+          const int e = s_topi[kk * 128 + et];
+          p.topk_idx[row * p.K + kk] = e;
+          p.topk_w[row * p.K + kk] = s_topp[kk * 128 + et] * inv;
+          atomicAdd(&s_cnt[e], 1);
         }
       }
       const float z = warp_sum(row_ok ? lse * lse : 0.f);
@@ -465,7 +464,7 @@ cudaError_t launch_router_fwd(const RouterFwdArgs& a, cudaStream_t stream) {
   p.status = a.status;
   p.timeout_ns = a.timeout_ns ? a.timeout_ns : kDefaultTimeoutNs;
 
-  const int smem = stages * stage_bytes + 1024 + 512 + kRouterMaxExperts * (8 + 4) + 64;
+  const int smem = stages * stage_bytes + 1024 + 512 + kRouterMaxExperts * (8 + 4) + kRouterMaxTopK * 128 * 8 + 64;
   static int configured_smem = 0;
   if (smem > configured_smem) {
     e = cudaFuncSetAttribute(router_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

@@ -261,7 +261,7 @@ def test_router_fwd_bwd(ext, status, N, H, E, K):
     assert _rel_err(glb, lg.grad) < 1e-2
 
 
-@pytest.mark.parametrize("rows,H", [(37, 128), (512, 2048), (100, 4096)])
+@pytest.mark.parametrize("rows,H", [(37, 128), (512, 2048), (100, 4096), (5000, 2048), (70, 8192)])
 def test_rmsnorm(ext, rows, H):
     torch.manual_seed(6)
     x = torch.randn(rows, H, device="cuda", dtype=torch.bfloat16)
