@@ -60,6 +60,12 @@ def main() -> int:
                 time.sleep(stall)
             super().put(key, payload)
 
+        def put_torch(self, key, obj):
+            if stall > 0 and not Store.stalled:
+                Store.stalled = True
+                time.sleep(stall)
+            super().put_torch(key, obj)
+
     ckpt = AsyncCheckpointer(Store(str(work / "ckpts")), None, retention=100, workers=1)
     log = (work / f"rank{rank}_gen{generation}.jsonl").open("a", buffering=1)
     start, cum_tokens = 0, 0

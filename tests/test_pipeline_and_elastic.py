@@ -11,6 +11,7 @@ import torch
 import torch.nn as nn
 
 from composed_mixture_of_experts_engine_b200.elastic import (CHECKPOINT_SCHEMA_VERSION, AsyncCheckpointer,
+                                                              ObjectStoreAdapter,
                                                              ClusterStateMachine, ElasticConfig,
                                                              ElasticTrainerHarness, LocalNVMeAdapter,
                                                              _check_schema_compatibility, _largest_divisor_le)
@@ -137,6 +138,10 @@ def test_pruning_never_deletes_a_newer_step_that_is_still_being_written(tmp_path
             time.sleep(random.Random(hash(key) & 0xFFFF).random() * 0.02)
             super().put(key, payload)
 
+        def put_torch(self, key, obj):
+            time.sleep(random.Random(hash(key) & 0xFFFF).random() * 0.02)
+            super().put_torch(key, obj)
+
     m, opt = _model_and_opt()
     local, remote = LocalNVMeAdapter(str(tmp_path / "l")), Jittery(str(tmp_path / "r"), use_odirect=False)
     ck = AsyncCheckpointer(local, remote, retention=1, workers=4)
@@ -161,6 +166,10 @@ def test_save_does_not_wait_for_slow_storage(tmp_path):
             time.sleep(0.3)
             super().put(key, payload)
 
+        def put_torch(self, key, obj):
+            time.sleep(0.3)
+            super().put_torch(key, obj)
+
     m, opt = _model_and_opt()
     ck = AsyncCheckpointer(Slow(str(tmp_path)), None, workers=1)
     t0 = time.perf_counter()
@@ -168,6 +177,54 @@ def test_save_does_not_wait_for_slow_storage(tmp_path):
     assert time.perf_counter() - t0 < 0.25  # enqueue only
     ck.shutdown(drain=True)
     assert ck.latest_step() == 1
+
+
+def test_checkpoint_files_are_written_without_an_in_memory_copy(tmp_path):
+    """The workers hand the snapshot itself to a local adapter (`put_torch`: torch's file writer, which does not
+    hold the interpreter lock) and only small objects go through `put(bytes)`; an adapter without `put_torch`
+    (an object store) still gets the serialised bytes."""
+    seen = []
+
+    class Spy(LocalNVMeAdapter):
+        def put(self, key, payload):
+            seen.append(("put", key, len(payload)))
+            super().put(key, payload)
+
+    class BytesOnly(ObjectStoreAdapter):
+        """An adapter of the reference's interface only (what an object store offers)."""
+
+        def __init__(self, root):
+            self.inner = LocalNVMeAdapter(root, use_odirect=False)
+
+        def put(self, key, payload):
+            seen.append(("remote", key, len(payload)))
+            self.inner.put(key, payload)
+
+        def get(self, key):
+            return self.inner.get(key)
+
+        def list(self, prefix):
+            return self.inner.list(prefix)
+
+        def delete(self, key):
+            self.inner.delete(key)
+
+        def _p(self, key):
+            return self.inner._p(key)
+
+    m, opt = _model_and_opt()
+    local, remote = Spy(str(tmp_path / "l")), BytesOnly(str(tmp_path / "r"))
+    ck = AsyncCheckpointer(local, remote, workers=1)
+    ck.save(m, opt, 3)
+    ck.shutdown()
+    assert ck.last_error is None
+    assert [k for kind, k, _ in seen if kind == "put"] == ["ckpts/step=000003/rank=000000.meta.json"]
+    assert ("ckpts/step=000003/rank=000000.pt" in [k for kind, k, _ in seen if kind == "remote"])
+    for store in (local, remote):
+        state = torch.load(store._p("ckpts/step=000003/rank=000000.pt"), map_location="cpu", weights_only=False)
+        assert set(state) >= {"model"}
+        for k, v in m.state_dict().items():
+            assert torch.equal(state["model"][k], v)
 
 
 def test_worker_survives_a_failing_store(tmp_path):
@@ -179,6 +236,12 @@ def test_worker_survives_a_failing_store(tmp_path):
             if Flaky.n == 1:
                 raise OSError("injected storage failure")
             super().put(key, payload)
+
+        def put_torch(self, key, obj):
+            Flaky.n += 1
+            if Flaky.n == 1:
+                raise OSError("injected storage failure")
+            super().put_torch(key, obj)
 
     m, opt = _model_and_opt()
     ck = AsyncCheckpointer(Flaky(str(tmp_path)), None, workers=1)
