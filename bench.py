@@ -244,7 +244,8 @@ def run_ours(args) -> dict:
         loss = trainer.train_step(ids, tgt)  # H2D copy of the pinned batch happens inside
         losses.append(float(loss.item()))     # D2H read of the step result
         if ckpt is not None and i == args.ckpt_step:
-            ckpt.save(trainer.model, None if args.ckpt_model_only else trainer.optimizer, 1000 + i, rank=rank)
+            ckpt.save(trainer.model, None if args.ckpt_model_only else trainer.optimizer, 1000 + i, rank=rank,
+                      guard_with=trainer.optimizer)
 
     for i in range(args.warmup):
         dev_step(i)

@@ -433,10 +433,14 @@ class AsyncCheckpointer:
         return {"model": dict(model.state_dict()), "optim": osd}
 
     def save(self, model: torch.nn.Module, optimizer, step: int, rank: int = 0,
-             extra_meta: Optional[Dict[str, Any]] = None) -> None:
+             extra_meta: Optional[Dict[str, Any]] = None, guard_with=None) -> None:
+        """Enqueue a checkpoint of ``model`` (and ``optimizer`` unless None).  ``guard_with``: the optimizer that
+        updates ``model`` when it is not the one being saved (weights-only checkpoints): its next step, not this
+        call, then waits for the device-to-host copy."""
         t0 = time.perf_counter()
+        hook_on = optimizer if optimizer is not None else guard_with
         snapshot, event, bufset = self._stager.snapshot(self._state(model, optimizer),
-                                                        defer_guard=self._guard_from_optimizer(optimizer))
+                                                        defer_guard=self._guard_from_optimizer(hook_on))
         meta = {
             "schema_version": CHECKPOINT_SCHEMA_VERSION,
             "step": step,
