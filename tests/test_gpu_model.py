@@ -240,6 +240,19 @@ def test_async_checkpoint_of_device_state_reuses_pinned_buffers_and_does_not_sta
         assert torch.equal(got["optim"]["groups"]["dense"]["master"], master.cpu())
     assert first_allocs > 0 and ck._stager.allocations == first_allocs  # saves 2 and 3 reused the pinned set
     assert len(opt._pre_step_hooks) == 1 and ck.last_d2h_ms > 0.0
+    # a weights-only save has no optimizer of its own to hook: `guard_with` names the one that updates the weights,
+    # so this save too leaves the wait to that optimizer's next step, and the file holds the weights as they were
+    want4 = {k: v.detach().clone() for k, v in net.state_dict().items()}
+    ck.save(net, None, 4, guard_with=opt)
+    assert ck._stager._pending is not None  # deferred, not waited for inside save()
+    for p in net.parameters():
+        p.main_grad.normal_()
+    opt.step()
+    assert ck._stager._pending is None
+    ck._q.join()
+    got = ck.load_raw(4)
+    for k, v in want4.items():
+        assert torch.equal(got["model"][k], v.cpu()), k
     ck.shutdown()
 
 
