@@ -110,22 +110,27 @@ if typer is not None:
     @app.command()
     def train(config: str = typer.Option(..., "--config", "-c"), nproc: int = typer.Option(1, "--nproc"),
               max_steps: Optional[int] = typer.Option(None, "--max-steps"), smoke: bool = typer.Option(False, "--smoke")):
+        """Validate CONFIG, then train: in this process (--nproc 1) or as NPROC ranks under torchrun on this node."""
         raise typer.Exit(cmd_train(config, nproc, max_steps, smoke))
 
     @app.command()
     def benchmark(cuda: bool = typer.Option(False, "--cuda"), json_out: Optional[str] = typer.Option(None, "--json")):
+        """Router / MoE-layer / token-conservation micro-benchmarks (benchmarks/run_benchmark.py)."""
         raise typer.Exit(cmd_benchmark(cuda, json_out))
 
     @app.command()
     def plan(config: str = typer.Option(..., "--config", "-c"), world: Optional[int] = typer.Option(None, "--world")):
+        """Per-GPU memory plan of CONFIG (weights, optimizer state, activations, transport buffers) against 180 GB."""
         raise typer.Exit(cmd_plan(config, world))
 
     @app.command()
     def validate(paths: List[str] = typer.Argument(...)):
+        """Validate YAML configs (files or directories); exit status 1 if any fails."""
         raise typer.Exit(cmd_validate(paths))
 
     @app.command()
     def info():
+        """Versions, devices, registered models and whether the sm_100a extension is built."""
         raise typer.Exit(cmd_info())
 
 
