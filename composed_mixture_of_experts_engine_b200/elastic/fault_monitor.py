@@ -162,13 +162,20 @@ class LocalNVMeAdapter(ObjectStoreAdapter):
         p = self._p(key)
         _make_dirs(p.parent)
         tmp = p.with_suffix(p.suffix + ".tmp")
-        torch.save(obj, str(tmp))
-        fd = os.open(str(tmp), os.O_RDONLY)
         try:
-            os.fsync(fd)
-        finally:
-            os.close(fd)
-        tmp.replace(p)
+            torch.save(obj, str(tmp))
+            fd = os.open(str(tmp), os.O_RDONLY)
+            try:
+                os.fsync(fd)
+            finally:
+                os.close(fd)
+            tmp.replace(p)
+        except BaseException:
+            try:  # no half-written file is left behind under a name that `list` would show
+                tmp.unlink()
+            except OSError:
+                pass
+            raise
         self.last_write_used_odirect = False
 
     def _write_chunked(self, path: Path, payload: bytes, chunk_bytes: Optional[int] = None) -> None:
