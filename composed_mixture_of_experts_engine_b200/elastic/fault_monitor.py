@@ -178,6 +178,17 @@ class LocalNVMeAdapter(ObjectStoreAdapter):
             raise
         self.last_write_used_odirect = False
 
+    def get_torch(self, key: str) -> Any:
+        """``torch.load`` of the file of ``key`` without an in-memory copy of the whole file: tensor storages are
+        memory-mapped (the mapping stays valid if a pruner unlinks the file meanwhile)."""
+        p = self._p(key)
+        if not p.is_file():
+            raise FileNotFoundError(str(p))
+        try:
+            return torch.load(str(p), map_location="cpu", weights_only=False, mmap=True)
+        except (RuntimeError, ValueError):  # not a zip-format file (written by an older `put(bytes)` of legacy pickles)
+            return torch.load(str(p), map_location="cpu", weights_only=False)
+
     def _write_chunked(self, path: Path, payload: bytes, chunk_bytes: Optional[int] = None) -> None:
         lib = _load_io_lib()
         view = memoryview(payload)
@@ -496,7 +507,19 @@ class AsyncCheckpointer:
             return payload
 
     def load_raw(self, step: int, rank: int = 0) -> Dict[str, Any]:
-        return _torch_loads(self._fetch(f"ckpts/step={step:06d}/rank={rank:06d}.pt"))
+        key = f"ckpts/step={step:06d}/rank={rank:06d}.pt"
+        read_file = getattr(self.local, "get_torch", None)
+        if read_file is not None:
+            # a local file is deserialised from the file itself (tensors mapped, not read into a bytes object and
+            # copied again); a miss falls through to the remote tier, which re-hydrates the local one
+            try:
+                return read_file(key)
+            except FileNotFoundError:
+                if self.remote is None:
+                    raise
+                self._fetch(key)
+                return read_file(key)
+        return _torch_loads(self._fetch(key))
 
     def load(self, model: torch.nn.Module, optimizer, step: int, rank: int = 0) -> Dict[str, Any]:
         obj = self.load_raw(step, rank)
