@@ -11,7 +11,8 @@ from composed_mixture_of_experts_engine_b200.utils.config import (ConfigValidati
                                                                   load_config)
 
 pytestmark = pytest.mark.cpu
-CONFIGS = Path(__file__).resolve().parent.parent / "configs"
+ROOT = Path(__file__).resolve().parent.parent
+CONFIGS = ROOT / "configs"
 
 
 @pytest.mark.parametrize("name", ["default", "smoke", "large_scale", "olmoe_1b7b", "mixtral_8x7b", "cpu_smoke_ep2",
@@ -159,3 +160,33 @@ def test_mark_expert_params_tags_only_the_stacked_expert_weights():
     tagged = {n for n, p in model.named_parameters() if getattr(p, "is_expert_param", False)}
     assert tagged == {f"blocks.{i}.moe.{w}" for i in range(c.model.num_layers) for w in ("w13", "w2")}
     assert apply_fsdp2(model, topo) is model  # dp == 1: nothing else to set up
+
+
+def test_validate_config_script_reports_per_file_and_sets_the_exit_status(tmp_path, capsys):
+    """`scripts/validate_config.py`: directories expand to their YAML files, a bad file fails only itself, a missing
+    path or an empty selection is an error (reference: scripts/validate_config.py)."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("validate_config_script", ROOT / "scripts" / "validate_config.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+
+    assert mod.main([str(ROOT / "configs")]) == 0
+    out = capsys.readouterr().out
+    assert "smoke.yaml" in out and "config(s) valid" in out and "FAIL" not in out
+
+    good = tmp_path / "good.yml"
+    good.write_text((ROOT / "configs" / "smoke.yaml").read_text())
+    bad = tmp_path / "bad.yaml"
+    bad.write_text("model:\n  top_k: 99\n  num_experts: 8\n")
+    broken = tmp_path / "broken.yaml"
+    broken.write_text("model: [unclosed\n")
+    assert mod.main([str(tmp_path)]) == 1
+    out = capsys.readouterr().out
+    assert out.count("FAIL") == 2 and "good.yml" in out and "1 of 3 config(s) valid, 2 failed" in out
+
+    assert mod.main([str(tmp_path / "nowhere.yaml")]) == 1
+    empty = tmp_path / "empty"
+    empty.mkdir()
+    assert mod.main([str(empty)]) == 1
+    assert mod.main([]) == 2
