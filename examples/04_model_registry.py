@@ -38,4 +38,13 @@ for arch in ("toy_moe", "moe_decoder", "two_layer_moe"):
     model = build_model_from_config(cfg, topo, arch=arch)
     out = model(torch.randint(0, 256, (2, 16)))
     print(f"{arch:14s} params={sum(p.numel() for p in model.parameters()):8d} output={tuple(out.shape)}")
+# the two mistakes the registry catches: registering a name twice, asking for a name nobody registered
+try:
+    register_model("two_layer_moe")(TwoLayerMoE)
+except ValueError as exc:
+    print("duplicate ->", exc)
+try:
+    build_model_from_config(cfg, topo, arch="no_such_model")
+except KeyError as exc:
+    print("unknown   ->", str(exc)[:100])
 ModelRegistry.unregister("two_layer_moe")
