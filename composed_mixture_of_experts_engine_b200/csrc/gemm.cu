@@ -15,7 +15,9 @@
 // Plain results leave through a 32 KiB swizzled staging area and TMA: `cp.async.bulk.tensor` stores, or
 // `cp.reduce.async.bulk.tensor ... add` when the fp32 result accumulates into global memory (weight gradients),
 // so the SM never reads the old values; rows that scatter to other ranks are copied out of the staging area
-// with whole-row coalesced stores.
+// with whole-row coalesced stores.  The SwiGLU epilogues use the same area in 64-byte-swizzled pieces of 32 columns:
+// the forward stages h / gate / up and stores them with TMA, the backward receives the saved gate / up pieces by TMA
+// one piece ahead, overwrites them in place with dGate / dUp and stores those with TMA.
 #include "gemm.cuh"
 
 #include <cstdio>

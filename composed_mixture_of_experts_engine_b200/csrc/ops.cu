@@ -185,7 +185,7 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
     }
   }
   if (dw_partial) {
-    // one row of partial column sums per CTA, summed by colsum_add_kernel: thousands of CTAs adding atomically to
+    // one row of partial column sums per CTA, summed in a fixed order by the colsum kernels: CTAs adding atomically to
     // the same H addresses serialise in L2 and cost more than the whole row pass
     float* out = dw_partial + static_cast<long long>(blockIdx.x) * H;
 #pragma unroll
