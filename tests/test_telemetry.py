@@ -89,3 +89,21 @@ def test_phase_timer_cpu_and_overlap():
     assert off.resolve() == {}
     assert overlap_ratio(1.0, 2.0, 2.0) == 1.0 and overlap_ratio(1.0, 2.0, 3.0) == 0.0
     assert overlap_ratio(0.0, 1.0, 1.0) == 0.0 and overlap_ratio(2.0, 2.0, 3.0) == 0.5
+
+
+def test_pull_overlap_ratio_from_device_stamps():
+    """The overlap ratio of the fused dispatch is the share of the transfer interval [first pull, last pull] that
+    lies inside the tensor-core interval [first MMA, last MMA] (reference semantics of `last_overlap_ratio`:
+    pkg/distributed/moe_layer.py:340-341); a launch that pulled nothing reports None."""
+    import torch
+
+    from composed_mixture_of_experts_engine_b200.ops import kernels
+
+    i64max = kernels._I64_MAX
+    t = lambda *v: torch.tensor(v, dtype=torch.int64)
+    assert kernels.pull_overlap_ratio(t(100, 700, 120, 1100)) == pytest.approx(580 / 600)   # MMAs start 20 ns in
+    assert kernels.pull_overlap_ratio(t(100, 700, 0, 2000)) == 1.0                          # transfer fully covered
+    assert kernels.pull_overlap_ratio(t(100, 700, 800, 900)) == 0.0                         # disjoint intervals
+    assert kernels.pull_overlap_ratio(t(100, 700, 400, 500)) == pytest.approx(100 / 600)    # MMAs inside the transfer
+    assert kernels.pull_overlap_ratio(t(i64max, 0, i64max, 0)) is None                      # nothing recorded
+    assert kernels.pull_overlap_ratio(t(100, 100, 50, 60)) is None                          # empty transfer interval
