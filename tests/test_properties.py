@@ -71,3 +71,20 @@ def test_config_validity_matches_rules(h, e, k):
         assert ok
     except ConfigValidationError:
         assert not ok
+
+
+def test_expert_parallel_buffer_sizing(monkeypatch):
+    """Row capacity of the expert-parallel buffers: a multiple of the 128-row tile, at least the expected rows plus one
+    tile of padding per local expert, never above the worst case (every slot routed here), scaled by the factor."""
+    from composed_mixture_of_experts_engine_b200.ops.kernels import ep_buffer_rows, plan_capacity_rows
+
+    monkeypatch.delenv("CMOE_EP_BUFFER_FACTOR", raising=False)
+    for n_slots, n_local in ((1, 1), (1000, 8), (131072, 16), (7, 64)):
+        cap = plan_capacity_rows(n_slots, n_local)
+        assert cap % 128 == 0 and cap >= n_slots + n_local * 127 and cap - (n_slots + n_local * 127) < 128
+    expected, n_local, worst = 131072, 8, 8 * 131072
+    rows = ep_buffer_rows(expected, n_local, worst)
+    assert rows % 128 == 0 and rows >= int(1.5 * expected) + n_local * 128 and rows < worst
+    assert ep_buffer_rows(expected, n_local, expected) == plan_capacity_rows(expected, n_local)  # capped by the worst case
+    monkeypatch.setenv("CMOE_EP_BUFFER_FACTOR", "1.0")
+    assert ep_buffer_rows(expected, n_local, worst) < rows
