@@ -1,5 +1,6 @@
 """Structured telemetry sinks."""
 
-from .logger import PhaseTimer, PrometheusExporter, StepRecord, StructuredLogger, WandBSink  # noqa: F401
+from .logger import (DeviceClockReader, PhaseTimer, PrometheusExporter, StepRecord, StructuredLogger,  # noqa: F401
+                     WandBSink)
 
 __all__ = ["StepRecord", "StructuredLogger", "WandBSink", "PrometheusExporter", "PhaseTimer"]

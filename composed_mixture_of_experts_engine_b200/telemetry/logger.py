@@ -76,6 +76,56 @@ class StepRecord:
             self.routing.setdefault(name, getattr(self, name))
 
 
+class DeviceClockReader:
+    """Reads (never sets) the SM clock, power draw and active clock-event reasons of one GPU through NVML.
+
+    On a power-capped part the sustained SM clock decides the step time (the same kernels ran 4 % apart on two
+    boxes whose clocks settled at 1406 and 1462 MHz), so a throughput figure without the clock beside it cannot
+    be compared across machines.  ``read()`` returns ``{}`` when NVML or the ``pynvml`` module is not there.
+    """
+
+    _REASONS = (("hw_slowdown", "nvmlClocksEventReasonHwSlowdown", "nvmlClocksThrottleReasonHwSlowdown"),
+                ("hw_thermal_slowdown", "nvmlClocksEventReasonHwThermalSlowdown",
+                 "nvmlClocksThrottleReasonHwThermalSlowdown"),
+                ("sw_thermal_slowdown", "nvmlClocksEventReasonSwThermalSlowdown",
+                 "nvmlClocksThrottleReasonSwThermalSlowdown"),
+                ("sw_power_cap", "nvmlClocksEventReasonSwPowerCap", "nvmlClocksThrottleReasonSwPowerCap"))
+
+    def __init__(self, device_index: int = 0, nvml: Any = None):
+        self._nvml, self._handle = None, None
+        try:
+            if nvml is None:
+                import pynvml as nvml  # type: ignore
+            nvml.nvmlInit()
+            self._nvml, self._handle = nvml, nvml.nvmlDeviceGetHandleByIndex(device_index)
+        except Exception:
+            self._nvml = None
+
+    def read(self) -> Dict[str, Any]:
+        n, h = self._nvml, self._handle
+        if n is None:
+            return {}
+        out: Dict[str, Any] = {}
+        try:
+            out["sm_clock_mhz"] = int(n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM))
+            out["sm_clock_max_mhz"] = int(n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM))
+            out["power_w"] = round(n.nvmlDeviceGetPowerUsage(h) / 1000.0, 1)
+            get = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                getattr(n, "nvmlDeviceGetCurrentClocksThrottleReasons")
+            mask = int(get(h))
+            active = []
+            for name, new_const, old_const in self._REASONS:
+                bit = getattr(n, new_const, None)
+                if bit is None:
+                    bit = getattr(n, old_const, 0)
+                if mask & int(bit):
+                    active.append(name)
+            out["clock_event_reasons"] = active
+        except Exception:
+            pass
+        return out
+
+
 def _nvtx_enabled() -> bool:
     """``CMOE_NVTX=1`` wraps every timed phase (and the trainer's microbatches / optimizer step) in an NVTX range."""
     return os.environ.get("CMOE_NVTX", "0") not in ("", "0") and torch.cuda.is_available()
@@ -286,6 +336,7 @@ class StructuredLogger:
             Path(tensorboard_dir).mkdir(parents=True, exist_ok=True)
             self._tb = SummaryWriter(log_dir=tensorboard_dir)
         self._peak_mem_prev = 0.0
+        self._clocks = DeviceClockReader(torch.cuda.current_device()) if torch.cuda.is_available() else None
         self._prom = PrometheusExporter(port=prometheus_port, rank=rank) if prometheus_port > 0 else None
         self._wandb = WandBSink(rank=rank, enabled=wandb_enabled, init_kwargs=wandb_init_kwargs)
 
@@ -299,6 +350,8 @@ class StructuredLogger:
                 "leak_delta_gb": round(alloc_gb - self._peak_mem_prev, 4),
             }
             self._peak_mem_prev = alloc_gb
+        if self._clocks is not None and "sm_clock_mhz" not in record.infra:
+            record.infra.update(self._clocks.read())  # clock, power, active clock-event reasons at emit time
         payload = asdict(record)
         payload["rank"] = self.rank
         payload["ts"] = time.time()

@@ -107,3 +107,61 @@ def test_pull_overlap_ratio_from_device_stamps():
     assert kernels.pull_overlap_ratio(t(100, 700, 400, 500)) == pytest.approx(100 / 600)    # MMAs inside the transfer
     assert kernels.pull_overlap_ratio(t(i64max, 0, i64max, 0)) is None                      # nothing recorded
     assert kernels.pull_overlap_ratio(t(100, 100, 50, 60)) is None                          # empty transfer interval
+
+
+def test_device_clock_reader_reads_nvml_without_changing_anything(tmp_path, monkeypatch):
+    """Clock, power and active clock-event reasons come from read-only NVML queries (tested against a fake NVML that
+    fails on any call that is not a query); without NVML the reader returns an empty dict."""
+    from composed_mixture_of_experts_engine_b200.telemetry.logger import DeviceClockReader
+
+    class FakeNvml:
+        NVML_CLOCK_SM = 1
+        nvmlClocksEventReasonHwSlowdown = 0x8
+        nvmlClocksEventReasonSwPowerCap = 0x4
+        nvmlClocksEventReasonHwThermalSlowdown = 0x40
+        nvmlClocksEventReasonSwThermalSlowdown = 0x20
+        calls = []
+
+        def nvmlInit(self):
+            self.calls.append("init")
+
+        def nvmlDeviceGetHandleByIndex(self, i):
+            self.calls.append(("handle", i))
+            return ("gpu", i)
+
+        def nvmlDeviceGetClockInfo(self, h, kind):
+            return 1462
+
+        def nvmlDeviceGetMaxClockInfo(self, h, kind):
+            return 1965
+
+        def nvmlDeviceGetPowerUsage(self, h):
+            return 992410  # milliwatts
+
+        def nvmlDeviceGetCurrentClocksEventReasons(self, h):
+            return 0x4
+
+        def __getattr__(self, name):  # anything else (a setter, a reset) is a test failure
+            raise AssertionError(f"unexpected NVML call {name}")
+
+    fake = FakeNvml()
+    got = DeviceClockReader(3, nvml=fake).read()
+    assert got == {"sm_clock_mhz": 1462, "sm_clock_max_mhz": 1965, "power_w": 992.4,
+                   "clock_event_reasons": ["sw_power_cap"]}
+    assert ("handle", 3) in fake.calls
+
+    class Broken:
+        def nvmlInit(self):
+            raise RuntimeError("no driver")
+
+    assert DeviceClockReader(0, nvml=Broken()).read() == {}
+
+    # the logger merges the reading into the infra block of a record that does not carry one already
+    logger = StructuredLogger(json_path=str(tmp_path / "s.jsonl"), tensorboard_dir=None, rank=0, also_stdout=False,
+                              wandb_enabled=False)
+    logger._clocks = DeviceClockReader(0, nvml=fake)
+    logger.emit(StepRecord(step=1, loss=1.0, mfu=0.5, tokens_per_sec=1e5, infra={"restart_count": 0}))
+    logger.close()
+    rec = json.loads((tmp_path / "s.jsonl").read_text().splitlines()[-1])
+    assert rec["infra"]["sm_clock_mhz"] == 1462 and rec["infra"]["restart_count"] == 0
+    assert rec["infra"]["clock_event_reasons"] == ["sw_power_cap"]
