@@ -211,6 +211,8 @@ def main(argv=None) -> int:
                 step=step, loss=loss, mfu=res.mfu, tokens_per_sec=res.tokens_per_sec * topo.data_replicas,
                 kernel=blocks["kernel"], collective=blocks["collective"],
                 infra={"async_ckpt_commit_ms": harness.async_ckpt.last_commit_ms,
+                       "async_ckpt_d2h_ms": harness.async_ckpt.last_d2h_ms,
+                       "async_ckpt_write_ms": harness.async_ckpt.last_write_ms,
                        "active_nodes": len(harness.state.alive_ranks()), "ep_world_size": topo.ep_size,
                        "lr": _get_lr(step, cfg), "grad_accum": t.gradient_accumulation_steps},
                 routing=blocks["routing"], wall_clock_ms=dt * 1e3, **blocks["extra"])
